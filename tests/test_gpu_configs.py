@@ -1,0 +1,86 @@
+"""GPU parity on the benchmark configurations, end to end through runner.run() on the cuda backend,
+against the CPU oracle run on the same seeded inputs and weights."""
+import numpy as np
+import pytest
+
+from oracle import ref_runner
+from webdnn_b200 import zoo
+
+from util import max_err_rel_linf, run_cuda
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-4
+
+
+def _all_on_cuda(r):
+    assert all(b == "cuda" for _, _, b in r.node_backends), [n for n in r.node_backends if n[2] != "cuda"]
+
+
+@pytest.mark.parametrize("trans_b", [True, False])
+def test_config1_mlp(cuda_context, trans_b):
+    model = zoo.mlp(64, trans_b)
+    x = zoo.make_input((64, 784), "uniform")
+    (want,) = ref_runner.run_model(model, [x])
+    (got,), r = run_cuda(model, [x], cuda_context, return_runner=True)
+    _all_on_cuda(r)
+    assert [t for _, t, _ in r.node_backends] == ["CudaGemmRelu", "CudaGemmRelu", "Gemm", "Softmax"]
+    r.dispose()
+    assert got.shape == (64, 10)
+    assert max_err_rel_linf(got, want) <= TOL
+
+
+def test_config2_conv_bn_relu_full_size(cuda_context):
+    model = zoo.conv_bn_relu(32, 64, 56)
+    x = zoo.make_input((32, 64, 56, 56))
+    (want,) = ref_runner.run_model(model, [x])
+    (got,), r = run_cuda(model, [x], cuda_context, return_runner=True)
+    _all_on_cuda(r)
+    assert [t for _, t, _ in r.node_backends] == ["CudaConvFused"]
+    r.dispose()
+    assert max_err_rel_linf(got, want) <= TOL
+
+
+def test_config2_unfused_nodes_agree(cuda_context):
+    """Conv, BatchNormalization and Relu as separate cuda nodes (graph outputs block the fusion)."""
+    model = zoo.conv_bn_relu(2, 64, 28)
+    from webdnn_b200 import onnx_io
+    for n in model.graph.node[:2]:
+        model.graph.output.append(onnx_io.ValueInfo(n.output[0], onnx_io.FLOAT, []))
+    x = zoo.make_input((2, 64, 28, 28))
+    want = ref_runner.run_model(model, [x])
+    got, r = run_cuda(model, [x], cuda_context, return_runner=True)
+    assert [t for _, t, _ in r.node_backends] == ["Conv", "BatchNormalization", "Relu"]
+    r.dispose()
+    for g, w in zip(got, want):
+        assert max_err_rel_linf(g, w) <= TOL
+
+
+@pytest.mark.parametrize("batch", [1, 2])
+def test_config3_resnet50(cuda_context, batch):
+    model = zoo.resnet50(batch)
+    x = zoo.make_input((batch, 3, 224, 224))
+    values = ref_runner.run_model(model, [x], return_all=True)
+    want = values[model.graph.output[0].name]
+    logits_name = model.graph.node[-1].input[0]
+    # also expose the logits: the softmax of this random-init net is one-hot, logits carry the signal
+    from webdnn_b200 import onnx_io
+    model.graph.output.append(onnx_io.ValueInfo(logits_name, onnx_io.FLOAT, []))
+    (got, got_logits), r = run_cuda(model, [x], cuda_context, return_runner=True)
+    _all_on_cuda(r)
+    types = [t for _, t, _ in r.node_backends]
+    assert types.count("CudaConvFused") == 53 and "BatchNormalization" not in types and "Add" not in types
+    r.dispose()
+    assert max_err_rel_linf(got_logits, values[logits_name]) <= TOL
+    assert max_err_rel_linf(got, want) <= TOL
+
+
+def test_config4_lstm(cuda_context):
+    model = zoo.lstm(128, 64, 256, 512)
+    x = zoo.make_input((128, 64, 256))
+    want = ref_runner.run_model(model, [x])
+    got, r = run_cuda(model, [x], cuda_context, return_runner=True)
+    _all_on_cuda(r)
+    r.dispose()
+    for g, w in zip(got, want):
+        assert g.shape == w.shape
+        assert max_err_rel_linf(g, w) <= 1e-3  # the stated LSTM tolerance after 128 steps

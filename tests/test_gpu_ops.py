@@ -1,0 +1,189 @@
+"""GPU parity: every single-op case runs through the shipped runner on the cuda backend (which calls
+the C ABI) and is compared with the CPU oracle on the same inputs, and with the golden tensors.
+
+Tolerances: integer / indexing ops bit-exact; floating point max|a-e| <= 1e-4 * ||e||_inf.
+"""
+import numpy as np
+import pytest
+
+from oracle import ops, ref_runner
+
+from util import known_answers, max_err_rel_linf, run_cuda, single_op_model, torch_cases
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-4
+EXACT_UNARY = {"Relu", "Abs", "Neg", "Ceil", "Floor", "Sign", "Round", "Identity"}
+
+
+def _check_all_on_cuda(runner):
+    assert runner.node_backends and all(b == "cuda" for _, _, b in runner.node_backends), runner.node_backends
+
+
+def test_relu_known_answer(cuda_context):
+    ka = known_answers()["relu_vector"]
+    x = np.asarray(ka["input"], np.float32)
+    (y,), r = run_cuda(single_op_model("Relu", {}, [x]), [x], cuda_context, return_runner=True)
+    _check_all_on_cuda(r)
+    assert y.tolist() == ka["expected"] and list(y.shape) == ka["dims"]
+    r.dispose()
+
+
+def test_relu_js_edge_semantics(cuda_context):
+    x = np.asarray([np.nan, -0.0, 0.0, -1.0, np.inf, -np.inf, 1e-45], np.float32)
+    (y,) = run_cuda(single_op_model("Relu", {}, [x]), [x], cuda_context)
+    e = ops.unary("Relu", x)
+    assert np.array_equal(y.view(np.uint32)[1:], e.view(np.uint32)[1:]) and np.isnan(y[0])
+
+
+@pytest.mark.parametrize("name", sorted(torch_cases()))
+def test_case_matches_oracle_and_golden(cuda_context, name):
+    case = torch_cases()[name]
+    model = single_op_model(case["op"], case["attrs"], case["inputs"], n_out=len(case["outputs"]))
+    want = ref_runner.run_model(model, case["inputs"])
+    got, r = run_cuda(model, case["inputs"], cuda_context, return_runner=True)
+    _check_all_on_cuda(r)
+    r.dispose()
+    for g, w, gold in zip(got, want, case["outputs"]):
+        assert list(g.shape) == list(w.shape), (g.shape, w.shape)
+        if w.dtype == np.int32:
+            assert np.array_equal(g, w)
+            continue
+        if case["op"] in EXACT_UNARY or case["op"] in ("MaxPool", "ReduceMax", "ReduceMin"):
+            assert np.array_equal(g.view(np.uint32), w.view(np.uint32)), name
+        assert max_err_rel_linf(g, w) <= TOL, name
+        assert max_err_rel_linf(g, gold) <= TOL, name
+
+
+UNARY_DOMAINS = {"Acos": (-1, 1), "Asin": (-1, 1), "Acosh": (1, 5), "Atanh": (-0.95, 0.95), "Log": (0.01, 10),
+                 "Sqrt": (0, 10), "Reciprocal": (0.1, 5), "Exp": (-10, 10), "Cosh": (-5, 5), "Tan": (-1.3, 1.3)}
+
+
+@pytest.mark.parametrize("op", ["Abs", "Acos", "Acosh", "Asin", "Asinh", "Atan", "Atanh", "Ceil", "Cos", "Cosh",
+                                "Exp", "Floor", "HardSwish", "Log", "Neg", "Reciprocal", "Relu", "Round",
+                                "Sigmoid", "Sign", "Sin", "Softplus", "Softsign", "Sqrt", "Tan", "Tanh", "Elu",
+                                "HardSigmoid", "LeakyRelu", "Selu", "ThresholdedRelu"])
+def test_unary_ops(cuda_context, op):
+    rng = np.random.default_rng(3)
+    lo, hi = UNARY_DOMAINS.get(op, (-6, 6))
+    x = rng.uniform(lo, hi, (7, 129)).astype(np.float32)  # odd length: vector body + scalar tail
+    x[0, :8] = [0.0, -0.0, 0.5, -0.5, 1.5, 2.5, -2.5, 3.0][:8] if op in ("Round", "Sign", "Relu", "HardSwish", "Ceil", "Floor") else x[0, :8]
+    model = single_op_model(op, {}, [x])
+    (want,) = ref_runner.run_model(model, [x])
+    (got,) = run_cuda(model, [x], cuda_context)
+    if op in EXACT_UNARY:
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert max_err_rel_linf(got, want) <= TOL
+
+
+def test_clip_opset6(cuda_context):
+    x = np.linspace(-3, 3, 50, dtype=np.float32)
+    model = single_op_model("Clip", {"min": -1.0, "max": 1.5, "_opset": 6}, [x])
+    (want,) = ref_runner.run_model(model, [x])
+    (got,) = run_cuda(model, [x], cuda_context)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("op", ["Add", "Sub", "Mul", "Div", "Pow"])
+def test_int32_binary_bit_exact(cuda_context, op):
+    rng = np.random.default_rng(5)
+    a = rng.integers(-2 ** 31, 2 ** 31, (4, 1, 33), dtype=np.int64).astype(np.int32)
+    b = rng.integers(-2 ** 31, 2 ** 31, (1, 5, 33), dtype=np.int64).astype(np.int32)
+    if op == "Pow":
+        a = rng.integers(-9, 10, (4, 1, 33)).astype(np.int32)
+        b = rng.integers(0, 9, (1, 5, 33)).astype(np.int32)
+    a[0, 0, :4] = [2147483647, -2147483648, 123456789, 5]
+    b[0, 0, :4] = [1, -1, 987654321, 0] if op != "Pow" else [1, 2, 3, 0]
+    model = single_op_model(op, {}, [a, b])
+    (want,) = ref_runner.run_model(model, [a, b])
+    (got,) = run_cuda(model, [a, b], cuda_context)
+    assert got.dtype == np.int32 and np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("op", ["Abs", "Neg", "Relu", "Sign"])
+def test_int32_unary_bit_exact(cuda_context, op):
+    x = np.asarray([-2147483648, 2147483647, 0, -5, 7], np.int32)
+    model = single_op_model(op, {}, [x])
+    (want,) = ref_runner.run_model(model, [x])
+    (got,) = run_cuda(model, [x], cuda_context)
+    assert np.array_equal(got, want)
+
+
+def test_broadcast_ranks_up_to_6(cuda_context):
+    rng = np.random.default_rng(6)
+    for sa, sb in [((2, 1, 3, 1, 4, 5), (1, 3, 1, 2, 1, 5)), ((3, 4, 5), (5,)), ((3, 4, 5), (4, 1)), ((), (2, 3)),
+                   ((6, 1), (1, 7)), ((0, 3), (1, 3))]:
+        a, b = rng.standard_normal(sa).astype(np.float32), rng.standard_normal(sb).astype(np.float32)
+        model = single_op_model("Sub", {}, [a, b])
+        (want,) = ref_runner.run_model(model, [a, b])
+        (got,) = run_cuda(model, [a, b], cuda_context)
+        assert got.shape == want.shape and np.array_equal(got, want)  # IEEE sub is exact either way
+
+
+def test_indexing_ops_bit_exact(cuda_context):
+    rng = np.random.default_rng(7)
+    x = rng.standard_normal((3, 4, 5, 6)).astype(np.float32)
+    cases = [
+        ("Transpose", {"perm": [2, 0, 3, 1]}, [x], 1),
+        ("Transpose", {}, [x[0]], 1),
+        ("Transpose", {"perm": [0, 2, 3, 1]}, [rng.standard_normal((2, 40, 9, 9)).astype(np.float32)], 1),
+        ("Concat", {"axis": 1}, [x, x[:, :2], x[:, 1:]], 1),
+        ("Concat", {"axis": -1}, [x, x], 1),
+        ("Split", {"axis": -1, "split": [2, 3, 1], "_opset": 11}, [x], 3),
+        ("Split", {"axis": 0}, [rng.standard_normal((30, 4)).astype(np.float32)], 3),
+        ("Flatten", {"axis": 1}, [x], 1),
+        ("Squeeze", {"axes": [2, 4], "_opset": 11}, [rng.standard_normal((3, 4, 1, 5, 1, 6)).astype(np.float32)], 1),
+        ("Unsqueeze", {"axes": [0, 3], "_opset": 11}, [x], 1),
+        ("Cast", {"to": 6}, [(x * 100).astype(np.float32)], 1),
+        ("Identity", {}, [x], 1),
+    ]
+    for op, attrs, ins, n_out in cases:
+        model = single_op_model(op, attrs, ins, n_out=n_out)
+        want = ref_runner.run_model(model, ins)
+        got = run_cuda(model, ins, cuda_context)
+        for g, w in zip(got, want):
+            assert g.shape == w.shape and g.dtype == w.dtype, (op, g.shape, w.shape)
+            assert np.array_equal(g.view(np.uint32), w.view(np.uint32)), op
+
+
+def test_reshape_slice_gather_with_cpu_operands(cuda_context):
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((100, 200)).astype(np.float32)
+    for op, attrs, ins, n_graph in [
+        ("Reshape", {}, [x, np.asarray([0, 10, -1], np.int64)], 1),
+        ("Slice", {}, [x, np.asarray([10, 20], np.int64), np.asarray([50, -20], np.int64)], 1),
+        ("Slice", {}, [x, np.asarray([5], np.int64), np.asarray([90], np.int64), np.asarray([1], np.int64),
+                       np.asarray([3], np.int64)], 1),
+        ("Gather", {"axis": 1}, [x, np.asarray([3, -1, 7, 7], np.int32)], 2),
+    ]:
+        model = single_op_model(op, attrs, ins, n_graph_inputs=n_graph)
+        want = ref_runner.run_model(model, ins[:n_graph])
+        got = run_cuda(model, ins[:n_graph], cuda_context)
+        assert got[0].shape == want[0].shape and np.array_equal(got[0], want[0]), op
+
+
+def test_softmax_edge_rows(cuda_context):
+    x = np.zeros((5, 10), np.float32)
+    x[1] = 1e4
+    x[2, 3] = -np.inf
+    x[3] = np.linspace(-80, 80, 10)
+    x[4] = -1e30
+    for arr in (x, np.zeros((0, 7), np.float32), np.random.default_rng(0).standard_normal((3, 1, 1)).astype(np.float32)):
+        model = single_op_model("Softmax", {"axis": -1}, [arr])
+        (want,) = ref_runner.run_model(model, [arr])
+        (got,) = run_cuda(model, [arr], cuda_context)
+        assert got.shape == want.shape
+        if arr.size:
+            assert max_err_rel_linf(got, want) <= TOL
+
+
+def test_gemm_larger_and_odd_shapes(cuda_context):
+    rng = np.random.default_rng(9)
+    for m, n, k, ta, tb in [(64, 512, 784, 0, 1), (64, 10, 512, 0, 1), (129, 67, 33, 1, 0), (1, 1, 1, 0, 0),
+                            (256, 1000, 2048, 0, 1)]:
+        a = rng.standard_normal((k, m) if ta else (m, k)).astype(np.float32)
+        b = (rng.standard_normal((n, k) if tb else (k, n)) * np.sqrt(2.0 / k)).astype(np.float32)
+        c = rng.uniform(-0.1, 0.1, n).astype(np.float32)
+        model = single_op_model("Gemm", {"transA": ta, "transB": tb}, [a, b, c])
+        (want,) = ref_runner.run_model(model, [a, b, c])
+        (got,) = run_cuda(model, [a, b, c], cuda_context)
+        assert max_err_rel_linf(got, want) <= TOL, (m, n, k)

@@ -1,0 +1,358 @@
+"""Tensors and backend contexts of the Python host mirror.
+
+Mirrors the reference's L1 layer:
+
+* ``TensorImpl`` (``core/tensorImpl.ts:4-36``): dims, ndim, length, row-major strides.
+* ``CPUTensor`` (``backend/cpu/cpuTensorImpl.ts:14-89``): a typed array plus dims; the I/O type of
+  ``runner.run()``.
+* ``CudaTensor``: modelled on ``WebGPUTensorImpl`` (``backend/webgpu/webgpuTensorImpl.ts:6-75``) with
+  the refcounted shared buffer and ``alias()`` of ``WasmTensorImpl``
+  (``backend/wasm/wasmTensorImpl.ts:16-52,77-85``).  Supports float32 and int32.  Carries a
+  ``layout`` tag the way ``WebGLTensor`` carries its texture shape: a 4-D tensor may be stored
+  channels-last ("nhwc") because the convolution kernels want the reduction axis contiguous;
+  ``dims`` always stay the logical NCHW dims.
+* ``WebDNNCudaContext``: ``BackendContext`` (``interface/core/backendContext.ts:4-8``) with
+  ``emptyTensor`` / ``moveTensor`` plus typed kernel launchers.
+
+Nothing here computes on the CPU: every method either moves bytes or enqueues a kernel of
+libwebdnn_cuda.so on the context's stream.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import byref, c_void_p
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+
+from .lib import (DTYPE_CODE, ConvDesc, CudaBackendError, GemmDesc, Library, PoolDesc, i64_array)
+
+NP_DTYPE = {"float32": np.float32, "int32": np.int32, "bool": np.uint8}
+
+
+def calc_strides(dims: Sequence[int]) -> List[int]:
+    strides: List[int] = []
+    length = 1
+    for d in reversed(dims):
+        strides.insert(0, length)
+        length *= d
+    return strides
+
+
+class TensorImpl:
+    backend = "cpu"
+
+    def __init__(self, dims: Sequence[int], data_type: str, backend: str):
+        self.dims = [int(d) for d in dims]
+        self.ndim = len(self.dims)
+        self.data_type = data_type
+        self.backend = backend
+        self.strides = calc_strides(self.dims)
+        length = 1
+        for d in self.dims:
+            length *= d
+        self.length = length
+
+
+class CPUTensor(TensorImpl):
+    """Host tensor: a flat numpy array of ``length`` elements plus dims."""
+
+    def __init__(self, dims: Sequence[int], data_type: str = "float32", data: Optional[np.ndarray] = None):
+        super().__init__(dims, data_type, "cpu")
+        if data is None:
+            self.data = np.zeros(self.length, dtype=NP_DTYPE[data_type])
+            self.use_external_buffer = False
+        else:
+            arr = np.asarray(data)
+            if arr.dtype != NP_DTYPE[data_type]:
+                raise TypeError(f"CPUTensor: data dtype {arr.dtype} does not match {data_type}")
+            self.data = arr.reshape(-1)
+            if self.data.size != self.length:
+                raise ValueError("CPUTensor: data length does not match dims")
+            self.use_external_buffer = True
+
+    @classmethod
+    def from_array(cls, arr: np.ndarray) -> "CPUTensor":
+        arr = np.ascontiguousarray(arr)
+        dt = {np.dtype(np.float32): "float32", np.dtype(np.int32): "int32", np.dtype(np.uint8): "bool"}[arr.dtype]
+        return cls(arr.shape, dt, arr.reshape(-1))
+
+    def get_data(self) -> np.ndarray:
+        return self.data
+
+    def set_data(self, data: np.ndarray) -> None:
+        self.data[:] = np.asarray(data).reshape(-1)
+
+    def get_value(self, idxs: Sequence[int]):
+        return self.data[sum(i * s for i, s in zip(idxs, self.strides))]
+
+    def set_value(self, value, idxs: Sequence[int]) -> None:
+        self.data[sum(i * s for i, s in zip(idxs, self.strides))] = value
+
+    def numpy(self) -> np.ndarray:
+        return self.data.reshape(self.dims)
+
+    def dispose(self) -> None:
+        pass
+
+
+class CudaSharedBuffer:
+    """Refcounted device allocation shared by aliases of one tensor."""
+
+    def __init__(self, context: "WebDNNCudaContext", byte_length: int):
+        self.context = context
+        self.byte_length = byte_length
+        self.ptr = context._alloc(byte_length)
+        self.ref_count = 1
+
+    def incr_ref(self) -> None:
+        self.ref_count += 1
+
+    def dispose(self) -> None:
+        self.ref_count -= 1
+        if self.ref_count == 0 and self.ptr is not None:
+            self.context._free(self.ptr)
+            self.ptr = None
+
+
+class CudaTensor(TensorImpl):
+    def __init__(self, context: "WebDNNCudaContext", dims: Sequence[int], data_type: str = "float32",
+                 shared_buffer: Optional[CudaSharedBuffer] = None, layout: str = "nchw"):
+        super().__init__(dims, data_type, "cuda")
+        if data_type not in ("float32", "int32"):
+            raise TypeError(f"CudaTensor: dataType {data_type} is not supported")
+        self.context = context
+        self.byte_length = max(self.length * 4, 4)
+        self.shared_buffer = shared_buffer or CudaSharedBuffer(context, self.byte_length)
+        if layout == "nhwc" and self.ndim != 4:
+            raise ValueError("channels-last layout needs a 4-D tensor")
+        self.layout = layout
+        self.aux: Dict[str, "CudaTensor"] = {}  # derived device data that lives and dies with this tensor
+        self.disposed = False
+
+    @property
+    def ptr(self) -> int:
+        if self.disposed or self.shared_buffer.ptr is None:
+            raise CudaBackendError(1, "CudaTensor used after dispose")
+        return self.shared_buffer.ptr
+
+    def alias(self, dims: Sequence[int]) -> "CudaTensor":
+        """New dims over the same device memory (Reshape/Flatten/Squeeze/Unsqueeze)."""
+        self.shared_buffer.incr_ref()
+        return CudaTensor(self.context, dims, self.data_type, self.shared_buffer)
+
+    def get_data(self) -> np.ndarray:
+        """D2H of the canonical (NCHW row-major) contents; waits for the stream."""
+        src = self.context.canonical(self)
+        out = np.empty(self.length, dtype=NP_DTYPE[self.data_type])
+        if self.length:
+            self.context._download(out, src.ptr, self.length * 4)
+        if src is not self:
+            src.dispose()
+        return out
+
+    def set_data(self, data: np.ndarray) -> None:
+        arr = np.ascontiguousarray(np.asarray(data).reshape(-1), dtype=NP_DTYPE[self.data_type])
+        if arr.size != self.length:
+            raise ValueError("CudaTensor.set_data: length mismatch")
+        if self.layout != "nchw":
+            raise ValueError("set_data writes canonical tensors only")
+        if self.length:
+            self.context._upload(self.ptr, arr)
+
+    def dispose(self) -> None:
+        if self.disposed:
+            return
+        for t in self.aux.values():
+            t.dispose()
+        self.aux.clear()
+        self.shared_buffer.dispose()
+        self.disposed = True
+
+    # physical element strides of the logical (n, c, h, w) axes
+    def nchw_strides(self) -> List[int]:
+        n, c, h, w = self.dims
+        if self.layout == "nhwc":
+            return [h * w * c, 1, w * c, c]
+        return [c * h * w, h * w, w, 1]
+
+
+class WebDNNCPUContext:
+    backend = "cpu"
+
+    def empty_tensor(self, dims: Sequence[int], data_type: str = "float32", data=None) -> CPUTensor:
+        return CPUTensor(dims, data_type, data)
+
+    def move_tensor(self, tensor, option=None) -> CPUTensor:
+        # backend/cpu/cpuContextImpl.ts:42-49
+        return CPUTensor(tensor.dims, tensor.data_type, tensor.get_data())
+
+    @staticmethod
+    def is_cpu_tensor(t) -> bool:
+        return isinstance(t, CPUTensor)
+
+    def asserts_cpu_tensor_array(self, tensors) -> None:
+        for t in tensors:
+            if not isinstance(t, CPUTensor):
+                raise TypeError("tensor is not CPUTensor")
+
+
+class WebDNNCudaContext:
+    """Owns one device context (stream + arena) of libwebdnn_cuda.so."""
+
+    backend = "cuda"
+
+    def __init__(self, cpu_context: Optional[WebDNNCPUContext] = None, device: int = 0,
+                 arena_bytes: int = 0):
+        self.cpu_context = cpu_context or WebDNNCPUContext()
+        self.device = device
+        self.arena_bytes = arena_bytes
+        self._L = None
+        self.handle = None
+
+    # --- lifecycle
+    def initialize(self) -> None:
+        self._L = Library()
+        if self._L.device_count() <= self.device:
+            raise CudaBackendError(2, f"no CUDA device {self.device} available")
+        h = c_void_p()
+        st = self._L.lib.wdc_create(self.device, self.arena_bytes, byref(h))
+        self._L.check(None, st)
+        self.handle = h
+
+    def close(self) -> None:
+        if self.handle is not None:
+            self._L.lib.wdc_destroy(self.handle)
+            self.handle = None
+
+    def _call(self, name: str, *args) -> None:
+        st = getattr(self._L.lib, name)(self.handle, *args)
+        if st != 0:
+            self._L.check(self.handle, st)
+
+    # --- raw memory
+    def _alloc(self, nbytes: int) -> int:
+        p = c_void_p()
+        self._call("wdc_alloc", nbytes, byref(p))
+        return p.value
+
+    def _free(self, ptr: int) -> None:
+        if self.handle is not None:
+            self._call("wdc_free", c_void_p(ptr))
+
+    def _upload(self, ptr: int, arr: np.ndarray) -> None:
+        # cudaMemcpyAsync from pageable memory returns once the source has been staged, so the
+        # caller may release `arr` right away; pinned sources must outlive the copy
+        self._call("wdc_upload", c_void_p(ptr), arr.ctypes.data_as(c_void_p), arr.nbytes)
+
+    def _download(self, out: np.ndarray, ptr: int, nbytes: int) -> None:
+        self._call("wdc_download", out.ctypes.data_as(c_void_p), c_void_p(ptr), nbytes)
+
+    def sync(self) -> None:
+        self._call("wdc_sync")
+
+    def stream_handle(self) -> int:
+        return self._L.lib.wdc_stream(self.handle)
+
+    def stats(self) -> Dict[str, int]:
+        out = (ctypes.c_int64 * 8)()
+        self._call("wdc_stats", out, 8)
+        keys = ["bytes_in_use", "high_water_bytes", "reserved_bytes", "allocs", "frees", "launches",
+                "h2d_bytes", "d2h_bytes"]
+        return dict(zip(keys, list(out)))
+
+    def reset_stats(self) -> None:
+        self._call("wdc_reset_stats")
+
+    def profile_enable(self, on: bool) -> None:
+        self._call("wdc_profile_enable", int(on))
+
+    def profile_read(self):
+        """(milliseconds, launches, algorithmic FLOPs) of the contraction kernels since the last read."""
+        ms, n, fl = ctypes.c_double(), ctypes.c_int64(), ctypes.c_double()
+        self._call("wdc_profile_read", 0, byref(ms), byref(n), byref(fl))
+        return ms.value, n.value, fl.value
+
+    def pinned_array(self, shape, dtype=np.float32) -> np.ndarray:
+        """numpy view of page-locked host memory (kept alive by the context)."""
+        n = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        p = c_void_p()
+        self._call("wdc_host_alloc", n, byref(p))
+        buf = (ctypes.c_char * max(n, 1)).from_address(p.value)
+
+        class _Pinned(np.ndarray):
+            _wdc_pinned = True
+
+        arr = np.frombuffer(buf, dtype=dtype, count=int(np.prod(shape))).reshape(shape).view(_Pinned)
+        return arr
+
+    # --- BackendContext
+    def is_cuda_tensor(self, t) -> bool:
+        return isinstance(t, CudaTensor)
+
+    def asserts_cuda_tensor(self, t) -> None:
+        if not isinstance(t, CudaTensor):
+            raise TypeError("tensor is not CudaTensor")
+
+    def asserts_cuda_tensor_array(self, tensors) -> None:
+        for t in tensors:
+            self.asserts_cuda_tensor(t)
+
+    def empty_tensor(self, dims: Sequence[int], data_type: str = "float32", layout: str = "nchw") -> CudaTensor:
+        return CudaTensor(self, dims, data_type, layout=layout)
+
+    def move_tensor(self, tensor, option=None) -> CudaTensor:
+        dst = CudaTensor(self, tensor.dims, tensor.data_type)
+        dst.set_data(tensor.get_data())
+        return dst
+
+    # --- layout helpers
+    def canonical(self, t: CudaTensor) -> CudaTensor:
+        """Return ``t`` itself if it is stored row-major, else a converted copy."""
+        if t.layout == "nchw":
+            return t
+        n, c, h, w = t.dims
+        if c == 1 or h * w == 1:
+            t.shared_buffer.incr_ref()
+            return CudaTensor(self, t.dims, t.data_type, t.shared_buffer)
+        out = CudaTensor(self, t.dims, t.data_type)
+        self.strided_copy(t, out, t.dims, t.nchw_strides(), 0, out.strides, 0)
+        return out
+
+    def channels_last(self, t: CudaTensor) -> CudaTensor:
+        if t.layout == "nhwc":
+            return t
+        n, c, h, w = t.dims
+        if c == 1 or h * w == 1:
+            t.shared_buffer.incr_ref()
+            return CudaTensor(self, t.dims, t.data_type, t.shared_buffer, layout="nhwc")
+        out = CudaTensor(self, t.dims, t.data_type, layout="nhwc")
+        # iterate destination in (n, h, w, c) order
+        self.strided_copy(t, out, [n, h, w, c], [c * h * w, w, 1, h * w], 0, [h * w * c, w * c, c, 1], 0)
+        return out
+
+    # --- kernel launchers (one per C entry point)
+    def strided_copy(self, src: CudaTensor, dst: CudaTensor, dims, sstr, soff, dstr, doff) -> None:
+        self._call("wdc_strided_copy", c_void_p(src.ptr), c_void_p(dst.ptr), len(dims), i64_array(dims),
+                   i64_array(sstr), soff, i64_array(dstr), doff)
+
+    def unary(self, op: int, src: CudaTensor, dst: CudaTensor, p0: float = 0.0, p1: float = 0.0) -> None:
+        self._call("wdc_unary", op, DTYPE_CODE[src.data_type], c_void_p(src.ptr), c_void_p(dst.ptr),
+                   src.length, p0, p1)
+
+    def binary(self, op: int, a: CudaTensor, b: CudaTensor, out: CudaTensor, dims, sa, sb) -> None:
+        self._call("wdc_binary", op, DTYPE_CODE[a.data_type], c_void_p(a.ptr), c_void_p(b.ptr),
+                   c_void_p(out.ptr), len(dims), i64_array(dims), i64_array(sa), i64_array(sb))
+
+    def gemm(self, desc: GemmDesc, a: CudaTensor, b: CudaTensor, c: Optional[CudaTensor], y: CudaTensor) -> None:
+        self._call("wdc_gemm", byref(desc), c_void_p(a.ptr), c_void_p(b.ptr),
+                   c_void_p(c.ptr) if c is not None else None, c_void_p(y.ptr))
+
+    def conv2d(self, desc: ConvDesc, x, w, scale, shift, residual, y) -> None:
+        def p(t):
+            return c_void_p(t.ptr) if t is not None else None
+        self._call("wdc_conv2d", byref(desc), p(x), p(w), p(scale), p(shift), p(residual), p(y))
+
+    def pool(self, kind: str, desc: PoolDesc, x: CudaTensor, y: CudaTensor) -> None:
+        self._call("wdc_maxpool2d" if kind == "max" else "wdc_avgpool2d", byref(desc), c_void_p(x.ptr),
+                   c_void_p(y.ptr))

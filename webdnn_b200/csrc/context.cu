@@ -1,0 +1,359 @@
+// Context, stream-ordered arena, host<->device transfers and error reporting.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+static std::string g_last_error;  // for failures before a context exists
+static std::mutex g_mu;
+
+int wdc_fail(wdc_context* ctx, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  if (ctx) {
+    ctx->last_error = buf;
+  } else {
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_last_error = buf;
+  }
+  return code;
+}
+
+int wdc_check_cuda(wdc_context* ctx, cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return WDC_OK;
+  int code = (e == cudaErrorMemoryAllocation) ? WDC_ERR_OOM : WDC_ERR_CUDA;
+  return wdc_fail(ctx, code, "%s: %s (%s)", what, cudaGetErrorName(e), cudaGetErrorString(e));
+}
+
+int wdc_check_launch(wdc_context* ctx, const char* kernel) {
+  ctx->n_launch++;
+  return wdc_check_cuda(ctx, cudaGetLastError(), kernel);
+}
+
+extern "C" const char* wdc_last_error(wdc_context* ctx) {
+  if (ctx) return ctx->last_error.c_str();
+  return g_last_error.c_str();
+}
+
+extern "C" int wdc_device_count(int* count) {
+  if (!count) return wdc_fail(nullptr, WDC_ERR_INVALID, "wdc_device_count: null output");
+  cudaError_t e = cudaGetDeviceCount(count);
+  if (e != cudaSuccess) {
+    *count = 0;
+    return wdc_check_cuda(nullptr, e, "cudaGetDeviceCount");
+  }
+  return WDC_OK;
+}
+
+extern "C" int wdc_create(int device, int64_t arena_limit_bytes, wdc_context** out) {
+  if (!out) return wdc_fail(nullptr, WDC_ERR_INVALID, "wdc_create: null output");
+  *out = nullptr;
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) return wdc_check_cuda(nullptr, e, "cudaGetDeviceCount");
+  if (device < 0 || device >= n)
+    return wdc_fail(nullptr, WDC_ERR_INVALID, "wdc_create: device %d out of range (have %d)", device, n);
+  e = cudaSetDevice(device);
+  if (e != cudaSuccess) return wdc_check_cuda(nullptr, e, "cudaSetDevice");
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, device);
+  if (e != cudaSuccess) return wdc_check_cuda(nullptr, e, "cudaGetDeviceProperties");
+  if (prop.major != 10)
+    return wdc_fail(nullptr, WDC_ERR_UNSUPPORTED,
+                    "wdc_create: device %d is sm_%d%d; this library carries sm_100a code only",
+                    device, prop.major, prop.minor);
+  wdc_context* ctx = new wdc_context();
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  ctx->arena.limit = arena_limit_bytes;
+  e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&ctx->status_word, 256);
+  if (e == cudaSuccess) e = cudaMemset(ctx->status_word, 0, 256);
+  if (e == cudaSuccess) e = cudaMallocHost((void**)&ctx->status_word_host, 256);
+  if (e != cudaSuccess) {
+    int s = wdc_check_cuda(nullptr, e, "wdc_create");
+    delete ctx;
+    return s;
+  }
+  memset(ctx->status_word_host, 0, 256);
+  *out = ctx;
+  return WDC_OK;
+}
+
+extern "C" int wdc_destroy(wdc_context* ctx) {
+  if (!ctx) return WDC_OK;
+  DeviceGuard g(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  wdc_tc_destroy(ctx);
+  for (auto& s : ctx->arena.slabs) cudaFree(s.base);
+  cudaFree(ctx->status_word);
+  cudaFreeHost(ctx->status_word_host);
+  cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return WDC_OK;
+}
+
+static const int64_t kAlign = 512;
+static const int64_t kSlabMin = 256ll << 20;
+
+static void arena_erase_free(wdc_arena& a, int slab, int64_t off, int64_t size) {
+  auto range = a.free_by_size.equal_range(size);
+  for (auto it = range.first; it != range.second; ++it) {
+    if (it->second.first == slab && it->second.second == off) {
+      a.free_by_size.erase(it);
+      return;
+    }
+  }
+}
+
+extern "C" int wdc_alloc(wdc_context* ctx, int64_t bytes, void** dptr) {
+  if (!ctx || !dptr) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_alloc: null argument");
+  *dptr = nullptr;
+  if (bytes < 0) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_alloc: negative size %lld", (long long)bytes);
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  wdc_arena& a = ctx->arena;
+  int64_t need = ((bytes > 0 ? bytes : 1) + kAlign - 1) / kAlign * kAlign;
+  if (a.limit > 0 && a.in_use + need > a.limit)
+    return wdc_fail(ctx, WDC_ERR_OOM, "wdc_alloc: %lld bytes would exceed the arena budget of %lld (in use %lld)",
+                    (long long)need, (long long)a.limit, (long long)a.in_use);
+  auto it = a.free_by_size.lower_bound(need);
+  if (it == a.free_by_size.end()) {
+    DeviceGuard g(ctx->device);
+    int64_t slab_size = need > kSlabMin ? need : kSlabMin;
+    char* base = nullptr;
+    cudaError_t e = cudaMalloc((void**)&base, (size_t)slab_size);
+    if (e != cudaSuccess && slab_size > need) {
+      cudaGetLastError();
+      slab_size = need;
+      e = cudaMalloc((void**)&base, (size_t)slab_size);
+    }
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return wdc_fail(ctx, WDC_ERR_OOM, "wdc_alloc: cudaMalloc of %lld bytes failed: %s",
+                      (long long)slab_size, cudaGetErrorString(e));
+    }
+    wdc_arena::Slab s;
+    s.base = base;
+    s.size = slab_size;
+    s.blocks[0] = {slab_size, true};
+    a.slabs.push_back(std::move(s));
+    a.reserved += slab_size;
+    it = a.free_by_size.insert({slab_size, {(int)a.slabs.size() - 1, 0}});
+  }
+  int slab = it->second.first;
+  int64_t off = it->second.second, size = it->first;
+  a.free_by_size.erase(it);
+  auto& blocks = a.slabs[slab].blocks;
+  if (size - need >= kAlign) {
+    blocks[off] = {need, false};
+    blocks[off + need] = {size - need, true};
+    a.free_by_size.insert({size - need, {slab, off + need}});
+  } else {
+    need = size;
+    blocks[off] = {size, false};
+  }
+  void* p = a.slabs[slab].base + off;
+  a.live[p] = {slab, off};
+  a.in_use += need;
+  if (a.in_use > a.high_water) a.high_water = a.in_use;
+  ctx->n_alloc++;
+  *dptr = p;
+  return WDC_OK;
+}
+
+extern "C" int wdc_free(wdc_context* ctx, void* dptr) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_free: null context");
+  if (!dptr) return WDC_OK;
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  wdc_arena& a = ctx->arena;
+  auto lit = a.live.find(dptr);
+  if (lit == a.live.end())
+    return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_free: %p is not a live allocation of this context", dptr);
+  int slab = lit->second.first;
+  int64_t off = lit->second.second;
+  a.live.erase(lit);
+  auto& blocks = a.slabs[slab].blocks;
+  auto it = blocks.find(off);
+  int64_t size = it->second.size;
+  a.in_use -= size;
+  ctx->n_free++;
+  // coalesce with the next block
+  auto nx = std::next(it);
+  if (nx != blocks.end() && nx->second.free) {
+    arena_erase_free(a, slab, nx->first, nx->second.size);
+    size += nx->second.size;
+    blocks.erase(nx);
+  }
+  // coalesce with the previous block
+  if (it != blocks.begin()) {
+    auto pv = std::prev(it);
+    if (pv->second.free) {
+      arena_erase_free(a, slab, pv->first, pv->second.size);
+      size += pv->second.size;
+      off = pv->first;
+      blocks.erase(it);
+      it = pv;
+    }
+  }
+  it->second = {size, true};
+  a.free_by_size.insert({size, {slab, off}});
+  return WDC_OK;
+}
+
+extern "C" int wdc_host_alloc(wdc_context* ctx, int64_t bytes, void** hptr) {
+  if (!ctx || !hptr || bytes < 0) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_host_alloc: bad argument");
+  DeviceGuard g(ctx->device);
+  WDC_CUDA(ctx, cudaMallocHost(hptr, (size_t)(bytes > 0 ? bytes : 1)));
+  return WDC_OK;
+}
+
+extern "C" int wdc_host_free(wdc_context* ctx, void* hptr) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_host_free: null context");
+  if (!hptr) return WDC_OK;
+  DeviceGuard g(ctx->device);
+  WDC_CUDA(ctx, cudaFreeHost(hptr));
+  return WDC_OK;
+}
+
+extern "C" int wdc_upload(wdc_context* ctx, void* dst, const void* host, int64_t bytes) {
+  if (!ctx || bytes < 0 || (bytes > 0 && (!dst || !host)))
+    return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_upload: bad argument");
+  if (bytes == 0) return WDC_OK;
+  DeviceGuard g(ctx->device);
+  WDC_CUDA(ctx, cudaMemcpyAsync(dst, host, (size_t)bytes, cudaMemcpyHostToDevice, ctx->stream));
+  ctx->h2d_bytes += bytes;
+  return WDC_OK;
+}
+
+static int report_device_status(wdc_context* ctx) {
+  // status_word_host is refreshed by the download/sync paths below
+  if (ctx->status_word_host[0] != 0) {
+    int code = ctx->status_word_host[0];
+    ctx->status_word_host[0] = 0;
+    cudaMemsetAsync(ctx->status_word, 0, 256, ctx->stream);
+    return wdc_fail(ctx, WDC_ERR_DEVICE_WAIT, "a bounded device-side wait expired (kernel status %d)", code);
+  }
+  return WDC_OK;
+}
+
+extern "C" int wdc_sync(wdc_context* ctx) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_sync: null context");
+  DeviceGuard g(ctx->device);
+  WDC_CUDA(ctx, cudaMemcpyAsync(ctx->status_word_host, ctx->status_word, sizeof(int),
+                                cudaMemcpyDeviceToHost, ctx->stream));
+  WDC_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  return report_device_status(ctx);
+}
+
+extern "C" int wdc_download(wdc_context* ctx, void* host, const void* src, int64_t bytes) {
+  if (!ctx || bytes < 0 || (bytes > 0 && (!host || !src)))
+    return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_download: bad argument");
+  DeviceGuard g(ctx->device);
+  if (bytes > 0) {
+    WDC_CUDA(ctx, cudaMemcpyAsync(host, src, (size_t)bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    ctx->d2h_bytes += bytes;
+  }
+  return wdc_sync(ctx);
+}
+
+extern "C" int wdc_copy(wdc_context* ctx, void* dst, const void* src, int64_t bytes) {
+  if (!ctx || bytes < 0 || (bytes > 0 && (!dst || !src)))
+    return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_copy: bad argument");
+  if (bytes == 0) return WDC_OK;
+  DeviceGuard g(ctx->device);
+  WDC_CUDA(ctx, cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  return WDC_OK;
+}
+
+__global__ void fill_u32_kernel(uint32_t* dst, uint32_t v, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) dst[i] = v;
+}
+
+extern "C" int wdc_fill_u32(wdc_context* ctx, void* dst, uint32_t value, int64_t count) {
+  if (!ctx || count < 0 || (count > 0 && !dst))
+    return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_fill_u32: bad argument");
+  if (count == 0) return WDC_OK;
+  DeviceGuard g(ctx->device);
+  fill_u32_kernel<<<grid_for(ctx, count, 256), 256, 0, ctx->stream>>>((uint32_t*)dst, value, count);
+  return wdc_check_launch(ctx, "fill_u32_kernel");
+}
+
+extern "C" void* wdc_stream(wdc_context* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+extern "C" int wdc_stats(wdc_context* ctx, int64_t* out, int n) {
+  if (!ctx || !out || n < 0) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_stats: bad argument");
+  int64_t v[8] = {ctx->arena.in_use, ctx->arena.high_water, ctx->arena.reserved, ctx->n_alloc,
+                  ctx->n_free,       ctx->n_launch,         ctx->h2d_bytes,      ctx->d2h_bytes};
+  for (int i = 0; i < n && i < 8; i++) out[i] = v[i];
+  return WDC_OK;
+}
+
+extern "C" int wdc_reset_stats(wdc_context* ctx) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_reset_stats: null context");
+  ctx->n_alloc = ctx->n_free = ctx->n_launch = ctx->h2d_bytes = ctx->d2h_bytes = 0;
+  ctx->arena.high_water = ctx->arena.in_use;
+  return WDC_OK;
+}
+
+extern "C" int wdc_profile_enable(wdc_context* ctx, int on) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_profile_enable: null context");
+  ctx->profile = on != 0;
+  return WDC_OK;
+}
+
+extern "C" int wdc_profile_read(wdc_context* ctx, int family, double* ms, int64_t* launches, double* flops) {
+  if (!ctx || !ms || !launches || !flops || family != 0)
+    return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_profile_read: bad argument");
+  DeviceGuard g(ctx->device);
+  WDC_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  double total = 0, fl = 0;
+  for (auto& r : ctx->prof) {
+    float t = 0;
+    cudaEventElapsedTime(&t, r.start, r.stop);
+    total += t;
+    fl += r.flops;
+    cudaEventDestroy(r.start);
+    cudaEventDestroy(r.stop);
+  }
+  *ms = total;
+  *launches = (int64_t)ctx->prof.size();
+  *flops = fl;
+  ctx->prof.clear();
+  return WDC_OK;
+}
+
+extern "C" int wdc_peer_copy(wdc_context* dst_ctx, void* dst, wdc_context* src_ctx, const void* src,
+                             int64_t bytes) {
+  if (!dst_ctx || !src_ctx || bytes < 0 || (bytes > 0 && (!dst || !src)))
+    return wdc_fail(dst_ctx, WDC_ERR_INVALID, "wdc_peer_copy: bad argument");
+  if (bytes == 0) return WDC_OK;
+  // Order the copy after everything already enqueued on the source stream, run it on the
+  // destination stream.
+  cudaEvent_t ev;
+  {
+    DeviceGuard g(src_ctx->device);
+    WDC_CUDA(src_ctx, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    WDC_CUDA(src_ctx, cudaEventRecord(ev, src_ctx->stream));
+  }
+  DeviceGuard g(dst_ctx->device);
+  WDC_CUDA(dst_ctx, cudaStreamWaitEvent(dst_ctx->stream, ev, 0));
+  WDC_CUDA(dst_ctx, cudaMemcpyPeerAsync(dst, dst_ctx->device, src, src_ctx->device, (size_t)bytes,
+                                        dst_ctx->stream));
+  // the source must not reuse the buffer before the copy has read it
+  cudaEvent_t done;
+  WDC_CUDA(dst_ctx, cudaEventCreateWithFlags(&done, cudaEventDisableTiming));
+  WDC_CUDA(dst_ctx, cudaEventRecord(done, dst_ctx->stream));
+  {
+    DeviceGuard g2(src_ctx->device);
+    WDC_CUDA(src_ctx, cudaStreamWaitEvent(src_ctx->stream, done, 0));
+  }
+  cudaEventDestroy(ev);
+  cudaEventDestroy(done);
+  return WDC_OK;
+}

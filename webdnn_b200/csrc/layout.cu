@@ -1,0 +1,145 @@
+// Data-movement kernels on 4-byte elements: general strided copy (<= 6-D) with a tiled
+// shared-memory path for batched 2-D transposes (the NCHW <-> NHWC conversions), and gather.
+#include "common.cuh"
+
+struct CopyShape {
+  int64_t dims[6];
+  int64_t sstr[6];
+  int64_t dstr[6];
+};
+
+__global__ void __launch_bounds__(256) strided_copy_kernel(const uint32_t* __restrict__ src,
+                                                           uint32_t* __restrict__ dst, int64_t n,
+                                                           CopyShape sh) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) {
+    int64_t rem = i, is = 0, id = 0;
+#pragma unroll
+    for (int d = 5; d >= 0; d--) {
+      int64_t c = rem % sh.dims[d];
+      rem /= sh.dims[d];
+      is += c * sh.sstr[d];
+      id += c * sh.dstr[d];
+    }
+    dst[id] = src[is];
+  }
+}
+
+// dst[b][r][c] (dense, c innermost) <- src[b][c][r]: src element (b, r, c) at b*sb + c*rows + r.
+// 32x32 tiles through shared memory (padded against bank conflicts): both sides coalesced.
+__global__ void __launch_bounds__(256) transpose_tile_kernel(const uint32_t* __restrict__ src,
+                                                             uint32_t* __restrict__ dst, int64_t batch,
+                                                             int64_t rows, int64_t cols) {
+  __shared__ uint32_t tile[32][33];
+  int64_t tiles_r = (rows + 31) / 32, tiles_c = (cols + 31) / 32;
+  int64_t ntiles = batch * tiles_r * tiles_c;
+  int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (int64_t t = blockIdx.x; t < ntiles; t += gridDim.x) {
+    int64_t b = t / (tiles_r * tiles_c);
+    int64_t rem = t % (tiles_r * tiles_c);
+    int64_t r0 = (rem / tiles_c) * 32, c0 = (rem % tiles_c) * 32;
+    const uint32_t* s = src + b * rows * cols;
+    uint32_t* d = dst + b * rows * cols;
+    // read: src is [cols][rows] with rows innermost
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      int64_t c = c0 + ty + k * 8, r = r0 + tx;
+      if (c < cols && r < rows) tile[ty + k * 8][tx] = s[c * rows + r];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      int64_t r = r0 + ty + k * 8, c = c0 + tx;
+      if (r < rows && c < cols) d[r * cols + c] = tile[tx][ty + k * 8];
+    }
+    __syncthreads();
+  }
+}
+
+extern "C" int wdc_strided_copy(wdc_context* ctx, const void* src, void* dst, int ndim,
+                                const int64_t* dims, const int64_t* sstr, int64_t src_off,
+                                const int64_t* dstr, int64_t dst_off) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_strided_copy: null context");
+  WDC_REQUIRE(ctx, ndim >= 0 && ndim <= 6, "wdc_strided_copy: rank %d not in 0..6", ndim);
+  WDC_REQUIRE(ctx, ndim == 0 || (dims && sstr && dstr), "wdc_strided_copy: null shape");
+  WDC_REQUIRE(ctx, src_off >= 0 && dst_off >= 0, "wdc_strided_copy: negative offset");
+  // drop size-1 axes and merge axes that are contiguous on both sides
+  int64_t md[6], ms[6], mt[6];
+  int m = 0;
+  int64_t n = 1;
+  for (int i = 0; i < ndim; i++) {
+    WDC_REQUIRE(ctx, dims[i] >= 0, "wdc_strided_copy: negative dim");
+    n *= dims[i];
+    if (dims[i] == 1) continue;
+    if (m > 0 && ms[m - 1] == sstr[i] * dims[i] && mt[m - 1] == dstr[i] * dims[i]) {
+      md[m - 1] *= dims[i];
+      ms[m - 1] = sstr[i];
+      mt[m - 1] = dstr[i];
+    } else {
+      md[m] = dims[i];
+      ms[m] = sstr[i];
+      mt[m] = dstr[i];
+      m++;
+    }
+  }
+  if (n == 0) return WDC_OK;
+  WDC_REQUIRE(ctx, src && dst, "wdc_strided_copy: null buffer");
+  DeviceGuard g(ctx->device);
+  const uint32_t* s = (const uint32_t*)src + src_off;
+  uint32_t* d = (uint32_t*)dst + dst_off;
+  if (m == 0 || (m == 1 && ms[0] == 1 && mt[0] == 1)) return wdc_copy(ctx, d, s, n * 4);
+  // batched 2-D transpose: dst dense [b][r][c], src [b][c][r]
+  if ((m == 2 || m == 3) && mt[m - 1] == 1 && mt[m - 2] == md[m - 1] && ms[m - 2] == 1 &&
+      ms[m - 1] == md[m - 2] && md[m - 1] >= 8 && md[m - 2] >= 8 &&
+      (m == 2 || (mt[0] == md[1] * md[2] && ms[0] == md[1] * md[2]))) {
+    int64_t batch = m == 3 ? md[0] : 1, rows = md[m - 2], cols = md[m - 1];
+    int64_t ntiles = batch * ((rows + 31) / 32) * ((cols + 31) / 32);
+    int64_t cap = (int64_t)ctx->sm_count * 16;
+    int grid = (int)(ntiles < cap ? ntiles : cap);
+    transpose_tile_kernel<<<grid, 256, 0, ctx->stream>>>(s, d, batch, rows, cols);
+    return wdc_check_launch(ctx, "transpose_tile_kernel");
+  }
+  CopyShape sh;
+  for (int i = 0; i < 6; i++) {
+    sh.dims[i] = 1;
+    sh.sstr[i] = sh.dstr[i] = 0;
+  }
+  for (int i = 0; i < m; i++) {
+    sh.dims[6 - m + i] = md[i];
+    sh.sstr[6 - m + i] = ms[i];
+    sh.dstr[6 - m + i] = mt[i];
+  }
+  strided_copy_kernel<<<grid_for(ctx, n, 256, 8), 256, 0, ctx->stream>>>(s, d, n, sh);
+  return wdc_check_launch(ctx, "strided_copy_kernel");
+}
+
+__global__ void __launch_bounds__(256) gather_kernel(const uint32_t* __restrict__ data,
+                                                     const int32_t* __restrict__ idx,
+                                                     uint32_t* __restrict__ out, int64_t outer,
+                                                     int64_t axis_len, int64_t inner, int64_t n_idx) {
+  int64_t n = outer * n_idx * inner;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) {
+    int64_t in = i % inner, k = (i / inner) % n_idx, o = i / (inner * n_idx);
+    int64_t j = idx[k];
+    if (j < 0) j += axis_len;
+    // out-of-range indices are clamped instead of read out of bounds
+    j = j < 0 ? 0 : (j >= axis_len ? axis_len - 1 : j);
+    out[i] = data[(o * axis_len + j) * inner + in];
+  }
+}
+
+extern "C" int wdc_gather(wdc_context* ctx, const void* data, const int32_t* idx, void* out,
+                          int64_t outer, int64_t axis_len, int64_t inner, int64_t n_idx) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_gather: null context");
+  WDC_REQUIRE(ctx, outer >= 0 && axis_len > 0 && inner >= 0 && n_idx >= 0, "wdc_gather: bad shape");
+  int64_t n = outer * n_idx * inner;
+  if (n == 0) return WDC_OK;
+  WDC_REQUIRE(ctx, data && idx && out, "wdc_gather: null buffer");
+  DeviceGuard g(ctx->device);
+  gather_kernel<<<grid_for(ctx, n, 256, 8), 256, 0, ctx->stream>>>((const uint32_t*)data, idx,
+                                                                  (uint32_t*)out, outer, axis_len, inner, n_idx);
+  return wdc_check_launch(ctx, "gather_kernel");
+}

@@ -1,0 +1,457 @@
+// Streaming elementwise kernels: unary, broadcast binary, cast, per-channel affine.
+// All are HBM-bound: 128-bit accesses where alignment allows, grid-stride loops, grids sized from
+// the SM count.
+#include <math.h>
+
+#include "common.cuh"
+
+// JS ToInt32 of a double: what a store into an Int32Array does
+// (operators/cpu/operators/standard/binary7.ts writes doubles into typed arrays).
+__device__ __forceinline__ int32_t to_int32(double d) {
+  if (!isfinite(d)) return 0;
+  double t = trunc(d);
+  double m = fmod(t, 4294967296.0);
+  if (m < 0) m += 4294967296.0;
+  if (m >= 2147483648.0) m -= 4294967296.0;
+  return (int32_t)m;
+}
+
+template <int OP>
+__device__ __forceinline__ float unary_f32(float v, float p0, float p1) {
+  switch (OP) {
+    case WDC_U_ABS: return fabsf(v);
+    case WDC_U_ACOS: return acosf(v);
+    case WDC_U_ACOSH: return acoshf(v);
+    case WDC_U_ASIN: return asinf(v);
+    case WDC_U_ASINH: return asinhf(v);
+    case WDC_U_ATAN: return atanf(v);
+    case WDC_U_ATANH: return atanhf(v);
+    case WDC_U_CEIL: return ceilf(v);
+    case WDC_U_COS: return cosf(v);
+    case WDC_U_COSH: return coshf(v);
+    case WDC_U_EXP: return expf(v);
+    case WDC_U_FLOOR: return floorf(v);
+    case WDC_U_HARDSWISH:
+      if (v <= -3.f) return 0.f;
+      if (v >= 3.f) return v;
+      return (v * (v + 3.f)) / 6.f;
+    case WDC_U_LOG: return logf(v);
+    case WDC_U_NEG: return -v;
+    case WDC_U_RECIPROCAL: return 1.f / v;
+    case WDC_U_RELU:  // Math.max(v, 0): NaN propagates, -0 becomes +0
+      return v > 0.f ? v : (v == v ? 0.f : v);
+    case WDC_U_ROUND: {  // Math.round: ties toward +Infinity, keeps -0 for (-0.5, -0]
+      if (!(fabsf(v) < 8388608.f)) return v;
+      float r = floorf(v + 0.5f);
+      // v + 0.5f can round up for the largest float below 0.5
+      if (r - v > 0.5f) r -= 1.f;
+      if (r == 0.f && (v < 0.f || (v == 0.f && signbit(v)))) return -0.f;
+      return r;
+    }
+    case WDC_U_SIGMOID: return (tanhf(v * 0.5f) + 1.f) * 0.5f;
+    case WDC_U_SIGN: return v > 0.f ? 1.f : (v < 0.f ? -1.f : v);
+    case WDC_U_SIN: return sinf(v);
+    case WDC_U_SOFTPLUS: return logf(expf(v) + 1.f);
+    case WDC_U_SOFTSIGN: return v / (1.f + fabsf(v));
+    case WDC_U_SQRT: return sqrtf(v);
+    case WDC_U_TAN: return tanf(v);
+    case WDC_U_TANH: return tanhf(v);
+    case WDC_U_ELU: return v >= 0.f ? v : (expf(v) - 1.f) * p0;
+    case WDC_U_HARDSIGMOID: {
+      float t = v * p0 + p1;
+      if (t != t) return t;
+      float m = t < 1.f ? t : 1.f;
+      return m > 0.f ? m : 0.f;
+    }
+    case WDC_U_LEAKYRELU: return v >= 0.f ? v : v * p0;
+    case WDC_U_SELU: return v > 0.f ? p1 * v : p1 * (p0 * expf(v) - p0);
+    case WDC_U_THRESHOLDEDRELU: return v > p0 ? v : 0.f;
+    case WDC_U_CLIP: {
+      if (v != v) return v;
+      float t = v > p0 ? v : p0;
+      return t < p1 ? t : p1;
+    }
+    default: return v;
+  }
+}
+
+template <int OP>
+__global__ void __launch_bounds__(256) unary_f32_kernel(const float* __restrict__ src,
+                                                        float* __restrict__ dst, int64_t n,
+                                                        float p0, float p1, int vec_ok) {
+  int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  if (vec_ok) {
+    int64_t n4 = n >> 2;
+    const float4* s4 = reinterpret_cast<const float4*>(src);
+    float4* d4 = reinterpret_cast<float4*>(dst);
+    for (int64_t i = tid; i < n4; i += step) {
+      float4 v = __ldg(s4 + i);
+      v.x = unary_f32<OP>(v.x, p0, p1);
+      v.y = unary_f32<OP>(v.y, p0, p1);
+      v.z = unary_f32<OP>(v.z, p0, p1);
+      v.w = unary_f32<OP>(v.w, p0, p1);
+      d4[i] = v;
+    }
+    for (int64_t i = (n4 << 2) + tid; i < n; i += step) dst[i] = unary_f32<OP>(src[i], p0, p1);
+  } else {
+    for (int64_t i = tid; i < n; i += step) dst[i] = unary_f32<OP>(src[i], p0, p1);
+  }
+}
+
+__global__ void unary_i32_kernel(int op, const int32_t* __restrict__ src, int32_t* __restrict__ dst,
+                                 int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) {
+    int32_t v = src[i];
+    int32_t r;
+    switch (op) {
+      case WDC_U_ABS: r = v < 0 ? (int32_t)(0u - (uint32_t)v) : v; break;  // |INT_MIN| wraps
+      case WDC_U_NEG: r = (int32_t)(0u - (uint32_t)v); break;
+      case WDC_U_RELU: r = v > 0 ? v : 0; break;
+      case WDC_U_SIGN: r = (v > 0) - (v < 0); break;
+      default: r = v; break;
+    }
+    dst[i] = r;
+  }
+}
+
+template <int OP>
+static int launch_unary(wdc_context* ctx, const float* src, float* dst, int64_t n, float p0, float p1) {
+  int vec_ok = ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0) ? 1 : 0;
+  int64_t items = vec_ok ? (n + 3) / 4 : n;
+  unary_f32_kernel<OP><<<grid_for(ctx, items, 256), 256, 0, ctx->stream>>>(src, dst, n, p0, p1, vec_ok);
+  return wdc_check_launch(ctx, "unary_f32_kernel");
+}
+
+extern "C" int wdc_unary(wdc_context* ctx, int op, int dtype, const void* src, void* dst, int64_t n,
+                         float p0, float p1) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_unary: null context");
+  WDC_REQUIRE(ctx, n >= 0 && (n == 0 || (src && dst)), "wdc_unary: bad buffer or count");
+  if (n == 0) return WDC_OK;
+  DeviceGuard g(ctx->device);
+  if (dtype == 1) {
+    WDC_REQUIRE(ctx, op == WDC_U_ABS || op == WDC_U_NEG || op == WDC_U_RELU || op == WDC_U_SIGN ||
+                         op == WDC_U_IDENTITY,
+                "wdc_unary: op %d does not accept int32", op);
+    unary_i32_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(op, (const int32_t*)src,
+                                                                    (int32_t*)dst, n);
+    return wdc_check_launch(ctx, "unary_i32_kernel");
+  }
+  WDC_REQUIRE(ctx, dtype == 0, "wdc_unary: dtype %d not supported", dtype);
+  const float* s = (const float*)src;
+  float* d = (float*)dst;
+#define U(OPC) case OPC: return launch_unary<OPC>(ctx, s, d, n, p0, p1);
+  switch (op) {
+    U(WDC_U_ABS) U(WDC_U_ACOS) U(WDC_U_ACOSH) U(WDC_U_ASIN) U(WDC_U_ASINH) U(WDC_U_ATAN)
+    U(WDC_U_ATANH) U(WDC_U_CEIL) U(WDC_U_COS) U(WDC_U_COSH) U(WDC_U_EXP) U(WDC_U_FLOOR)
+    U(WDC_U_HARDSWISH) U(WDC_U_LOG) U(WDC_U_NEG) U(WDC_U_RECIPROCAL) U(WDC_U_RELU) U(WDC_U_ROUND)
+    U(WDC_U_SIGMOID) U(WDC_U_SIGN) U(WDC_U_SIN) U(WDC_U_SOFTPLUS) U(WDC_U_SOFTSIGN) U(WDC_U_SQRT)
+    U(WDC_U_TAN) U(WDC_U_TANH) U(WDC_U_ELU) U(WDC_U_HARDSIGMOID) U(WDC_U_LEAKYRELU) U(WDC_U_SELU)
+    U(WDC_U_THRESHOLDEDRELU) U(WDC_U_CLIP) U(WDC_U_IDENTITY)
+  }
+#undef U
+  return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_unary: unknown op %d", op);
+}
+
+// ------------------------------------------------------------------------------- binary
+__device__ __forceinline__ float js_powf(float a, float b) {
+  if (b != b) return NAN;
+  if ((a == 1.f || a == -1.f) && isinf(b)) return NAN;
+  return powf(a, b);
+}
+
+template <int OP>
+__device__ __forceinline__ float binary_f32(float l, float r) {
+  switch (OP) {
+    case WDC_B_ADD: return l + r;
+    case WDC_B_SUB: return l - r;
+    case WDC_B_MUL: return l * r;
+    case WDC_B_DIV: return l / r;  // IEEE division; equals the double quotient rounded to float
+    case WDC_B_POW: return js_powf(l, r);
+    case WDC_B_MAX: return (l != l || r != r) ? NAN : (l > r ? l : r);
+    default: return (l != l || r != r) ? NAN : (l < r ? l : r);
+  }
+}
+
+__device__ __forceinline__ int32_t binary_i32(int op, int32_t l, int32_t r) {
+  switch (op) {
+    case WDC_B_ADD: return (int32_t)((uint32_t)l + (uint32_t)r);
+    case WDC_B_SUB: return (int32_t)((uint32_t)l - (uint32_t)r);
+    case WDC_B_MUL: return to_int32((double)l * (double)r);  // double product, not a wrapping mul
+    case WDC_B_DIV: return to_int32((double)l / (double)r);
+    case WDC_B_POW: {
+      double a = l, b = r;
+      if ((a == 1.0 || a == -1.0) && isinf(b)) return 0;
+      return to_int32(pow(a, b));
+    }
+    case WDC_B_MAX: return l > r ? l : r;
+    default: return l < r ? l : r;
+  }
+}
+
+struct BinaryShape {
+  int64_t dims[6];
+  int64_t sa[6];
+  int64_t sb[6];
+};
+
+// mode 0: both contiguous same shape; 1: b is a scalar; 2: a is a scalar;
+// 3: b repeats with period `period` along the innermost run (bias over the last axis)
+template <int OP>
+__global__ void __launch_bounds__(256) binary_f32_fast_kernel(const float* __restrict__ a,
+                                                              const float* __restrict__ b,
+                                                              float* __restrict__ out, int64_t n,
+                                                              int mode, int64_t period, int vec_ok) {
+  int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  if (vec_ok) {
+    int64_t n4 = n >> 2;
+    float sb = (mode == 1) ? b[0] : 0.f, sa = (mode == 2) ? a[0] : 0.f;
+    for (int64_t i = tid; i < n4; i += step) {
+      float4 x, y;
+      if (mode == 2) x = make_float4(sa, sa, sa, sa);
+      else x = __ldg(reinterpret_cast<const float4*>(a) + i);
+      if (mode == 1) y = make_float4(sb, sb, sb, sb);
+      else if (mode == 3) y = __ldg(reinterpret_cast<const float4*>(b + ((i << 2) % period)));
+      else y = __ldg(reinterpret_cast<const float4*>(b) + i);
+      float4 r;
+      r.x = binary_f32<OP>(x.x, y.x);
+      r.y = binary_f32<OP>(x.y, y.y);
+      r.z = binary_f32<OP>(x.z, y.z);
+      r.w = binary_f32<OP>(x.w, y.w);
+      reinterpret_cast<float4*>(out)[i] = r;
+    }
+    tid += n4 << 2;
+  }
+  for (int64_t i = tid; i < n; i += step) {
+    float x = mode == 2 ? a[0] : a[i];
+    float y = mode == 1 ? b[0] : (mode == 3 ? b[i % period] : b[i]);
+    out[i] = binary_f32<OP>(x, y);
+  }
+}
+
+template <int OP>
+__global__ void __launch_bounds__(256) binary_f32_general_kernel(const float* __restrict__ a,
+                                                                 const float* __restrict__ b,
+                                                                 float* __restrict__ out, int64_t n,
+                                                                 BinaryShape sh) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) {
+    int64_t rem = i, ia = 0, ib = 0;
+#pragma unroll
+    for (int d = 5; d >= 0; d--) {
+      int64_t c = rem % sh.dims[d];
+      rem /= sh.dims[d];
+      ia += c * sh.sa[d];
+      ib += c * sh.sb[d];
+    }
+    out[i] = binary_f32<OP>(a[ia], b[ib]);
+  }
+}
+
+__global__ void binary_i32_kernel(int op, const int32_t* __restrict__ a, const int32_t* __restrict__ b,
+                                  int32_t* __restrict__ out, int64_t n, BinaryShape sh) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) {
+    int64_t rem = i, ia = 0, ib = 0;
+#pragma unroll
+    for (int d = 5; d >= 0; d--) {
+      int64_t c = rem % sh.dims[d];
+      rem /= sh.dims[d];
+      ia += c * sh.sa[d];
+      ib += c * sh.sb[d];
+    }
+    out[i] = binary_i32(op, a[ia], b[ib]);
+  }
+}
+
+template <int OP>
+static int launch_binary_f32(wdc_context* ctx, const float* a, const float* b, float* out, int64_t n,
+                             const BinaryShape& sh, int mode, int64_t period) {
+  if (mode >= 0) {
+    int vec_ok = ((((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) & 15) == 0) &&
+                 (mode != 3 || (period % 4) == 0);
+    int64_t items = vec_ok ? (n + 3) / 4 : n;
+    binary_f32_fast_kernel<OP><<<grid_for(ctx, items, 256), 256, 0, ctx->stream>>>(a, b, out, n, mode,
+                                                                                  period, vec_ok);
+    return wdc_check_launch(ctx, "binary_f32_fast_kernel");
+  }
+  binary_f32_general_kernel<OP><<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(a, b, out, n, sh);
+  return wdc_check_launch(ctx, "binary_f32_general_kernel");
+}
+
+extern "C" int wdc_binary(wdc_context* ctx, int op, int dtype, const void* a, const void* b, void* out,
+                          int ndim, const int64_t* dims, const int64_t* sa, const int64_t* sb) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_binary: null context");
+  WDC_REQUIRE(ctx, ndim >= 0 && ndim <= 6, "wdc_binary: rank %d not in 0..6", ndim);
+  WDC_REQUIRE(ctx, op >= WDC_B_ADD && op <= WDC_B_MIN, "wdc_binary: unknown op %d", op);
+  WDC_REQUIRE(ctx, dtype == 0 || dtype == 1, "wdc_binary: dtype %d not supported", dtype);
+  WDC_REQUIRE(ctx, ndim == 0 || (dims && sa && sb), "wdc_binary: null shape");
+  BinaryShape sh;
+  int64_t n = 1;
+  for (int i = 0; i < 6; i++) {
+    sh.dims[i] = 1;
+    sh.sa[i] = sh.sb[i] = 0;
+  }
+  for (int i = 0; i < ndim; i++) {
+    WDC_REQUIRE(ctx, dims[i] >= 0, "wdc_binary: negative dim");
+    sh.dims[6 - ndim + i] = dims[i];
+    sh.sa[6 - ndim + i] = sa[i];
+    sh.sb[6 - ndim + i] = sb[i];
+    n *= dims[i];
+  }
+  if (n == 0) return WDC_OK;
+  WDC_REQUIRE(ctx, a && b && out, "wdc_binary: null buffer");
+  DeviceGuard g(ctx->device);
+  if (dtype == 1) {
+    binary_i32_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>(op, (const int32_t*)a,
+                                                                     (const int32_t*)b, (int32_t*)out, n, sh);
+    return wdc_check_launch(ctx, "binary_i32_kernel");
+  }
+  // classify
+  bool a_contig = true, b_contig = true, a_scalar = true, b_scalar = true;
+  int64_t run = 1;
+  for (int d = 5; d >= 0; d--) {
+    if (sh.dims[d] == 1) continue;
+    if (sh.sa[d] != run) a_contig = false;
+    if (sh.sb[d] != run) b_contig = false;
+    if (sh.sa[d] != 0) a_scalar = false;
+    if (sh.sb[d] != 0) b_scalar = false;
+    run *= sh.dims[d];
+  }
+  int mode = -1;
+  int64_t period = 1;
+  if (a_contig && b_contig) mode = 0;
+  else if (a_contig && b_scalar) mode = 1;
+  else if (a_scalar && b_contig) mode = 2;
+  else if (a_contig) {
+    // b dense over a trailing run of axes and broadcast over all leading ones
+    int64_t r = 1;
+    int d = 5;
+    bool ok = true;
+    for (; d >= 0; d--) {
+      if (sh.dims[d] == 1) continue;
+      if (sh.sb[d] == r) r *= sh.dims[d];
+      else break;
+    }
+    for (; d >= 0; d--)
+      if (sh.dims[d] != 1 && sh.sb[d] != 0) ok = false;
+    if (ok && r > 1) {
+      mode = 3;
+      period = r;
+    }
+  }
+  const float* fa = (const float*)a;
+  const float* fb = (const float*)b;
+  float* fo = (float*)out;
+  switch (op) {
+    case WDC_B_ADD: return launch_binary_f32<WDC_B_ADD>(ctx, fa, fb, fo, n, sh, mode, period);
+    case WDC_B_SUB: return launch_binary_f32<WDC_B_SUB>(ctx, fa, fb, fo, n, sh, mode, period);
+    case WDC_B_MUL: return launch_binary_f32<WDC_B_MUL>(ctx, fa, fb, fo, n, sh, mode, period);
+    case WDC_B_DIV: return launch_binary_f32<WDC_B_DIV>(ctx, fa, fb, fo, n, sh, mode, period);
+    case WDC_B_POW: return launch_binary_f32<WDC_B_POW>(ctx, fa, fb, fo, n, sh, mode, period);
+    case WDC_B_MAX: return launch_binary_f32<WDC_B_MAX>(ctx, fa, fb, fo, n, sh, mode, period);
+    default: return launch_binary_f32<WDC_B_MIN>(ctx, fa, fb, fo, n, sh, mode, period);
+  }
+}
+
+// --------------------------------------------------------------------------------- cast
+__global__ void cast_f32_i32_kernel(const float* __restrict__ s, int32_t* __restrict__ d, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) d[i] = to_int32((double)s[i]);
+}
+__global__ void cast_i32_f32_kernel(const int32_t* __restrict__ s, float* __restrict__ d, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) d[i] = (float)s[i];
+}
+
+extern "C" int wdc_cast(wdc_context* ctx, int src_dtype, int dst_dtype, const void* src, void* dst,
+                        int64_t n) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_cast: null context");
+  WDC_REQUIRE(ctx, n >= 0 && (n == 0 || (src && dst)), "wdc_cast: bad buffer or count");
+  if (n == 0) return WDC_OK;
+  DeviceGuard g(ctx->device);
+  if (src_dtype == dst_dtype && (src_dtype == 0 || src_dtype == 1)) return wdc_copy(ctx, dst, src, n * 4);
+  if (src_dtype == 0 && dst_dtype == 1) {
+    cast_f32_i32_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>((const float*)src, (int32_t*)dst, n);
+    return wdc_check_launch(ctx, "cast_f32_i32_kernel");
+  }
+  if (src_dtype == 1 && dst_dtype == 0) {
+    cast_i32_f32_kernel<<<grid_for(ctx, n, 256), 256, 0, ctx->stream>>>((const int32_t*)src, (float*)dst, n);
+    return wdc_check_launch(ctx, "cast_i32_f32_kernel");
+  }
+  return wdc_fail(ctx, WDC_ERR_UNSUPPORTED, "wdc_cast: %d -> %d not supported", src_dtype, dst_dtype);
+}
+
+// ---------------------------------------------------------------------- per-channel affine
+__global__ void __launch_bounds__(256) channel_affine_kernel(const float* __restrict__ x,
+                                                             const float* __restrict__ scale,
+                                                             const float* __restrict__ shift,
+                                                             float* __restrict__ y, int64_t n,
+                                                             int64_t channels, int64_t inner, int relu,
+                                                             int vec_ok) {
+  int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  if (vec_ok) {  // inner == 1 (channels innermost, multiple of 4) or inner % 4 == 0
+    int64_t n4 = n >> 2;
+    for (int64_t i = tid; i < n4; i += step) {
+      float4 v = __ldg(reinterpret_cast<const float4*>(x) + i);
+      int64_t e = i << 2;
+      float4 r;
+      if (inner == 1) {
+        int64_t c = e % channels;
+        float4 s = __ldg(reinterpret_cast<const float4*>(scale + c));
+        float4 t = __ldg(reinterpret_cast<const float4*>(shift + c));
+        r.x = fmaf(v.x, s.x, t.x);
+        r.y = fmaf(v.y, s.y, t.y);
+        r.z = fmaf(v.z, s.z, t.z);
+        r.w = fmaf(v.w, s.w, t.w);
+      } else {
+        int64_t c = (e / inner) % channels;
+        float s = __ldg(scale + c), t = __ldg(shift + c);
+        r.x = fmaf(v.x, s, t);
+        r.y = fmaf(v.y, s, t);
+        r.z = fmaf(v.z, s, t);
+        r.w = fmaf(v.w, s, t);
+      }
+      if (relu) {
+        r.x = r.x > 0.f ? r.x : (r.x == r.x ? 0.f : r.x);
+        r.y = r.y > 0.f ? r.y : (r.y == r.y ? 0.f : r.y);
+        r.z = r.z > 0.f ? r.z : (r.z == r.z ? 0.f : r.z);
+        r.w = r.w > 0.f ? r.w : (r.w == r.w ? 0.f : r.w);
+      }
+      reinterpret_cast<float4*>(y)[i] = r;
+    }
+    return;
+  }
+  for (int64_t i = tid; i < n; i += step) {
+    int64_t c = (i / inner) % channels;
+    float r = fmaf(x[i], scale[c], shift[c]);
+    if (relu) r = r > 0.f ? r : (r == r ? 0.f : r);
+    y[i] = r;
+  }
+}
+
+extern "C" int wdc_channel_affine(wdc_context* ctx, const float* x, const float* scale,
+                                  const float* shift, float* y, int64_t outer, int64_t channels,
+                                  int64_t inner, int relu) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_channel_affine: null context");
+  WDC_REQUIRE(ctx, outer >= 0 && channels > 0 && inner > 0, "wdc_channel_affine: bad shape");
+  int64_t n = outer * channels * inner;
+  if (n == 0) return WDC_OK;
+  WDC_REQUIRE(ctx, x && y && scale && shift, "wdc_channel_affine: null buffer");
+  DeviceGuard g(ctx->device);
+  bool aligned = ((((uintptr_t)x | (uintptr_t)y | (uintptr_t)scale | (uintptr_t)shift) & 15) == 0);
+  int vec_ok = aligned && (n % 4 == 0) &&
+               ((inner == 1 && channels % 4 == 0) || (inner > 1 && inner % 4 == 0));
+  int64_t items = vec_ok ? n / 4 : n;
+  channel_affine_kernel<<<grid_for(ctx, items, 256), 256, 0, ctx->stream>>>(x, scale, shift, y, n,
+                                                                           channels, inner, relu, vec_ok);
+  return wdc_check_launch(ctx, "channel_affine_kernel");
+}

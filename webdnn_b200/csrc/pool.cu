@@ -1,0 +1,154 @@
+// Pooling kernels.  Tensors are addressed through (n, c, h, w) element strides so that the
+// channels-last tensors the convolution path produces and canonical NCHW tensors share the code.
+// When channels are innermost (stride 1) and a multiple of 4, each thread handles 4 channels with
+// 128-bit accesses.
+#include <math.h>
+
+#include "common.cuh"
+
+template <bool IS_MAX, int VEC>
+__global__ void __launch_bounds__(256) pool2d_kernel(wdc_pool_desc d, const float* __restrict__ x,
+                                                     float* __restrict__ y, int c_fastest) {
+  int64_t chv = d.ch / VEC;
+  int64_t n = d.batch * chv * d.out_h * d.out_w;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) {
+    int64_t b, c, oy, ox, rem = i;
+    if (c_fastest) {  // consecutive threads walk channels: coalesced for channels-last tensors
+      c = (rem % chv) * VEC; rem /= chv;
+      ox = rem % d.out_w; rem /= d.out_w;
+      oy = rem % d.out_h; rem /= d.out_h;
+      b = rem;
+    } else {          // consecutive threads walk output columns: coalesced for NCHW
+      ox = rem % d.out_w; rem /= d.out_w;
+      oy = rem % d.out_h; rem /= d.out_h;
+      c = (rem % chv) * VEC; rem /= chv;
+      b = rem;
+    }
+    float acc[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; v++) acc[v] = IS_MAX ? -INFINITY : 0.f;
+    double dacc[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; v++) dacc[v] = 0.0;
+    int ctr = 0;
+    for (int64_t ky = 0; ky < d.k_h; ky++) {
+      int64_t iny = oy * d.stride_h - d.pad_t + ky * d.dil_h;
+      if (iny < 0 || iny >= d.in_h) continue;
+      for (int64_t kx = 0; kx < d.k_w; kx++) {
+        int64_t inx = ox * d.stride_w - d.pad_l + kx * d.dil_w;
+        if (inx < 0 || inx >= d.in_w) continue;
+        const float* p = x + b * d.xs_n + c * d.xs_c + iny * d.xs_h + inx * d.xs_w;
+        float val[VEC];
+        if (VEC == 4) {
+          float4 t = __ldg(reinterpret_cast<const float4*>(p));
+          val[0] = t.x; val[1 % VEC] = t.y; val[2 % VEC] = t.z; val[3 % VEC] = t.w;
+        } else {
+          val[0] = __ldg(p);
+        }
+#pragma unroll
+        for (int v = 0; v < VEC; v++) {
+          if (IS_MAX) {
+            if (val[v] > acc[v]) acc[v] = val[v];  // strict >, NaN never wins (maxpool.ts:96)
+          } else {
+            dacc[v] += (double)val[v];
+          }
+        }
+        ctr++;
+      }
+    }
+    float out[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; v++) {
+      if (IS_MAX) out[v] = acc[v];
+      else out[v] = (float)(d.count_include_pad ? dacc[v] / (double)(d.k_h * d.k_w) : dacc[v] / (double)ctr);
+    }
+    float* q = y + b * d.ys_n + c * d.ys_c + oy * d.ys_h + ox * d.ys_w;
+    if (VEC == 4) *reinterpret_cast<float4*>(q) = make_float4(out[0], out[1 % VEC], out[2 % VEC], out[3 % VEC]);
+    else *q = out[0];
+  }
+}
+
+static int pool_common(wdc_context* ctx, const wdc_pool_desc* d, const float* x, float* y, bool is_max,
+                       const char* who) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "%s: null context", who);
+  WDC_REQUIRE(ctx, d != nullptr, "%s: null descriptor", who);
+  WDC_REQUIRE(ctx, d->batch >= 0 && d->ch >= 0 && d->in_h > 0 && d->in_w > 0 && d->out_h >= 0 &&
+                       d->out_w >= 0 && d->k_h > 0 && d->k_w > 0 && d->stride_h > 0 && d->stride_w > 0 &&
+                       d->dil_h > 0 && d->dil_w > 0,
+              "%s: bad shape", who);
+  int64_t n = d->batch * d->ch * d->out_h * d->out_w;
+  if (n == 0) return WDC_OK;
+  WDC_REQUIRE(ctx, x && y, "%s: null buffer", who);
+  DeviceGuard g(ctx->device);
+  bool cl = d->xs_c == 1 && d->ys_c == 1;
+  bool vec = cl && d->ch % 4 == 0 && ((((uintptr_t)x | (uintptr_t)y) & 15) == 0) && d->xs_n % 4 == 0 &&
+             d->xs_h % 4 == 0 && d->xs_w % 4 == 0 && d->ys_n % 4 == 0 && d->ys_h % 4 == 0 && d->ys_w % 4 == 0;
+  int64_t items = vec ? n / 4 : n;
+  int grid = grid_for(ctx, items, 256, 8);
+  if (is_max) {
+    if (vec) pool2d_kernel<true, 4><<<grid, 256, 0, ctx->stream>>>(*d, x, y, 1);
+    else pool2d_kernel<true, 1><<<grid, 256, 0, ctx->stream>>>(*d, x, y, cl ? 1 : 0);
+  } else {
+    if (vec) pool2d_kernel<false, 4><<<grid, 256, 0, ctx->stream>>>(*d, x, y, 1);
+    else pool2d_kernel<false, 1><<<grid, 256, 0, ctx->stream>>>(*d, x, y, cl ? 1 : 0);
+  }
+  return wdc_check_launch(ctx, "pool2d_kernel");
+}
+
+extern "C" int wdc_maxpool2d(wdc_context* ctx, const wdc_pool_desc* d, const float* x, float* y) {
+  return pool_common(ctx, d, x, y, true, "wdc_maxpool2d");
+}
+extern "C" int wdc_avgpool2d(wdc_context* ctx, const wdc_pool_desc* d, const float* x, float* y) {
+  return pool_common(ctx, d, x, y, false, "wdc_avgpool2d");
+}
+
+// Global average pool.  Channels-last: one thread per (b, c), walking pixels with stride xs_p,
+// coalesced across c.  NCHW: one warp per (b, c), lanes stride the pixels.
+__global__ void __launch_bounds__(256) gap_cl_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                     int64_t batch, int64_t ch, int64_t area,
+                                                     int64_t xs_n, int64_t xs_p) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < batch * ch; i += step) {
+    int64_t b = i / ch, c = i % ch;
+    const float* p = x + b * xs_n + c;
+    double s = 0;
+    for (int64_t a = 0; a < area; a++) s += (double)__ldg(p + a * xs_p);
+    y[i] = (float)(s / (double)area);
+  }
+}
+
+__global__ void __launch_bounds__(256) gap_warp_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                       int64_t batch, int64_t ch, int64_t area,
+                                                       int64_t xs_n, int64_t xs_c, int64_t xs_p) {
+  int lane = threadIdx.x & 31;
+  int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  int64_t rstep = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (; row < batch * ch; row += rstep) {
+    int64_t b = row / ch, c = row % ch;
+    const float* p = x + b * xs_n + c * xs_c;
+    double s = 0;
+    for (int64_t a = lane; a < area; a += 32) s += (double)__ldg(p + a * xs_p);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) y[row] = (float)(s / (double)area);
+  }
+}
+
+extern "C" int wdc_global_avgpool(wdc_context* ctx, const float* x, float* y, int64_t batch, int64_t ch,
+                                  int64_t area, int64_t xs_n, int64_t xs_c, int64_t xs_p) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_global_avgpool: null context");
+  WDC_REQUIRE(ctx, batch >= 0 && ch >= 0 && area > 0, "wdc_global_avgpool: bad shape");
+  if (batch * ch == 0) return WDC_OK;
+  WDC_REQUIRE(ctx, x && y, "wdc_global_avgpool: null buffer");
+  DeviceGuard g(ctx->device);
+  if (xs_c == 1) {
+    gap_cl_kernel<<<grid_for(ctx, batch * ch, 256, 8), 256, 0, ctx->stream>>>(x, y, batch, ch, area, xs_n, xs_p);
+    return wdc_check_launch(ctx, "gap_cl_kernel");
+  }
+  gap_warp_kernel<<<grid_for(ctx, batch * ch * 32, 256, 8), 256, 0, ctx->stream>>>(x, y, batch, ch, area,
+                                                                                  xs_n, xs_c, xs_p);
+  return wdc_check_launch(ctx, "gap_warp_kernel");
+}

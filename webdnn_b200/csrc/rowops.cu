@@ -1,0 +1,332 @@
+// Row-wise kernels: softmax, single-axis reductions, layer normalisation, argmax.
+// Each row is owned by one warp (rows up to 1024 elements are held in registers so the input is
+// read from HBM exactly once) or by one CTA (longer rows, re-read through L2).
+#include <math.h>
+
+#include "common.cuh"
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// ------------------------------------------------------------------------------ softmax
+// operators/cpu/operators/standard/softmax.ts:39-57: max, exp(v - max), sum, divide.
+template <int ITEMS>
+__global__ void __launch_bounds__(256) softmax_warp_kernel(const float* __restrict__ x,
+                                                           float* __restrict__ y, int64_t outer,
+                                                           int len) {
+  int lane = threadIdx.x & 31;
+  int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  int64_t rstep = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (; row < outer; row += rstep) {
+    const float* xr = x + row * len;
+    float v[ITEMS];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+      int c = i * 32 + lane;
+      v[i] = c < len ? xr[c] : -INFINITY;
+      mx = fmaxf(mx, v[i]);
+    }
+    mx = warp_max(mx);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+      int c = i * 32 + lane;
+      v[i] = c < len ? expf(v[i] - mx) : 0.f;
+      s += v[i];
+    }
+    s = warp_sum(s);
+    float* yr = y + row * len;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+      int c = i * 32 + lane;
+      if (c < len) yr[c] = v[i] / s;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(512) softmax_block_kernel(const float* __restrict__ x,
+                                                            float* __restrict__ y, int64_t outer,
+                                                            int64_t len) {
+  __shared__ float red[32];
+  __shared__ float bcast;
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int64_t row = blockIdx.x; row < outer; row += gridDim.x) {
+    const float* xr = x + row * len;
+    float* yr = y + row * len;
+    float mx = -INFINITY;
+    for (int64_t c = threadIdx.x; c < len; c += blockDim.x) mx = fmaxf(mx, xr[c]);
+    mx = warp_max(mx);
+    if (lane == 0) red[wid] = mx;
+    __syncthreads();
+    if (wid == 0) {
+      float t = lane < nw ? red[lane] : -INFINITY;
+      t = warp_max(t);
+      if (lane == 0) bcast = t;
+    }
+    __syncthreads();
+    mx = bcast;
+    float s = 0.f;
+    for (int64_t c = threadIdx.x; c < len; c += blockDim.x) {
+      float e = expf(xr[c] - mx);
+      yr[c] = e;
+      s += e;
+    }
+    s = warp_sum(s);
+    __syncthreads();
+    if (lane == 0) red[wid] = s;
+    __syncthreads();
+    if (wid == 0) {
+      float t = lane < nw ? red[lane] : 0.f;
+      t = warp_sum(t);
+      if (lane == 0) bcast = t;
+    }
+    __syncthreads();
+    s = bcast;
+    for (int64_t c = threadIdx.x; c < len; c += blockDim.x) yr[c] = yr[c] / s;
+    __syncthreads();
+  }
+}
+
+extern "C" int wdc_softmax(wdc_context* ctx, const float* x, float* y, int64_t outer, int64_t len) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_softmax: null context");
+  WDC_REQUIRE(ctx, outer >= 0 && len >= 0, "wdc_softmax: negative shape");
+  if (outer == 0 || len == 0) return WDC_OK;
+  WDC_REQUIRE(ctx, x && y, "wdc_softmax: null buffer");
+  DeviceGuard g(ctx->device);
+  if (len <= 1024) {
+    int wpb = 8;
+    int grid = grid_for(ctx, outer * 32, wpb * 32, 8);
+    int l = (int)len;
+#define SM(IT) softmax_warp_kernel<IT><<<grid, wpb * 32, 0, ctx->stream>>>(x, y, outer, l)
+    if (len <= 32) SM(1);
+    else if (len <= 128) SM(4);
+    else if (len <= 256) SM(8);
+    else if (len <= 512) SM(16);
+    else SM(32);
+#undef SM
+    return wdc_check_launch(ctx, "softmax_warp_kernel");
+  }
+  int grid = (int)(outer < (int64_t)ctx->sm_count * 4 ? outer : (int64_t)ctx->sm_count * 4);
+  softmax_block_kernel<<<grid, 512, 0, ctx->stream>>>(x, y, outer, len);
+  return wdc_check_launch(ctx, "softmax_block_kernel");
+}
+
+// ------------------------------------------------------------------------------- reduce
+// One pass of operators/cpu/operators/standard/reduce.ts:41-103 over [outer, red, inner].
+// Sums are accumulated in double like the reference's JS numbers; the reference's per-pass
+// application of abs/square/exp and its ReduceLogSum indexing (reduce.ts:288-312) are kept.
+enum { R_SUM = 0, R_MEAN, R_MAX, R_MIN, R_PROD, R_L1, R_L2, R_LOGSUM, R_LOGSUMEXP, R_SUMSQUARE };
+
+__device__ __forceinline__ double red_map(int kind, float v) {
+  switch (kind) {
+    case R_L1: return fabs((double)v);
+    case R_L2:
+    case R_SUMSQUARE: return (double)v * (double)v;
+    case R_LOGSUMEXP: return exp((double)v);
+    default: return (double)v;
+  }
+}
+__device__ __forceinline__ double red_combine(int kind, double a, double b) {
+  switch (kind) {
+    case R_MAX: return b > a ? b : a;
+    case R_MIN: return b < a ? b : a;
+    case R_PROD: return a * b;
+    default: return a + b;
+  }
+}
+__device__ __forceinline__ double red_finish(int kind, int final, double s, int64_t total) {
+  if (!final) return s;
+  switch (kind) {
+    case R_MEAN: return s / (double)total;
+    case R_L2: return sqrt(s);
+    case R_LOGSUM:
+    case R_LOGSUMEXP: return log(s);
+    default: return s;
+  }
+}
+
+// inner == 1: one warp per output element, lanes stride the reduced axis.
+__global__ void __launch_bounds__(256) reduce_rows_kernel(int kind, int final, const float* __restrict__ x,
+                                                          float* __restrict__ y, int64_t outer,
+                                                          int64_t red, int64_t total) {
+  int lane = threadIdx.x & 31;
+  int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  int64_t rstep = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (; row < outer; row += rstep) {
+    const float* p = x + row * red;
+    double ident = (kind == R_PROD) ? 1.0 : (kind == R_MAX ? -INFINITY : (kind == R_MIN ? INFINITY : 0.0));
+    double s = ident;
+    for (int64_t r = lane; r < red; r += 32) s = red_combine(kind, s, red_map(kind, p[r]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s = red_combine(kind, s, __shfl_xor_sync(0xffffffffu, s, o));
+    if (lane == 0) y[row] = (float)red_finish(kind, final, s, total);
+  }
+}
+
+// inner > 1: one thread per (outer, inner) output, coalesced across inner.
+__global__ void __launch_bounds__(256) reduce_cols_kernel(int kind, int final, const float* __restrict__ x,
+                                                          float* __restrict__ y, int64_t outer,
+                                                          int64_t red, int64_t inner, int64_t total) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  int64_t n = outer * inner;
+  for (; i < n; i += step) {
+    int64_t o = i / inner, in = i % inner;
+    const float* p = x + o * red * inner + in;
+    double s;
+    if (kind == R_LOGSUM) {
+      s = 0;
+      for (int64_t r = 0; r < red; r++) s += (double)x[o * red + r];
+    } else if (kind == R_MAX || kind == R_MIN) {
+      s = p[0];
+      for (int64_t r = 1; r < red; r++) s = red_combine(kind, s, (double)p[r * inner]);
+    } else {
+      s = (kind == R_PROD) ? 1.0 : 0.0;
+      for (int64_t r = 0; r < red; r++) s = red_combine(kind, s, red_map(kind, p[r * inner]));
+    }
+    y[i] = (float)red_finish(kind, final, s, total);
+  }
+}
+
+extern "C" int wdc_reduce_axis(wdc_context* ctx, int kind, int final, const float* x, float* y,
+                               int64_t outer, int64_t red, int64_t inner, int64_t total) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_reduce_axis: null context");
+  WDC_REQUIRE(ctx, kind >= R_SUM && kind <= R_SUMSQUARE, "wdc_reduce_axis: unknown kind %d", kind);
+  WDC_REQUIRE(ctx, outer >= 0 && red > 0 && inner > 0, "wdc_reduce_axis: bad shape");
+  if (outer == 0) return WDC_OK;
+  WDC_REQUIRE(ctx, x && y, "wdc_reduce_axis: null buffer");
+  DeviceGuard g(ctx->device);
+  if (inner == 1 && red >= 64) {
+    reduce_rows_kernel<<<grid_for(ctx, outer * 32, 256, 8), 256, 0, ctx->stream>>>(kind, final, x, y,
+                                                                                  outer, red, total);
+    return wdc_check_launch(ctx, "reduce_rows_kernel");
+  }
+  reduce_cols_kernel<<<grid_for(ctx, outer * inner, 256, 8), 256, 0, ctx->stream>>>(
+      kind, final, x, y, outer, red, inner, total);
+  return wdc_check_launch(ctx, "reduce_cols_kernel");
+}
+
+// --------------------------------------------------------------------------- layer norm
+// Equals the reference's decomposed chain ReduceMean -> Sub -> Mul(x,x) -> ReduceMean -> Add(eps)
+// -> Sqrt -> Div -> Mul(gamma) -> Add(beta) with a float rounding after each node.
+template <int ITEMS>
+__global__ void __launch_bounds__(256) layernorm_warp_kernel(const float* __restrict__ x,
+                                                             const float* __restrict__ gamma,
+                                                             const float* __restrict__ beta,
+                                                             float* __restrict__ y, int64_t outer,
+                                                             int len, float eps) {
+  int lane = threadIdx.x & 31;
+  int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  int64_t rstep = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (; row < outer; row += rstep) {
+    const float* xr = x + row * len;
+    float v[ITEMS];
+    double s = 0;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+      int c = i * 32 + lane;
+      v[i] = c < len ? xr[c] : 0.f;
+      s += (double)v[i];
+    }
+    float mean = (float)(warp_sum_d(s) / (double)len);
+    double q = 0;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+      int c = i * 32 + lane;
+      v[i] = v[i] - mean;                      // Sub
+      float sq = v[i] * v[i];                  // Mul / Pow 2
+      q += c < len ? (double)sq : 0.0;
+    }
+    float var = (float)(warp_sum_d(q) / (double)len);  // ReduceMean
+    float den = sqrtf(var + eps);                       // Add, Sqrt
+    float* yr = y + row * len;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+      int c = i * 32 + lane;
+      if (c < len) {
+        float r = v[i] / den;                  // Div
+        if (gamma) r = r * gamma[c];           // Mul
+        if (beta) r = r + beta[c];             // Add
+        yr[c] = r;
+      }
+    }
+  }
+}
+
+extern "C" int wdc_layernorm(wdc_context* ctx, const float* x, const float* gamma, const float* beta,
+                             float* y, int64_t outer, int64_t len, float eps) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_layernorm: null context");
+  WDC_REQUIRE(ctx, outer >= 0 && len > 0, "wdc_layernorm: bad shape");
+  if (len > 1024)
+    return wdc_fail(ctx, WDC_ERR_UNSUPPORTED, "wdc_layernorm: rows longer than 1024 (%lld) not supported",
+                    (long long)len);
+  if (outer == 0) return WDC_OK;
+  WDC_REQUIRE(ctx, x && y, "wdc_layernorm: null buffer");
+  DeviceGuard g(ctx->device);
+  int grid = grid_for(ctx, outer * 32, 256, 8);
+  int l = (int)len;
+#define LN(IT) layernorm_warp_kernel<IT><<<grid, 256, 0, ctx->stream>>>(x, gamma, beta, y, outer, l, eps)
+  if (len <= 32) LN(1);
+  else if (len <= 128) LN(4);
+  else if (len <= 256) LN(8);
+  else if (len <= 512) LN(16);
+  else LN(32);
+#undef LN
+  return wdc_check_launch(ctx, "layernorm_warp_kernel");
+}
+
+// ------------------------------------------------------------------------------- argmax
+__global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ x, int32_t* __restrict__ y,
+                                                     int64_t outer, int64_t len, int select_last) {
+  int lane = threadIdx.x & 31;
+  int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  int64_t rstep = (int64_t)gridDim.x * (blockDim.x >> 5);
+  for (; row < outer; row += rstep) {
+    const float* p = x + row * len;
+    // NaN never wins a strict comparison; start from element 0 like a sequential scan
+    float bv = p[0];
+    int64_t bi = 0;
+    for (int64_t r = lane; r < len; r += 32) {
+      float v = p[r];
+      if (v > bv || (v == bv && (select_last ? r > bi : r < bi))) {
+        bv = v;
+        bi = r;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      int64_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && (select_last ? oi > bi : oi < bi))) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    if (lane == 0) y[row] = (int32_t)bi;
+  }
+}
+
+extern "C" int wdc_argmax(wdc_context* ctx, const float* x, int32_t* y, int64_t outer, int64_t len,
+                          int select_last) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_argmax: null context");
+  WDC_REQUIRE(ctx, outer >= 0 && len > 0, "wdc_argmax: bad shape");
+  if (outer == 0) return WDC_OK;
+  WDC_REQUIRE(ctx, x && y, "wdc_argmax: null buffer");
+  DeviceGuard g(ctx->device);
+  argmax_kernel<<<grid_for(ctx, outer * 32, 256, 8), 256, 0, ctx->stream>>>(x, y, outer, len, select_last);
+  return wdc_check_launch(ctx, "argmax_kernel");
+}

@@ -1,0 +1,274 @@
+"""``WebDNN.load`` and ``RunnerImpl`` for the Python host mirror.
+
+``load()`` follows ``src/descriptor_runner/index.ts:42-149``: a cpu context always exists, each
+name of ``backendOrder`` is tried in turn, the first that initialises wins, and the runner is built
+with ``[succeeded, "cpu"]``.  Only ``"cuda"`` and ``"cpu"`` exist here.
+
+``Runner.run()`` restates ``core/runnerImpl.ts:315-596`` step by step: seed the per-backend tensor
+maps with initializers (and the device copies cached from earlier runs), bind inputs positionally,
+compute release timing, then for each node find where its inputs live, instantiate the operator,
+move inputs according to its backend requirement, run it, file its outputs under their backend and
+dispose tensors after their last consumer; finally move outputs to the cpu and dispose the rest.
+
+One deliberate difference: the reference retries a failing node once on the cpu backend
+(``runnerImpl.ts:511-520``).  This backend ships no cpu implementation of the arithmetic ops, so a
+node that fails on ``cuda`` raises; ``node_backends`` of the last run is exposed so callers can
+assert that nothing ran on the host except shape bookkeeping.
+"""
+from __future__ import annotations
+
+import json
+import logging
+import os
+import time
+from typing import Dict, List, Optional, Sequence, Union
+
+import numpy as np
+
+from . import onnx_io
+from .backend import CPUTensor, WebDNNCPUContext, WebDNNCudaContext
+from .model_transform import find_tensor_release_timing, model_transform
+from .onnx_io import FLOAT, INT32, INT64, Model, clip_long
+from .operator_table import instantiate_operator, register_operators, registered_op_types
+
+logger = logging.getLogger("WebDNN.runner")
+
+BACKENDS = ["cpu", "cuda"]
+BACKENDS_WITHOUT_CPU = ["cuda"]
+
+_registered_backends = set()
+
+
+def _register(backend: str) -> None:
+    if backend in _registered_backends:
+        return
+    if backend == "cpu":
+        from .operators.host import get_op_entries
+    else:
+        from .operators.cuda import get_op_entries
+    register_operators(get_op_entries())
+    _registered_backends.add(backend)
+
+
+class Runner:
+    def __init__(self, backend_order: Sequence[str], backend_contexts: Dict[str, object]):
+        self.backend_order = list(backend_order)
+        self.backend_contexts = backend_contexts
+        self.model: Optional[Model] = None
+        self.loaded = False
+        self.opset = 0
+        self.initializer_tensors: Dict[str, CPUTensor] = {}
+        self.copied_initializer_tensors: Dict[str, Dict[str, object]] = {b: {} for b in BACKENDS_WITHOUT_CPU}
+        self.tensor_move_options: Dict[str, dict] = {}
+        self.force_operator_backend_order: Dict[str, List[str]] = {}
+        self.inputs_without_initializer = []
+        self.node_backends: List[tuple] = []      # (node name, op type, backend) of the last run
+        self.node_performances: List[dict] = []
+
+    # ---- runnerImpl.ts:88-134
+    def load_model(self, source: Union[str, bytes, Model], onnx_basename: str = "model.onnx") -> None:
+        if isinstance(source, Model):
+            model = onnx_io.decode_model(onnx_io.encode_model(source))  # private copy
+        elif isinstance(source, (bytes, bytearray)):
+            model = onnx_io.decode_model(bytes(source))
+        else:
+            path = os.path.join(source, onnx_basename) if os.path.isdir(source) else source
+            model = onnx_io.load_model(path)
+        model_transform(model, self.backend_order)
+        if not model.opset_import:
+            raise ValueError("opsetImport is empty")
+        self.opset = int(model.opset_import[0][1])
+        self.model = model
+        self.initializer_tensors = self._extract_initializer_tensor()
+        for md_key, md_value in model.metadata_props.items():
+            if md_key == "WebDNN2.TensorMoveOptions":
+                self.tensor_move_options = json.loads(md_value)
+            elif md_key == "WebDNN2.ForceOperatorBackendOrder":
+                self.force_operator_backend_order = json.loads(md_value)
+        init_names = set(self.initializer_tensors)
+        self.inputs_without_initializer = [vi for vi in model.graph.input if vi.name not in init_names]
+        self.loaded = True
+
+    # ---- runnerImpl.ts:136-233
+    def _extract_initializer_tensor(self) -> Dict[str, CPUTensor]:
+        tensors: Dict[str, CPUTensor] = {}
+        cpu = self.backend_contexts["cpu"]
+        for t in self.model.graph.initializer:
+            dims = [clip_long(int(d)) for d in t.dims]
+            if t.data_type == FLOAT:
+                tensors[t.name] = cpu.empty_tensor(dims, "float32", np.ascontiguousarray(t.array, dtype=np.float32))
+            elif t.data_type == INT64:
+                arr = np.clip(t.array.astype(np.int64), -(2 ** 31), 2 ** 31 - 1).astype(np.int32)
+                tensors[t.name] = cpu.empty_tensor(dims, "int32", arr)
+            elif t.data_type == INT32:
+                tensors[t.name] = cpu.empty_tensor(dims, "int32", np.ascontiguousarray(t.array, dtype=np.int32))
+            else:
+                raise ValueError(f"Unsupported initializer dataType {t.data_type}")
+        return tensors
+
+    def get_input_names(self) -> List[str]:
+        return [vi.name for vi in self.inputs_without_initializer]
+
+    def get_output_names(self) -> List[str]:
+        return [vi.name for vi in self.model.graph.output]
+
+    # ---- runnerImpl.ts:315-596
+    def run(self, inputs: Sequence[CPUTensor], measure_performance: bool = False,
+            outputs_on_device: bool = False) -> List[CPUTensor]:
+        """``inputs`` are CPUTensors as in the reference; a tensor that already lives on a device
+        backend is filed under that backend instead (used to time the device path with resident
+        inputs).  ``outputs_on_device`` skips the final move to the cpu and returns the device
+        tensors, which the caller must dispose."""
+        if self.model is None or not self.loaded:
+            raise RuntimeError("not initialized")
+        graph = self.model.graph
+        tensors_for_backends: Dict[str, Dict[str, object]] = {b: {} for b in BACKENDS}
+        for name, tensor in self.initializer_tensors.items():
+            tensors_for_backends["cpu"][name] = tensor
+        for backend, kv in self.copied_initializer_tensors.items():
+            for name, tensor in kv.items():
+                tensors_for_backends[backend][name] = tensor
+
+        if len(self.inputs_without_initializer) != len(inputs):
+            raise ValueError("length of inputs mismatch")
+        borrowed = set()
+        for vi, t in zip(self.inputs_without_initializer, inputs):
+            tensors_for_backends[t.backend][vi.name] = t
+            if t.backend != "cpu":
+                borrowed.add(vi.name)  # caller-owned device tensor: never disposed here
+
+        release_timing = find_tensor_release_timing(self.model, set(self.initializer_tensors))
+        self.node_backends = []
+        self.node_performances = []
+
+        for node in graph.node:
+            t0 = time.perf_counter()
+            op_type = node.op_type
+            order = self.force_operator_backend_order.get(node.name) or self.backend_order
+            current: List[List[str]] = []
+            for input_name in node.input:
+                bs = [b for b in order if input_name in tensors_for_backends[b]]
+                if not bs:
+                    bs = [b for b in BACKENDS if input_name in tensors_for_backends[b]]
+                current.append(bs)
+            operator = instantiate_operator(op_type, self.opset, order, current)
+            if operator is None:
+                raise RuntimeError(f"Operator implementation for {op_type}, opset={self.opset} does not exist.")
+            operator.initialize(node.attribute)
+            requirement = operator.get_tensor_backend_requirement(len(node.input), len(node.output))
+            operator_inputs = []
+            for j, input_name in enumerate(node.input):
+                req = requirement[j]
+                if not req:
+                    if not current[j]:
+                        raise RuntimeError(f"Input {input_name} not found")
+                    operator_inputs.append(tensors_for_backends[current[j][0]][input_name])
+                    continue
+                t = tensors_for_backends[req].get(input_name)
+                if t is not None:
+                    operator_inputs.append(t)
+                    continue
+                for other in self.backend_order:
+                    other_t = tensors_for_backends[other].get(input_name)
+                    if other_t is not None:
+                        moved = self.backend_contexts[req].move_tensor(
+                            other_t, self.tensor_move_options.get(input_name, {}))
+                        tensors_for_backends[req][input_name] = moved
+                        operator_inputs.append(moved)
+                        break
+                else:
+                    raise RuntimeError(f"Input {input_name} not found")
+            context = self.backend_contexts[operator.backend]
+            logger.debug("Running %s(%s) on %s", node.name, op_type, operator.backend)
+            outputs = operator.run(context, operator_inputs, len(node.output))
+            for j, output_name in enumerate(node.output):
+                tensors_for_backends[outputs[j].backend][output_name] = outputs[j]
+            self.node_backends.append((node.name, op_type, operator.backend))
+
+            for name in release_timing.get(node.name, []):
+                for backend in BACKENDS:
+                    t = tensors_for_backends[backend].pop(name, None)
+                    if t is not None:
+                        t.dispose()
+            if measure_performance:
+                self.node_performances.append(dict(
+                    opType=op_type, name=node.name, backend=operator.backend,
+                    inputDims=[t.dims for t in operator_inputs], outputDims=[t.dims for t in outputs],
+                    elapsed=(time.perf_counter() - t0) * 1e3))
+
+        results: List[CPUTensor] = []
+        kept = set()
+        for vi in graph.output:
+            out = tensors_for_backends["cpu"].get(vi.name)
+            if out is None and outputs_on_device:
+                for other in self.backend_order:
+                    out = tensors_for_backends[other].get(vi.name)
+                    if out is not None:
+                        kept.add(vi.name)
+                        break
+            if out is None:
+                for other in self.backend_order:
+                    other_t = tensors_for_backends[other].get(vi.name)
+                    if other_t is not None:
+                        out = self.backend_contexts["cpu"].move_tensor(other_t, {})
+                        tensors_for_backends["cpu"][vi.name] = out
+                        break
+            if out is None:
+                raise RuntimeError(f"Output {vi.name} not found")
+            results.append(out)
+
+        for backend in BACKENDS_WITHOUT_CPU:
+            for name, t in tensors_for_backends[backend].items():
+                if name in self.initializer_tensors:
+                    self.copied_initializer_tensors[backend][name] = t
+                elif name not in borrowed and name not in kept:
+                    t.dispose()
+        return results
+
+    def nodes_on(self, backend: str) -> List[tuple]:
+        return [n for n in self.node_backends if n[2] == backend]
+
+    def dispose(self) -> None:
+        for kv in self.copied_initializer_tensors.values():
+            for t in kv.values():
+                t.dispose()
+            kv.clear()
+
+
+def load(source: Union[str, bytes, Model], backend_order: Optional[Sequence[str]] = None,
+         backend_options: Optional[dict] = None, onnx_basename: str = "model.onnx") -> Runner:
+    """``WebDNN.load(directory, {backendOrder, backendOptions})`` (index.ts:42-149)."""
+    backend_order = list(backend_order) if backend_order is not None else ["cuda", "cpu"]
+    backend_options = backend_options or {}
+    cpu_context = WebDNNCPUContext()
+    _register("cpu")
+    contexts: Dict[str, object] = {"cpu": cpu_context}
+    succeeded = None
+    errors = []
+    for name in backend_order:
+        if name == "cpu":
+            succeeded = "cpu"
+            break
+        if name != "cuda":
+            errors.append(f"unknown backend {name}")
+            continue
+        try:
+            opts = backend_options.get("cuda", {})
+            ctx = opts.get("context")
+            if ctx is None:
+                ctx = WebDNNCudaContext(cpu_context, device=opts.get("device", 0),
+                                        arena_bytes=opts.get("arenaBytes", 0))
+                ctx.initialize()
+            contexts["cuda"] = ctx
+            _register("cuda")
+            succeeded = "cuda"
+            break
+        except Exception as e:  # index.ts:68-79: try the next backend
+            errors.append(f"{name}: {e}")
+            logger.warning("backend %s failed to initialise: %s", name, e)
+    if succeeded is None:
+        raise RuntimeError("No backend available: " + "; ".join(errors))
+    order = [succeeded] if succeeded == "cpu" else [succeeded, "cpu"]
+    runner = Runner(order, contexts)
+    runner.load_model(source, onnx_basename)
+    return runner

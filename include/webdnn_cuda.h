@@ -55,7 +55,7 @@ int wdc_sync(wdc_context* ctx);
 /* cudaStream_t of the context, for callers that record their own events around launches. */
 void* wdc_stream(wdc_context* ctx);
 /* out[0..n): bytes_in_use, high_water_bytes, reserved_bytes, allocs, frees, launches,
- * h2d_bytes, d2h_bytes. */
+ * h2d_bytes, d2h_bytes, tensor_core_launches (launches of the tcgen05 contraction kernel). */
 int wdc_stats(wdc_context* ctx, int64_t* out, int n);
 int wdc_reset_stats(wdc_context* ctx);
 /* Per-family device timing.  While enabled, every contraction launch (wdc_gemm / wdc_conv2d) is

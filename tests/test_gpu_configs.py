@@ -49,7 +49,7 @@ def test_config2_unfused_nodes_agree(cuda_context):
     x = zoo.make_input((2, 64, 28, 28))
     want = ref_runner.run_model(model, [x])
     got, r = run_cuda(model, [x], cuda_context, return_runner=True)
-    assert [t for _, t, _ in r.node_backends] == ["Conv", "BatchNormalization", "Relu"]
+    assert [t for _, t, _ in r.node_backends] == ["CudaConvFused", "BatchNormalization", "Relu"]  # bias folded only
     r.dispose()
     for g, w in zip(got, want):
         assert max_err_rel_linf(g, w) <= TOL

@@ -1,0 +1,114 @@
+"""GPU parity of the tcgen05 (3xTF32) implicit-GEMM kernel against the CPU oracle, through the
+runner and the C ABI.  Each case also checks that the tensor-core kernel really launched."""
+import numpy as np
+import pytest
+
+from oracle import ops, ref_runner
+
+from util import max_err_rel_linf, run_cuda, single_op_model
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-4
+
+
+def _conv_case(ctx, n, cin, cout, size, k, stride, pad, dil=1, bias=True, seed=0):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((n, cin, size[0], size[1])).astype(np.float32)
+    w = (rng.standard_normal((cout, cin, k, k)) * np.sqrt(2.0 / (cin * k * k))).astype(np.float32)
+    ins = [x, w] + ([rng.uniform(-0.1, 0.1, cout).astype(np.float32)] if bias else [])
+    attrs = dict(kernel_shape=[k, k], strides=[stride, stride], pads=[pad] * 4, dilations=[dil, dil])
+    model = single_op_model("Conv", attrs, ins, n_graph_inputs=1)
+    (want,) = ref_runner.run_model(model, [x])
+    before = ctx.stats()["tensor_core_launches"]
+    (got,) = run_cuda(model, [x], ctx)
+    assert ctx.stats()["tensor_core_launches"] > before, "tensor-core kernel did not launch"
+    assert got.shape == want.shape
+    return max_err_rel_linf(got, want)
+
+
+@pytest.mark.parametrize("n,cin,cout,size,k,stride,pad,dil", [
+    (2, 64, 64, (56, 56), 3, 1, 1, 1),      # layer1 3x3
+    (3, 64, 256, (17, 19), 1, 1, 0, 1),     # 1x1, M = 969 (tail rows), N = 2 tiles
+    (2, 128, 128, (28, 28), 3, 2, 1, 1),    # stride-2 3x3
+    (2, 256, 512, (14, 14), 1, 2, 0, 1),    # stride-2 1x1 downsample
+    (1, 512, 512, (7, 7), 3, 1, 1, 1),      # K = 4608, single partly filled M tile
+    (1, 32, 32, (9, 11), 3, 1, 2, 2),       # dilation 2, tile_n 32
+    (2, 96, 72, (12, 12), 3, 1, 1, 1),      # Cout not a multiple of 32 (masked columns)
+    (1, 64, 64, (160, 128), 1, 1, 0, 1),    # 160 M tiles: more tiles than SMs, several per CTA
+])
+def test_conv_shapes(cuda_context, n, cin, cout, size, k, stride, pad, dil):
+    assert _conv_case(cuda_context, n, cin, cout, size, k, stride, pad, dil) <= TOL
+
+
+def test_fused_epilogue_through_c_abi(cuda_context):
+    """scale/shift/residual/Relu epilogue against conv -> affine -> add -> relu on the oracle."""
+    from ctypes import byref
+    from webdnn_b200.backend import CPUTensor
+    from webdnn_b200.lib import ConvDesc
+    ctx = cuda_context
+    rng = np.random.default_rng(1)
+    n, c, h, w_, co = 2, 64, 20, 20, 128
+    x = rng.standard_normal((n, c, h, w_)).astype(np.float32)
+    wt = (rng.standard_normal((co, c, 3, 3)) * 0.06).astype(np.float32)
+    scale = rng.uniform(0.5, 1.5, co).astype(np.float32)
+    shift = rng.standard_normal(co).astype(np.float32)
+    res = rng.standard_normal((n, co, h, w_)).astype(np.float32)
+    conv = ops.conv2d(x, wt, None, (1, 1), (1, 1, 1, 1))
+    want = conv.astype(np.float64) * scale[None, :, None, None] + shift[None, :, None, None] + res
+    want = np.maximum(want, 0).astype(np.float32)
+    dx = ctx.channels_last(ctx.move_tensor(CPUTensor.from_array(x)))
+    dres = ctx.channels_last(ctx.move_tensor(CPUTensor.from_array(res)))
+    dw = ctx.move_tensor(CPUTensor.from_array(wt))
+    dwp = ctx.empty_tensor([co, 3, 3, c])
+    ctx._call("wdc_pack_conv_weight", dw.ptr, dwp.ptr, co, c, 3, 3)
+    dsc, dsh = ctx.move_tensor(CPUTensor.from_array(scale)), ctx.move_tensor(CPUTensor.from_array(shift))
+    y = ctx.empty_tensor([n, co, h, w_], layout="nhwc")
+    d = ConvDesc(batch=n, ch_in=c, in_h=h, in_w=w_, ch_out=co, k_h=3, k_w=3, out_h=h, out_w=w_, stride_h=1,
+                 stride_w=1, pad_t=1, pad_l=1, dil_h=1, dil_w=1, group=1, relu=1)
+    before = ctx.stats()["tensor_core_launches"]
+    ctx.conv2d(d, dx, dwp, dsc, dsh, dres, y)
+    got = y.get_data().reshape(n, co, h, w_)
+    assert ctx.stats()["tensor_core_launches"] == before + 1
+    assert max_err_rel_linf(got, want) <= TOL
+    for t in (dx, dres, dw, dwp, dsc, dsh, y):
+        t.dispose()
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 512, 784), (64, 10, 512), (256, 1000, 2048), (8192, 2048, 256), (33, 40, 36)])
+def test_gemm_transb_on_tensor_cores(cuda_context, m, n, k):
+    rng = np.random.default_rng(2)
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = (rng.standard_normal((n, k)) * np.sqrt(2.0 / k)).astype(np.float32)
+    c = rng.uniform(-0.1, 0.1, n).astype(np.float32)
+    model = single_op_model("Gemm", {"transB": 1, "alpha": 0.75, "beta": 1.5}, [a, b, c])
+    (want,) = ref_runner.run_model(model, [a, b, c])
+    before = cuda_context.stats()["tensor_core_launches"]
+    (got,) = run_cuda(model, [a, b, c], cuda_context)
+    assert cuda_context.stats()["tensor_core_launches"] > before
+    assert max_err_rel_linf(got, want) <= TOL
+
+
+def test_split_precision_is_fp32_class(cuda_context):
+    """Values chosen so that a single-pass TF32 product (10-bit mantissa) would be off by ~1e-3:
+    the 3xTF32 result must stay within a few fp32 ulps of the double-accumulated oracle."""
+    rng = np.random.default_rng(3)
+    m, n, k = 128, 64, 512
+    a = (1.0 + rng.uniform(0, 1, (m, k)) * 2.0 ** -9).astype(np.float32)   # low-order mantissa bits matter
+    b = (1.0 + rng.uniform(0, 1, (n, k)) * 2.0 ** -9).astype(np.float32)
+    model = single_op_model("Gemm", {"transB": 1}, [a, b])
+    (want,) = ref_runner.run_model(model, [a, b])
+    (got,) = run_cuda(model, [a, b], cuda_context)
+    assert max_err_rel_linf(got, want) <= 2e-6
+
+
+def test_weight_split_cache_follows_buffer_lifetime(cuda_context):
+    """The cached hi/lo split of a weight buffer must not outlive the buffer: a new tensor that lands
+    on the same address with other values has to give the new result."""
+    rng = np.random.default_rng(4)
+    a = rng.standard_normal((64, 64)).astype(np.float32)
+    for seed in (10, 11, 12):
+        b = np.random.default_rng(seed).standard_normal((32, 64)).astype(np.float32)
+        model = single_op_model("Gemm", {"transB": 1}, [a, b])
+        (want,) = ref_runner.run_model(model, [a, b])
+        (got,) = run_cuda(model, [a, b], cuda_context)
+        assert max_err_rel_linf(got, want) <= TOL

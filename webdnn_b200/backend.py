@@ -73,7 +73,9 @@ class CPUTensor(TensorImpl):
 
     @classmethod
     def from_array(cls, arr: np.ndarray) -> "CPUTensor":
-        arr = np.ascontiguousarray(arr)
+        arr = np.asarray(arr)
+        if not arr.flags.c_contiguous:
+            arr = arr.copy(order="C")  # (np.ascontiguousarray would turn a 0-d array into 1-d)
         dt = {np.dtype(np.float32): "float32", np.dtype(np.int32): "int32", np.dtype(np.uint8): "bool"}[arr.dtype]
         return cls(arr.shape, dt, arr.reshape(-1))
 
@@ -255,10 +257,10 @@ class WebDNNCudaContext:
         return self._L.lib.wdc_stream(self.handle)
 
     def stats(self) -> Dict[str, int]:
-        out = (ctypes.c_int64 * 8)()
-        self._call("wdc_stats", out, 8)
+        out = (ctypes.c_int64 * 9)()
+        self._call("wdc_stats", out, 9)
         keys = ["bytes_in_use", "high_water_bytes", "reserved_bytes", "allocs", "frees", "launches",
-                "h2d_bytes", "d2h_bytes"]
+                "h2d_bytes", "d2h_bytes", "tensor_core_launches"]
         return dict(zip(keys, list(out)))
 
     def reset_stats(self) -> None:

@@ -37,7 +37,7 @@ struct wdc_context {
   wdc_arena arena;
   std::string last_error;
   std::mutex mu;
-  int64_t n_alloc = 0, n_free = 0, n_launch = 0, h2d_bytes = 0, d2h_bytes = 0;
+  int64_t n_alloc = 0, n_free = 0, n_launch = 0, h2d_bytes = 0, d2h_bytes = 0, n_tc_launch = 0;
   int sm_count = 0;
   int* status_word = nullptr;       // device word set by kernels whose bounded waits expire
   int* status_word_host = nullptr;  // pinned mirror
@@ -116,3 +116,5 @@ int wdc_tc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, cons
 int wdc_tc_gemm(wdc_context* ctx, const wdc_gemm_desc* d, const float* A, const float* B,
                 const float* C, float* Y);
 void wdc_tc_destroy(wdc_context* ctx);
+// Drops the cached hi/lo split of a weight matrix when its buffer is freed or overwritten.
+void wdc_tc_evict(wdc_context* ctx, const void* ptr);

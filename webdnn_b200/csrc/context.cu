@@ -168,6 +168,7 @@ extern "C" int wdc_alloc(wdc_context* ctx, int64_t bytes, void** dptr) {
 extern "C" int wdc_free(wdc_context* ctx, void* dptr) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_free: null context");
   if (!dptr) return WDC_OK;
+  wdc_tc_evict(ctx, dptr);
   std::lock_guard<std::mutex> lk(ctx->mu);
   wdc_arena& a = ctx->arena;
   auto lit = a.live.find(dptr);
@@ -224,6 +225,7 @@ extern "C" int wdc_upload(wdc_context* ctx, void* dst, const void* host, int64_t
     return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_upload: bad argument");
   if (bytes == 0) return WDC_OK;
   DeviceGuard g(ctx->device);
+  wdc_tc_evict(ctx, dst);
   WDC_CUDA(ctx, cudaMemcpyAsync(dst, host, (size_t)bytes, cudaMemcpyHostToDevice, ctx->stream));
   ctx->h2d_bytes += bytes;
   return WDC_OK;
@@ -265,6 +267,7 @@ extern "C" int wdc_copy(wdc_context* ctx, void* dst, const void* src, int64_t by
     return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_copy: bad argument");
   if (bytes == 0) return WDC_OK;
   DeviceGuard g(ctx->device);
+  wdc_tc_evict(ctx, dst);
   WDC_CUDA(ctx, cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToDevice, ctx->stream));
   return WDC_OK;
 }
@@ -288,15 +291,16 @@ extern "C" void* wdc_stream(wdc_context* ctx) { return ctx ? (void*)ctx->stream 
 
 extern "C" int wdc_stats(wdc_context* ctx, int64_t* out, int n) {
   if (!ctx || !out || n < 0) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_stats: bad argument");
-  int64_t v[8] = {ctx->arena.in_use, ctx->arena.high_water, ctx->arena.reserved, ctx->n_alloc,
-                  ctx->n_free,       ctx->n_launch,         ctx->h2d_bytes,      ctx->d2h_bytes};
-  for (int i = 0; i < n && i < 8; i++) out[i] = v[i];
+  int64_t v[9] = {ctx->arena.in_use, ctx->arena.high_water, ctx->arena.reserved, ctx->n_alloc,
+                  ctx->n_free,       ctx->n_launch,         ctx->h2d_bytes,      ctx->d2h_bytes,
+                  ctx->n_tc_launch};
+  for (int i = 0; i < n && i < 9; i++) out[i] = v[i];
   return WDC_OK;
 }
 
 extern "C" int wdc_reset_stats(wdc_context* ctx) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_reset_stats: null context");
-  ctx->n_alloc = ctx->n_free = ctx->n_launch = ctx->h2d_bytes = ctx->d2h_bytes = 0;
+  ctx->n_alloc = ctx->n_free = ctx->n_launch = ctx->h2d_bytes = ctx->d2h_bytes = ctx->n_tc_launch = 0;
   ctx->arena.high_water = ctx->arena.in_use;
   return WDC_OK;
 }

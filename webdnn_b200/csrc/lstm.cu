@@ -73,7 +73,7 @@ extern "C" int wdc_lstm(wdc_context* ctx, const float* X, const float* W, const 
     d.sa0 = H; d.sa1 = 1; d.sb0 = 1; d.sb1 = H;  // B = R^T
     d.sc0 = 4 * H; d.sc1 = 1;
     d.alpha = 1.f; d.beta = 1.f;
-    s = wdc_simt_gemm(ctx, &d, Yh, R, P + t * Bt * 4 * H, G);
+    s = wdc_gemm(ctx, &d, Yh, R, P + t * Bt * 4 * H, G);
     if (s != WDC_OK) break;
     lstm_gate_kernel<<<grid_for(ctx, Bt * H, 256, 4), 256, 0, ctx->stream>>>(G, bias, Yc, Yh,
                                                                             Y + t * Bt * H, Bt, H);

@@ -182,9 +182,23 @@ __device__ __forceinline__ int32_t binary_i32(int op, int32_t l, int32_t r) {
     case WDC_B_MUL: return to_int32((double)l * (double)r);  // double product, not a wrapping mul
     case WDC_B_DIV: return to_int32((double)l / (double)r);
     case WDC_B_POW: {
-      double a = l, b = r;
-      if ((a == 1.0 || a == -1.0) && isinf(b)) return 0;
-      return to_int32(pow(a, b));
+      // Integer powers by repeated squaring in double: exact (hence identical to a correctly
+      // rounded pow) while the result stays below 2^53; the library pow() may be an ulp off an
+      // exact integer, which truncation would turn into a wrong int.
+      double a = l;
+      if (r < 0) {
+        if (l == 1) return 1;
+        if (l == -1) return (r & 1) ? -1 : 1;
+        return 0;  // 1 / a^|r| truncates to 0 (and 1/0 = Infinity stores as 0)
+      }
+      double acc = 1.0;
+      unsigned e = (unsigned)r;
+      while (e) {
+        if (e & 1) acc *= a;
+        a *= a;
+        e >>= 1;
+      }
+      return to_int32(acc);
     }
     case WDC_B_MAX: return l > r ? l : r;
     default: return l < r ? l : r;

@@ -49,13 +49,23 @@ def instantiate_operator(op_type: str, opset: int, backend_order: Sequence[str],
                 local_order = [backend]
     elif op_type == "Shape":
         local_order = ["cpu"]
-    for backend in local_order:
-        for e in entries:
-            if e.backend != backend:
-                continue
-            if e.opset_min > opset:
-                continue
-            if e.opset_max is not None and e.opset_max <= opset:
-                continue
-            return e.factory()
-    return None
+    def pick(order):
+        for backend in order:
+            for e in entries:
+                if e.backend != backend:
+                    continue
+                if e.opset_min > opset:
+                    continue
+                if e.opset_max is not None and e.opset_max <= opset:
+                    continue
+                return e.factory()
+        return None
+
+    op = pick(local_order)
+    if op is None and local_order != list(backend_order):
+        # The reference gets here with null, throws, and reruns the node on its cpu backend
+        # (runnerImpl.ts:511-520).  This backend has no cpu kernels to fall back to, so a shape-like
+        # node whose data sits on the cpu (a graph input) is given to the regular backend order and
+        # its input is moved to the device.
+        op = pick(backend_order)
+    return op

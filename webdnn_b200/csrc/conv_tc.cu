@@ -7,21 +7,41 @@
 // hi = tf32(x), lo = tf32(x - hi); the product is accumulated as A_lo*W_hi + A_hi*W_lo + A_hi*W_hi
 // in fp32 TMEM accumulators (the lo*lo term, ~2^-22 relative, is dropped).
 //
-// One persistent CTA per SM, warp specialised:
-//   warps 0-7   A producers: gather the im2col tile from global memory (128-bit loads, zero fill for
-//               padding), split into hi/lo in registers and store both into 128B-swizzled shared
-//               memory tiles (generic-proxy stores + fence.proxy.async).
-//   warp  8     W producer: one lane issues two TMA tile loads per stage (pre-split W_hi, W_lo).
-//   warp  9     MMA issuer: one lane issues tcgen05.mma.kind::tf32 (M=128, N=tile, K=8), 12 per
-//               32-wide K block; tcgen05.commit releases the stage / publishes the accumulator.
-//   warps 10-13 epilogue: tcgen05.ld the accumulator (double buffered in TMEM so the next tile's
-//               main loop overlaps), apply scale/shift (bias, folded BatchNormalization), residual
-//               add, Relu, and store NHWC with 128-bit stores.
+// The tensor core's fp32 accumulator truncates when it aligns addends, which biases long sums
+// toward zero (measured ~0.15 ulp of the running sum per MMA).  To keep fp32-class accuracy through
+// 50+ layers the accumulation has two levels: TMEM holds the partial sum of one SEGMENT of 4 K blocks
+// (K = 128), and the epilogue warps add each finished segment into fp32 registers with
+// round-to-nearest while the next segment runs into the other TMEM buffer.
+//
+// Shared memory bandwidth (128 B/clk) is the scarce resource of a 3xTF32 kernel: with both operands
+// in shared memory a 128x128x8 MMA reads 8 KB per 64 clocks, which alone saturates it.  So the A
+// operand (activations, gathered and split by ordinary threads anyway) lives in TENSOR MEMORY: the
+// producer threads write A_hi / A_lo with tcgen05.st and the MMA takes A from TMEM, W from shared
+// memory.  Shared memory then carries only the weight tiles (TMA in, MMA out).
+//
+// One persistent CTA per SM, warp specialised, 16 warps (4 per SM sub-partition, so that every
+// thread can have 128 registers):
+//   warps 0-3   A producers: thread (w, l) owns row 32w+l of the 128-row tile (= TMEM lane).  Per K
+//               block it gathers the row's 32 values from global memory (8 x 128-bit loads, zero fill
+//               for padding, loads running 2 K blocks ahead and crossing tile boundaries), splits them
+//               into hi/lo and writes 32+32 TMEM columns of the stage with tcgen05.st.
+//   warp  4     W producer: one lane issues two TMA tile loads per stage (pre-split W_hi, W_lo,
+//               128B-swizzled).
+//   warp  5     MMA issuer: one lane issues tcgen05.mma.kind::tf32 (M=128, N=tile, K=8, A from TMEM),
+//               12 per 32-wide K block; tcgen05.commit releases the stage / publishes the segment.
+//   warps 8-15  accumulate + epilogue: each warp owns one TMEM lane quadrant and half of the tile's
+//               columns; per segment tcgen05.ld + add into registers; at the end of a tile the
+//               accumulators are transposed through shared memory so that scale/shift (bias, folded
+//               BatchNormalization), residual add, Relu and the NHWC store touch 8 rows x 64
+//               contiguous bytes per warp instruction.
+// TMEM columns: [0,256) two segment accumulators of up to 128 columns, [256,512) four A stages of
+// 32 (hi) + 32 (lo) columns.
 // Every mbarrier wait is bounded in wall time; on expiry the kernel records an error code in the
 // context's status word, raises a CTA-wide abort flag so the other roles stop too, frees its TMEM
 // and returns.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <map>
 
 #include "common.cuh"
@@ -29,14 +49,19 @@
 namespace {
 
 constexpr int TILE_M = 128;
-constexpr int BLOCK_K = 32;           // fp32 elements per K block = one 128-byte swizzle row
-constexpr int STAGES = 3;
-constexpr int NUM_A_WARPS = 8;
-constexpr int TMA_WARP = 8;
-constexpr int MMA_WARP = 9;
-constexpr int NUM_THREADS = 14 * 32;
-constexpr int A_TILE_BYTES = TILE_M * BLOCK_K * 4;  // 16 KB
-constexpr int PREFETCH = 3;                          // K blocks of A held in registers per thread
+constexpr int BLOCK_K = 32;           // fp32 elements per K block = one 128-byte swizzle row of W
+constexpr int STAGES = 4;
+constexpr int NUM_A_WARPS = 4;
+constexpr int TMA_WARP = 4;
+constexpr int MMA_WARP = 5;
+constexpr int EPI_WARP0 = 8;
+constexpr int NUM_EPI_WARPS = 8;
+constexpr int NUM_THREADS = 16 * 32;
+constexpr int SEG_KBLOCKS = 4;        // K blocks accumulated in TMEM before the partial sum is drained
+constexpr int NBUF = 2;               // TMEM segment accumulators of 128 columns
+constexpr int TMEM_A_COL0 = NBUF * 128;  // first column of the A stages
+constexpr int W_TILE_BYTES = 128 * BLOCK_K * 4;  // 16 KB (hi) + 16 KB (lo) per stage
+constexpr int PREFETCH = 2;           // K blocks of A held in registers per thread
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 struct TcProblem {
@@ -49,6 +74,7 @@ struct TcProblem {
   int kblocks;        // ceil(K / 32)
   int cblocks;        // K blocks per filter tap = ceil(ch_in / 32)
   int tile_n;         // 32, 64 or 128
+  int c4;             // 1: input has 4 channels per pixel, one K block per filter row, chunk j = tap kx
   int64_t tiles_m, tiles_n;
   // epilogue
   const float* scale;     // per channel or null
@@ -57,19 +83,19 @@ struct TcProblem {
   int64_t res_stride;
   float alpha, shift_mul, res_mul;
   int relu;
+  int dbg;  // development switches (WDC_TC_DEBUG): 1 = no A loads, 2 = no epilogue memory traffic, 4 = no MMAs
   int* status;
 };
 
 struct __align__(1024) SharedStorage {
-  // tiles first: each must start on a 1024-byte boundary for the 128B swizzle
-  unsigned char a_hi[STAGES][A_TILE_BYTES];
-  unsigned char a_lo[STAGES][A_TILE_BYTES];
-  unsigned char w_hi[STAGES][128 * BLOCK_K * 4];
-  unsigned char w_lo[STAGES][128 * BLOCK_K * 4];
+  // weight tiles first: each must start on a 1024-byte boundary for the 128B swizzle
+  unsigned char w_hi[STAGES][W_TILE_BYTES];
+  unsigned char w_lo[STAGES][W_TILE_BYTES];
+  float epi_stage[NUM_EPI_WARPS][32][20];  // per-warp transpose buffer: 32 rows x 16 columns (+4 pad)
   unsigned long long full_bar[STAGES];
   unsigned long long empty_bar[STAGES];
-  unsigned long long tmem_full_bar[2];
-  unsigned long long tmem_empty_bar[2];
+  unsigned long long seg_full_bar[NBUF];
+  unsigned long long seg_empty_bar[NBUF];
   unsigned int tmem_base;
   volatile int abort_flag;
 };
@@ -159,14 +185,15 @@ __device__ __forceinline__ uint32_t make_idesc(int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
 }
 
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_c, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_c, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
       :
-      : "r"(tmem_c), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "r"(tmem_c), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
@@ -181,17 +208,24 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "r"(smem_u32(smem_dst)), "l"((unsigned long long)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   uint32_t* r = reinterpret_cast<uint32_t*>(v);
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
+  const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      :
+      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 
@@ -209,86 +243,107 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       mbar_init(&ss->full_bar[s], NUM_A_WARPS + 1);
       mbar_init(&ss->empty_bar[s], 1);
     }
-    for (int b = 0; b < 2; b++) {
-      mbar_init(&ss->tmem_full_bar[b], 1);
-      mbar_init(&ss->tmem_empty_bar[b], 4);
+    for (int b = 0; b < NBUF; b++) {
+      mbar_init(&ss->seg_full_bar[b], 1);
+      mbar_init(&ss->seg_empty_bar[b], NUM_EPI_WARPS);
     }
     ss->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == MMA_WARP) {
-    // 256 columns: two accumulators of up to 128 fp32 columns each
+    // all 512 columns: NBUF segment accumulators + STAGES x (A_hi, A_lo)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ss->tmem_base)),
-                 "r"(256));
+                 "r"(512));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = ss->tmem_base;
+  // Each CTA walks the K blocks from a different starting point so that the CTAs, which all need the
+  // same weight tiles, do not ask the same L2 lines at the same moment.
+  const int rot = (int)(((int64_t)blockIdx.x * p.kblocks) / gridDim.x);
 
   if (warp < NUM_A_WARPS) {
     // ===================================================================== A producers
     // Work items are (tile, K block) pairs in the order the MMA warp consumes them.  Loads run
-    // PREFETCH items ahead of the shared-memory stores and cross tile boundaries, so the global
-    // load latency is paid once per CTA, not once per tile.
-    const int t = threadIdx.x;        // 0..255
-    const int chunk = t & 7;          // 16-byte chunk of the 128-byte row
-    const int rgrp = t >> 3;          // rows rgrp, rgrp+32, rgrp+64, rgrp+96
+    // PREFETCH items ahead of the TMEM stores and cross tile boundaries, so the global load latency
+    // is paid once per CTA, not once per tile.
+    const int row = threadIdx.x;      // 0..127: tile row and TMEM lane of this thread
     const int64_t my_tiles = (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
     const int64_t items = my_tiles * p.kblocks;
-    const int64_t hw = (int64_t)p.out_h * p.out_w;
+    const uint32_t hw = (uint32_t)p.out_h * (uint32_t)p.out_w;
+    const int64_t img_elems = (int64_t)p.in_h * p.in_w * p.ch_in;
     // load-side cursor
-    int64_t ld_tile_i = -1;           // index into this CTA's tile sequence whose rows are cached
-    long long rbase[4];
-    int riy[4], rix[4];
+    int64_t ld_tile_i = -1;           // index into this CTA's tile sequence whose row is cached
+    const float* rptr = nullptr;      // pixel (n, 0, 0, channel 0) of this thread's row, null past M
+    int riy = 0, rix = 0;
     int ld_kb = 0;
     int64_t ld_tile_seq = 0;
     auto issue = [&](float4* dst) {
       if (ld_tile_seq != ld_tile_i) {
         ld_tile_i = ld_tile_seq;
         const int64_t tile = blockIdx.x + ld_tile_seq * gridDim.x;
-        const int64_t m0 = (tile / p.tiles_n) * TILE_M;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-          const int64_t m = m0 + rgrp + 32 * i;
-          if (m < p.M) {
-            const int64_t n = m / hw;
-            const int rem = (int)(m - n * hw);
-            const int oy = rem / p.out_w, ox = rem - oy * p.out_w;
-            rbase[i] = n * (int64_t)p.in_h * p.in_w * p.ch_in;
-            riy[i] = oy * p.stride_h - p.pad_t;
-            rix[i] = ox * p.stride_w - p.pad_l;
+        const int64_t m = (tile / p.tiles_n) * TILE_M + row;
+        if (m < p.M) {
+          uint32_t n, rem;
+          if (p.M <= 0x7fffffffll) {  // 32-bit division is several times cheaper
+            n = (uint32_t)m / hw;
+            rem = (uint32_t)m - n * hw;
           } else {
-            rbase[i] = -1;
-            riy[i] = rix[i] = 0;
+            n = (uint32_t)(m / hw);
+            rem = (uint32_t)(m - (int64_t)n * hw);
           }
+          const int oy = (int)(rem / (uint32_t)p.out_w), ox = (int)rem - oy * p.out_w;
+          rptr = x + (int64_t)n * img_elems;
+          riy = oy * p.stride_h - p.pad_t;
+          rix = ox * p.stride_w - p.pad_l;
+        } else {
+          rptr = nullptr;
         }
       }
-      const int tap = ld_kb / p.cblocks;
-      const int c0 = (ld_kb - tap * p.cblocks) * BLOCK_K + chunk * 4;
-      const int ky = tap / p.k_w, kx = tap - ky * p.k_w;
-      const bool cok = c0 < p.ch_in;
+      int kb = ld_kb + rot;
+      if (kb >= p.kblocks) kb -= p.kblocks;
+      if (p.c4) {
+        // one K block = one filter row: chunk j is tap kx = j (4 channels of one pixel)
+        const int iy = riy + kb * p.dil_h;
+        const bool rok = !(p.dbg & 1) && rptr != nullptr && (unsigned)iy < (unsigned)p.in_h;
 #pragma unroll
-      for (int i = 0; i < 4; i++) {
-        const int iy = riy[i] + ky * p.dil_h, ix = rix[i] + kx * p.dil_w;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (cok && rbase[i] >= 0 && (unsigned)iy < (unsigned)p.in_h && (unsigned)ix < (unsigned)p.in_w)
-          v = __ldg(reinterpret_cast<const float4*>(x + rbase[i] + ((long long)iy * p.in_w + ix) * p.ch_in + c0));
-        dst[i] = v;
+        for (int j = 0; j < 8; j++) {
+          const int ix = rix + j * p.dil_w;
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (rok && j < p.k_w && (unsigned)ix < (unsigned)p.in_w)
+            v = __ldg(reinterpret_cast<const float4*>(rptr + (iy * p.in_w + ix) * 4));
+          dst[j] = v;
+        }
+      } else {
+        const int tap = kb / p.cblocks;
+        const int c0 = (kb - tap * p.cblocks) * BLOCK_K;
+        const int ky = tap / p.k_w, kx = tap - ky * p.k_w;
+        const int iy = riy + ky * p.dil_h, ix = rix + kx * p.dil_w;
+        const bool rok = !(p.dbg & 1) && rptr != nullptr && (unsigned)iy < (unsigned)p.in_h &&
+                         (unsigned)ix < (unsigned)p.in_w;
+        const float* src = rptr + ((iy * p.in_w + ix) * p.ch_in + c0);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (rok && c0 + j * 4 < p.ch_in) v = __ldg(reinterpret_cast<const float4*>(src + j * 4));
+          dst[j] = v;
+        }
       }
       if (++ld_kb == p.kblocks) {
         ld_kb = 0;
         ld_tile_seq++;
       }
     };
-    float4 ring[PREFETCH][4];
+    float4 ring[PREFETCH][8];
 #pragma unroll
     for (int j = 0; j < PREFETCH; j++)
       if (j < items) issue(ring[j]);
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)TMEM_A_COL0;
     for (int64_t g0 = 0; g0 < items; g0 += PREFETCH) {
 #pragma unroll
       for (int j = 0; j < PREFETCH; j++) {
@@ -296,20 +351,33 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         if (ok && g < items) {
           ok = mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 12);
           if (ok) {
-            unsigned char* ahi = ss->a_hi[stage];
-            unsigned char* alo = ss->a_lo[stage];
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_hi = lane_base + (uint32_t)(stage * 64);
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-              const int r = rgrp + 32 * i;
-              const float4 v = ring[j][i];
-              float4 h, l;
-              h.x = to_tf32(v.x); h.y = to_tf32(v.y); h.z = to_tf32(v.z); h.w = to_tf32(v.w);
-              l.x = to_tf32(v.x - h.x); l.y = to_tf32(v.y - h.y); l.z = to_tf32(v.z - h.z); l.w = to_tf32(v.w - h.w);
-              const int off = r * 128 + ((chunk ^ (r & 7)) << 4);
-              *reinterpret_cast<float4*>(ahi + off) = h;
-              *reinterpret_cast<float4*>(alo + off) = l;
+            for (int h = 0; h < 2; h++) {
+              float hi[16], lo[16];
+#pragma unroll
+              for (int c = 0; c < 4; c++) {
+                const float4 v = ring[j][h * 4 + c];
+                const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int t = 0; t < 4; t++) {
+                  if (p.dbg & 8) { hi[c * 4 + t] = e[t]; lo[c * 4 + t] = 0.f; continue; }
+                  // hi = e rounded to TF32 (add half an ulp of the 10-bit mantissa, clear the low 13
+                  // bits): two full-rate integer ops instead of a quarter-rate cvt.  lo = e - hi is
+                  // exact in fp32; the tensor core ignores the low 13 bits of a tf32 operand, which
+                  // costs lo at most 2^-10 of its own size (2^-21 of e).
+                  const float hh = __uint_as_float((__float_as_uint(e[t]) + 0x1000u) & 0xffffe000u);
+                  hi[c * 4 + t] = hh;
+                  lo[c * 4 + t] = e[t] - hh;
+                }
+              }
+              if (p.dbg & 16) continue;
+              tmem_st16(a_hi + (uint32_t)(h * 16), hi);
+              tmem_st16(a_hi + 32u + (uint32_t)(h * 16), lo);
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&ss->full_bar[stage]);
             if (g + PREFETCH < items) issue(ring[j]);
@@ -330,8 +398,10 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         for (int kb = 0; kb < p.kblocks; kb++) {
           if (!mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 21)) { ok = false; break; }
           mbar_arrive_expect_tx(&ss->full_bar[stage], bytes);
-          tma_load_2d(ss->w_hi[stage], &map_w_hi, &ss->full_bar[stage], kb * BLOCK_K, n0);
-          tma_load_2d(ss->w_lo[stage], &map_w_lo, &ss->full_bar[stage], kb * BLOCK_K, n0);
+          int kr = kb + rot;
+          if (kr >= p.kblocks) kr -= p.kblocks;
+          tma_load_2d(ss->w_hi[stage], &map_w_hi, &ss->full_bar[stage], kr * BLOCK_K, n0);
+          tma_load_2d(ss->w_lo[stage], &map_w_lo, &ss->full_bar[stage], kr * BLOCK_K, n0);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -342,94 +412,168 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       int stage = 0;
       uint32_t phase = 0;
       const uint32_t idesc = make_idesc(p.tile_n);
-      int64_t it = 0;
+      int64_t seg = 0;  // segments issued by this CTA so far
       bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, it++) {
-        const int acc = (int)(it & 1);
-        const uint32_t acc_phase = (uint32_t)((it >> 1) & 1);
-        if (!mbar_wait(&ss->tmem_empty_bar[acc], acc_phase ^ 1, ss, p.status, 31)) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 128);
+      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        uint32_t d_tmem = 0;
+        int buf = 0;
         for (int kb = 0; kb < p.kblocks; kb++) {
+          const int in_seg = kb % SEG_KBLOCKS;
+          if (in_seg == 0) {
+            buf = (int)(seg % NBUF);
+            if (!mbar_wait(&ss->seg_empty_bar[buf], (uint32_t)((seg / NBUF) & 1) ^ 1, ss, p.status, 31)) { ok = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            d_tmem = tmem_base + (uint32_t)(buf * 128);
+          }
           if (!mbar_wait(&ss->full_bar[stage], phase, ss, p.status, 32)) { ok = false; break; }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint64_t da_hi = make_smem_desc(smem_u32(ss->a_hi[stage]));
-          const uint64_t da_lo = make_smem_desc(smem_u32(ss->a_lo[stage]));
+          const uint32_t a_hi = tmem_base + (uint32_t)(TMEM_A_COL0 + stage * 64);
+          const uint32_t a_lo = a_hi + 32u;
           const uint64_t dw_hi = make_smem_desc(smem_u32(ss->w_hi[stage]));
           const uint64_t dw_lo = make_smem_desc(smem_u32(ss->w_lo[stage]));
 #pragma unroll
           for (int k = 0; k < BLOCK_K / 8; k++) {
-            const uint64_t adv = (uint64_t)(k * 2);  // 8 tf32 = 32 bytes = 2 x 16-byte units
-            umma_tf32(d_tmem, da_lo + adv, dw_hi + adv, idesc, (kb | k) ? 1u : 0u);
-            umma_tf32(d_tmem, da_hi + adv, dw_lo + adv, idesc, 1u);
-            umma_tf32(d_tmem, da_hi + adv, dw_hi + adv, idesc, 1u);
+            const uint64_t adv = (uint64_t)(k * 2);  // 8 tf32 = 32 bytes = 2 x 16-byte units of W
+            const uint32_t acol = (uint32_t)(k * 8); // 8 TMEM columns of A
+            if (p.dbg & 4) continue;
+            umma_tf32_ts(d_tmem, a_lo + acol, dw_hi + adv, idesc, (in_seg | k) ? 1u : 0u);
+            umma_tf32_ts(d_tmem, a_hi + acol, dw_lo + adv, idesc, 1u);
+            umma_tf32_ts(d_tmem, a_hi + acol, dw_hi + adv, idesc, 1u);
           }
           umma_commit(&ss->empty_bar[stage]);  // stage reusable once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
-        }
-        if (ok) umma_commit(&ss->tmem_full_bar[acc]);
-      }
-    }
-  } else {
-    // ===================================================================== epilogue warps
-    const int q = warp & 3;             // TMEM lane quadrant this warp may read
-    const int row = q * 32 + lane;      // accumulator row (= TMEM lane) of this thread
-    int64_t it = 0;
-    bool ok = true;
-    for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, it++) {
-      const int buf = (int)(it & 1);
-      const uint32_t bphase = (uint32_t)((it >> 1) & 1);
-      const int64_t m0 = (tile / p.tiles_n) * TILE_M;
-      const int n0 = (int)(tile % p.tiles_n) * p.tile_n;
-      const int64_t m = m0 + row;
-      if (!mbar_wait(&ss->tmem_full_bar[buf], bphase, ss, p.status, 42)) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      for (int c0 = 0; c0 < p.tile_n; c0 += 32) {
-        float v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 128 + c0), v);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (m < p.M) {
-          const int nbase = n0 + c0;
-          float* yrow = y + m * (int64_t)p.N + nbase;
-          const float* rrow = p.residual ? p.residual + m * p.res_stride + nbase : nullptr;
-          if (nbase + 32 <= p.N && (p.N & 3) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float o[4];
-#pragma unroll
-              for (int e = 0; e < 4; e++) {
-                const int c = nbase + j + e;
-                float a = v[j + e] * (p.scale ? __ldg(p.scale + c) : p.alpha);
-                if (p.shift) a = fmaf(p.shift_mul, __ldg(p.shift + c), a);
-                o[e] = a;
-              }
-              if (rrow) {
-                const float4 r4 = __ldg(reinterpret_cast<const float4*>(rrow + j));
-                o[0] = fmaf(p.res_mul, r4.x, o[0]); o[1] = fmaf(p.res_mul, r4.y, o[1]);
-                o[2] = fmaf(p.res_mul, r4.z, o[2]); o[3] = fmaf(p.res_mul, r4.w, o[3]);
-              }
-              if (p.relu) {
-#pragma unroll
-                for (int e = 0; e < 4; e++) o[e] = o[e] > 0.f ? o[e] : (o[e] == o[e] ? 0.f : o[e]);
-              }
-              *reinterpret_cast<float4*>(yrow + j) = make_float4(o[0], o[1], o[2], o[3]);
-            }
-          } else {
-            for (int j = 0; j < 32; j++) {
-              const int c = nbase + j;
-              if (c >= p.N) break;
-              float a = v[j] * (p.scale ? __ldg(p.scale + c) : p.alpha);
-              if (p.shift) a = fmaf(p.shift_mul, __ldg(p.shift + c), a);
-              if (rrow) a = fmaf(p.res_mul, __ldg(rrow + j), a);
-              if (p.relu) a = a > 0.f ? a : (a == a ? 0.f : a);
-              yrow[j] = a;
-            }
+          if (in_seg == SEG_KBLOCKS - 1 || kb == p.kblocks - 1) {
+            umma_commit(&ss->seg_full_bar[buf]);  // partial sum of this segment is complete
+            seg++;
           }
         }
       }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ss->tmem_empty_bar[buf]);
+    }
+  } else if (warp >= EPI_WARP0) {
+    // ===================================================================== accumulate + epilogue warps
+    const int ew = warp - EPI_WARP0;
+    const int q = warp & 3;                       // TMEM lane quadrant this warp may read
+    const int half = ew >> 2;                     // which half of the tile's columns
+    const int ncols = p.tile_n >> 1;              // 16, 32 or 64 columns per warp
+    const int col0 = half * ncols;
+    const int nchunks = ncols >> 4;
+    const int nseg = (p.kblocks + SEG_KBLOCKS - 1) / SEG_KBLOCKS;
+    float (*stg)[20] = ss->epi_stage[ew];
+    // After the transpose through shared memory a lane owns 4 consecutive columns of 4 rows, so that a
+    // warp-wide access touches 8 rows x 64 contiguous bytes instead of 32 rows x 16 bytes.
+    const int tr = lane >> 2;                     // rows tr, tr+8, tr+16, tr+24 of the warp's 32
+    const int tc = (lane & 3) * 4;                // first of this lane's 4 columns inside a 16-column chunk
+    const bool vec = (p.N & 3) == 0;
+    int64_t seg = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int64_t mrow0 = (tile / p.tiles_n) * TILE_M + q * 32;   // first row of this warp
+      const int nbase = (int)(tile % p.tiles_n) * p.tile_n + col0;
+      float acc[64];
+#pragma unroll
+      for (int j = 0; j < 64; j++) acc[j] = 0.f;
+      float4 rcur[4];
+      auto load_res = [&](int c, float4* dst) {
+        const int col = nbase + c * 16 + tc;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          const int64_t m = mrow0 + tr + 8 * i;
+          float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (p.residual && !(p.dbg & 2) && m < p.M && col < p.N) {
+            const float* rp = p.residual + m * p.res_stride + col;
+            if (vec) r = __ldg(reinterpret_cast<const float4*>(rp));
+            else {
+              r.x = __ldg(rp);
+              if (col + 1 < p.N) r.y = __ldg(rp + 1);
+              if (col + 2 < p.N) r.z = __ldg(rp + 2);
+              if (col + 3 < p.N) r.w = __ldg(rp + 3);
+            }
+          }
+          dst[i] = r;
+        }
+      };
+      for (int s = 0; s < nseg && ok; s++, seg++) {
+        const int buf = (int)(seg % NBUF);
+        if (s == nseg - 1) {
+          load_res(0, rcur);  // in flight while the last segment finishes
+          if (p.residual && !(p.dbg & 2)) {  // pull the rest of the residual tile towards L2
+            for (int c = 1; c < nchunks; c++) {
+              const int col = nbase + c * 16 + tc;
+#pragma unroll
+              for (int i = 0; i < 4; i++) {
+                const int64_t m = mrow0 + tr + 8 * i;
+                if (m < p.M && col < p.N)
+                  asm volatile("prefetch.global.L2 [%0];" ::"l"(p.residual + m * p.res_stride + col));
+              }
+            }
+          }
+        }
+        ok = mbar_wait(&ss->seg_full_bar[buf], (uint32_t)((seg / NBUF) & 1), ss, p.status, 42);
+        if (!ok) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 128 + col0);
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          if (c < nchunks) {
+            float v[16];
+            tmem_ld16(taddr + (uint32_t)(c * 16), v);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 16; j++) acc[c * 16 + j] += v[j];
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ss->seg_empty_bar[buf]);
+      }
+      if (!ok) break;
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        if (c < nchunks) {
+          // row-per-lane -> shared memory
+#pragma unroll
+          for (int j = 0; j < 16; j += 4)
+            *reinterpret_cast<float4*>(&stg[lane][j]) =
+                make_float4(acc[c * 16 + j], acc[c * 16 + j + 1], acc[c * 16 + j + 2], acc[c * 16 + j + 3]);
+          __syncwarp();
+          const int col = nbase + c * 16 + tc;
+          if (col < p.N && !(p.dbg & 2)) {
+            float sc[4] = {p.alpha, p.alpha, p.alpha, p.alpha}, sh[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+              if (col + e < p.N) {
+                if (p.scale) sc[e] = __ldg(p.scale + col + e);
+                if (p.shift) sh[e] = p.shift_mul * __ldg(p.shift + col + e);
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+              const int64_t m = mrow0 + tr + 8 * i;
+              if (m < p.M) {
+                const float4 a = *reinterpret_cast<const float4*>(&stg[tr + 8 * i][tc]);
+                float o[4] = {a.x, a.y, a.z, a.w};
+                const float rr[4] = {rcur[i].x, rcur[i].y, rcur[i].z, rcur[i].w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                  float t = fmaf(o[e], sc[e], sh[e]);
+                  if (p.residual) t = fmaf(p.res_mul, rr[e], t);
+                  if (p.relu) t = t > 0.f ? t : (t == t ? 0.f : t);
+                  o[e] = t;
+                }
+                float* yp = y + m * (int64_t)p.N + col;
+                if (vec) *reinterpret_cast<float4*>(yp) = make_float4(o[0], o[1], o[2], o[3]);
+                else {
+#pragma unroll
+                  for (int e = 0; e < 4; e++)
+                    if (col + e < p.N) yp[e] = o[e];
+                }
+              }
+            }
+          }
+          __syncwarp();
+          if (c + 1 < nchunks) load_res(c + 1, rcur);
+        }
+      }
     }
   }
 
@@ -438,7 +582,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
   __syncthreads();
   if (warp == MMA_WARP) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
   }
 }
 
@@ -449,6 +593,36 @@ __global__ void split_tf32_kernel(const float* __restrict__ w, float* __restrict
   int64_t step = (int64_t)gridDim.x * blockDim.x;
   for (; i < n; i += step) {
     float v = w[i];
+    float h = to_tf32(v);
+    hi[i] = h;
+    lo[i] = to_tf32(v - h);
+  }
+}
+
+// Stem mode operand preparation: 4 channels per pixel, 8 taps per filter row.
+__global__ void pad_channels4_kernel(const float* __restrict__ x, float* __restrict__ x4, int64_t pixels, int cin) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < pixels; i += step) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* s = x + i * cin;
+    v.x = s[0];
+    if (cin > 1) v.y = s[1];
+    if (cin > 2) v.z = s[2];
+    if (cin > 3) v.w = s[3];
+    reinterpret_cast<float4*>(x4)[i] = v;
+  }
+}
+// w [n][k_h][k_w][cin] -> hi/lo of [n][k_h][8][4] (zero where kx >= k_w or c >= cin)
+__global__ void split_tf32_c4_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo,
+                                     int64_t rows, int k_h, int k_w, int cin) {
+  int64_t total = rows * k_h * 32;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < total; i += step) {
+    int c = (int)(i & 3), kx = (int)((i >> 2) & 7);
+    int64_t r = i >> 5;  // n * k_h + ky
+    float v = (kx < k_w && c < cin) ? w[(r * k_w + kx) * cin + c] : 0.f;
     float h = to_tf32(v);
     hi[i] = h;
     lo[i] = to_tf32(v - h);
@@ -493,7 +667,8 @@ int encode_map(TcState* st, CUtensorMap* map, float* base, int64_t rows, int64_t
 }
 
 // Looks up (or builds) the hi/lo split and the tensor maps of a [rows, k] K-major weight matrix.
-int get_weight(wdc_context* ctx, const float* w, int64_t rows, int64_t k, WeightEntry** out) {
+int get_weight(wdc_context* ctx, const float* w, int64_t rows, int64_t k, WeightEntry** out, int c4_kh = 0,
+               int c4_kw = 0, int c4_cin = 0) {
   TcState* st = tc_state(ctx);
   auto it = st->weights.find(w);
   if (it != st->weights.end() && it->second.rows == rows && it->second.k == k) {
@@ -516,7 +691,11 @@ int get_weight(wdc_context* ctx, const float* w, int64_t rows, int64_t k, Weight
     wdc_free(ctx, e.hi);
     return s;
   }
-  split_tf32_kernel<<<grid_for(ctx, rows * k, 256, 8), 256, 0, ctx->stream>>>(w, e.hi, e.lo, rows * k);
+  if (c4_kh)
+    split_tf32_c4_kernel<<<grid_for(ctx, rows * k, 256, 8), 256, 0, ctx->stream>>>(w, e.hi, e.lo, rows, c4_kh, c4_kw,
+                                                                                    c4_cin);
+  else
+    split_tf32_kernel<<<grid_for(ctx, rows * k, 256, 8), 256, 0, ctx->stream>>>(w, e.hi, e.lo, rows * k);
   s = wdc_check_launch(ctx, "split_tf32_kernel");
   int r1 = encode_map(st, &e.map_hi, e.hi, rows, k, e.tile_n);
   int r2 = encode_map(st, &e.map_lo, e.lo, rows, k, e.tile_n);
@@ -559,15 +738,24 @@ bool tc_ready(wdc_context* ctx) {
   return true;
 }
 
-int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, float* y) {
+int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, float* y, int c4_kw = 0,
+              int c4_cin = 0) {
   WeightEntry* we = nullptr;
-  int s = get_weight(ctx, w, p.N, p.K, &we);
+  int s = get_weight(ctx, w, p.N, p.K, &we, p.c4 ? p.K / 32 : 0, c4_kw, c4_cin);
   if (s != WDC_OK) return s;
   p.tile_n = we->tile_n;
   p.tiles_m = ceil_div64(p.M, TILE_M);
   p.tiles_n = ceil_div64(p.N, p.tile_n);
   p.kblocks = (p.K + BLOCK_K - 1) / BLOCK_K;
   p.status = ctx->status_word;
+  {
+    static int dbg = -1;
+    if (dbg < 0) {
+      const char* e = getenv("WDC_TC_DEBUG");
+      dbg = e ? atoi(e) : 0;
+    }
+    p.dbg = dbg;
+  }
   int64_t tiles = p.tiles_m * p.tiles_n;
   int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   tc_igemm_kernel<<<grid, NUM_THREADS, sizeof(SharedStorage) + 1024, ctx->stream>>>(p, x, we->map_hi, we->map_lo, y);
@@ -598,7 +786,8 @@ void wdc_tc_destroy(wdc_context* ctx) {
 
 int wdc_tc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, const float* w, const float* scale,
                   const float* shift, const float* residual, float* y) {
-  if (d->group != 1 || d->ch_in % BLOCK_K != 0 || d->ch_out % 4 != 0) return WDC_ERR_UNSUPPORTED;
+  const bool stem = d->group == 1 && d->ch_in <= 4 && d->k_w <= 8 && d->ch_out % 4 == 0;
+  if (!stem && (d->group != 1 || d->ch_in % BLOCK_K != 0 || d->ch_out % 4 != 0)) return WDC_ERR_UNSUPPORTED;
   if (!aligned16(x) || !aligned16(w) || !aligned16(y) || (residual && !aligned16(residual))) return WDC_ERR_UNSUPPORTED;
   const int64_t K = d->ch_in * d->k_h * d->k_w;
   if (K > (1 << 30) || d->ch_out > (1 << 24)) return WDC_ERR_UNSUPPORTED;
@@ -614,7 +803,24 @@ int wdc_tc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, cons
   p.cblocks = (int)(d->ch_in / BLOCK_K);
   p.scale = scale; p.shift = shift; p.residual = residual; p.res_stride = d->ch_out;
   p.alpha = 1.f; p.shift_mul = 1.f; p.res_mul = 1.f; p.relu = d->relu;
-  return launch_tc(ctx, p, x, w, y);
+  if (!stem) return launch_tc(ctx, p, x, w, y);
+  // Few input channels (the network's first convolution): pad the pixels to 4 channels so that one
+  // 16-byte chunk is one pixel, and lay the filter out as 8 taps x 4 channels per filter row.
+  float* x4 = nullptr;
+  const int64_t pixels = d->batch * d->in_h * d->in_w;
+  int s = wdc_alloc(ctx, pixels * 16, (void**)&x4);
+  if (s != WDC_OK) return s;
+  pad_channels4_kernel<<<grid_for(ctx, pixels, 256, 8), 256, 0, ctx->stream>>>(x, x4, pixels, (int)d->ch_in);
+  s = wdc_check_launch(ctx, "pad_channels4_kernel");
+  if (s == WDC_OK) {
+    p.c4 = 1;
+    p.ch_in = 4;
+    p.K = (int)d->k_h * 32;
+    p.cblocks = 1;
+    s = launch_tc(ctx, p, x4, w, y, (int)d->k_w, (int)d->ch_in);
+  }
+  wdc_free(ctx, x4);
+  return s;
 }
 
 int wdc_tc_gemm(wdc_context* ctx, const wdc_gemm_desc* d, const float* A, const float* B, const float* C,

@@ -132,11 +132,12 @@ __device__ __forceinline__ unsigned long long global_ns() {
 }
 
 // Bounded wait.  Returns false if the wait was abandoned (time limit or CTA-wide abort).
-__device__ __noinline__ bool mbar_wait_slow(unsigned long long* bar, uint32_t parity, SharedStorage* ss,
-                                            int* status, int code) {
-  unsigned long long t0 = global_ns();
+__device__ __noinline__ bool mbar_wait_timed(unsigned long long* bar, uint32_t parity, SharedStorage* ss,
+                                             int* status, int code) {
+  // reached only after a few thousand failed polls: now watch the clock and the abort flag
+  const unsigned long long t0 = global_ns();
   for (;;) {
-    for (int i = 0; i < 256; i++)
+    for (int i = 0; i < 1024; i++)
       if (mbar_try_wait(bar, parity)) return true;
     if (ss->abort_flag) return false;
     if (global_ns() - t0 > WAIT_LIMIT_NS) {
@@ -148,8 +149,10 @@ __device__ __noinline__ bool mbar_wait_slow(unsigned long long* bar, uint32_t pa
 }
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity, SharedStorage* ss,
                                           int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, ss, status, code);
+  // Hot path: plain polling, no timer read.
+  for (int i = 0; i < 4096; i++)
+    if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_timed(bar, parity, ss, status, code);
 }
 
 __device__ __forceinline__ bool elect_one() {

@@ -1,0 +1,85 @@
+"""Times wdc_conv2d on single convolution shapes (the ResNet-50 layers at a given batch).
+
+    python -m webdnn_b200.layer_bench [--batch 256] [--only l4.c2,l1.c3] [--reps 5]
+
+Prints, per layer, the mean device time of the contraction launch (CUDA events recorded by the
+library around each launch), algorithmic TFLOP/s, the tensor-issue rate (3 MMAs per algorithmic
+multiply-add) and the bytes the layer has to move.  Used to profile one kernel shape under ncu
+without running a whole network.
+"""
+from __future__ import annotations
+
+import argparse
+
+import numpy as np
+
+from .backend import CPUTensor, WebDNNCudaContext
+from .lib import ConvDesc
+
+# name, ch_in, ch_out, input size, kernel, stride, pad, residual
+LAYERS = [
+    ("stem 7x7 3->64 s2", 3, 64, 224, 7, 2, 3, 0),
+    ("l1.c1 1x1 64->64", 64, 64, 56, 1, 1, 0, 0),
+    ("l1.c2 3x3 64->64", 64, 64, 56, 3, 1, 1, 0),
+    ("l1.c3 1x1 64->256 +res", 64, 256, 56, 1, 1, 0, 1),
+    ("l1.c1b 1x1 256->64", 256, 64, 56, 1, 1, 0, 0),
+    ("l2.c2 3x3 128->128 s2", 128, 128, 56, 3, 2, 1, 0),
+    ("l2.c2b 3x3 128->128", 128, 128, 28, 3, 1, 1, 0),
+    ("l2.c3 1x1 128->512 +res", 128, 512, 28, 1, 1, 0, 1),
+    ("l3.c1 1x1 1024->256", 1024, 256, 14, 1, 1, 0, 0),
+    ("l3.c2 3x3 256->256", 256, 256, 14, 3, 1, 1, 0),
+    ("l3.c3 1x1 256->1024 +res", 256, 1024, 14, 1, 1, 0, 1),
+    ("l4.c1 1x1 2048->512", 2048, 512, 7, 1, 1, 0, 0),
+    ("l4.c2 3x3 512->512", 512, 512, 7, 3, 1, 1, 0),
+    ("l4.c3 1x1 512->2048 +res", 512, 2048, 7, 1, 1, 0, 1),
+]
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--only", default="")
+    ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--tf32-peak", type=float, default=752.0, help="TFLOP/s used for the issue-rate column")
+    args = ap.parse_args()
+    only = [s for s in args.only.split(",") if s]
+    ctx = WebDNNCudaContext()
+    ctx.initialize()
+    B = args.batch
+    total = 0.0
+    for name, cin, cout, hw, k, s, pad, res in LAYERS:
+        if only and not any(name.startswith(o) for o in only):
+            continue
+        oh = (hw + 2 * pad - k) // s + 1
+        x = ctx.empty_tensor([B, cin, hw, hw], layout="nhwc")
+        w = ctx.empty_tensor([cout, k, k, cin])
+        ctx._call("wdc_fill_u32", x.ptr, 0x3F800000, x.length)   # 1.0
+        ctx._call("wdc_fill_u32", w.ptr, 0x3C000000, w.length)   # 2^-7
+        sc = ctx.move_tensor(CPUTensor.from_array(np.ones(cout, np.float32)))
+        sh = ctx.move_tensor(CPUTensor.from_array(np.zeros(cout, np.float32)))
+        y = ctx.empty_tensor([B, cout, oh, oh], layout="nhwc")
+        r = ctx.empty_tensor([B, cout, oh, oh], layout="nhwc") if res else None
+        d = ConvDesc(batch=B, ch_in=cin, in_h=hw, in_w=hw, ch_out=cout, k_h=k, k_w=k, out_h=oh, out_w=oh,
+                     stride_h=s, stride_w=s, pad_t=pad, pad_l=pad, dil_h=1, dil_w=1, group=1, relu=1)
+        for _ in range(2):
+            ctx.conv2d(d, x, w, sc, sh, r, y)
+        ctx.profile_enable(True)
+        for _ in range(args.reps):
+            ctx.conv2d(d, x, w, sc, sh, r, y)
+        ms, _, fl = ctx.profile_read()
+        ctx.profile_enable(False)
+        ms /= args.reps
+        flops = fl / args.reps
+        nbytes = 4 * (x.length + y.length * (2 if res else 1) + w.length)
+        total += ms
+        print(f"{name:28s} {ms * 1e3:8.1f} us  {flops / ms / 1e9:7.1f} TFLOP/s algorithmic "
+              f"({3 * flops / ms / 1e9 / args.tf32_peak * 100:5.1f}% of TF32 issue)  {nbytes / ms / 1e6:7.0f} GB/s "
+              f"of algorithmic bytes")
+        for t in (x, w, sc, sh, y) + ((r,) if r else ()):
+            t.dispose()
+    print(f"sum {total:.3f} ms")
+    ctx.close()
+
+
+if __name__ == "__main__":
+    main()

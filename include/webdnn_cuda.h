@@ -197,6 +197,17 @@ int wdc_lstm(wdc_context* ctx, const float* X, const float* W, const float* R, c
              const float* h0, const float* c0, float* Y, float* Yh, float* Yc, int64_t T,
              int64_t Bt, int64_t I, int64_t H);
 
+/* wdc_lstm for callers that cannot allocate device memory while they run (a host that owns all GPU memory in
+ * its own pool, a real-time loop, a sandbox without cudaMalloc): same arguments and results as wdc_lstm, but the
+ * scratch is a fixed 4 MiB array inside the library image (held on every GPU that loads the library, until exit)
+ * and no cudaMalloc / cudaFree / allocating routine is called.  Limit: batch * 4 * hidden_size <= 1 048 576,
+ * otherwise WDC_ERR_UNSUPPORTED.  The first call on a device looks the array's address up; make it before any
+ * stream capture.  Calls on one device share the array: calls that overlap on the GPU race.  This entry point has
+ * no counterpart in the reference. */
+int wdc_lstm_static(wdc_context* ctx, const float* X, const float* W, const float* R, const float* bias,
+                    const float* h0, const float* c0, float* Y, float* Yh, float* Yc, int64_t T,
+                    int64_t Bt, int64_t I, int64_t H);
+
 #ifdef __cplusplus
 }
 #endif

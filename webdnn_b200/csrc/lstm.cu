@@ -83,3 +83,70 @@ extern "C" int wdc_lstm(wdc_context* ctx, const float* X, const float* W, const 
   wdc_free(ctx, P);
   return s;
 }
+
+// ------------------------------------------------------------------------------------------------
+// wdc_lstm_static: the same LSTM for callers that must not allocate.
+//
+// Some hosts of this library cannot take a device allocation in the middle of their work: a runtime
+// that has handed all of the GPU's memory to its own pool, a real-time loop that may not block in
+// the driver's allocator, a plug-in sandbox that forbids cudaMalloc after start-up.  wdc_lstm needs
+// scratch (the projected inputs of all steps and one step's gate pre-activations) and takes it from
+// the context arena, which may have to grow.  This variant keeps its scratch in a fixed array that
+// is part of the loaded library image instead: kLstmStaticFloats floats (4 MiB) per GPU that loads
+// the library, held until the process exits.  To stay inside that budget it projects the input one
+// step at a time, so the scratch is one [batch, 4*hidden] block, and it runs both contractions on
+// the CUDA-core kernel, whose launch allocates nothing (the tensor-core path caches a split copy of
+// its weights in the arena).
+//
+// In host code the array's name is only a handle for the symbol, not a device address; the address
+// comes from cudaGetSymbolAddress, asked once per device with that device current.  That lookup
+// happens in the first call on each device, so make that first call outside any stream capture.
+// All calls on a device share the one array: it holds whatever the previous call left (nothing here
+// needs to start at zero: every step overwrites the block before reading it), and two calls that
+// overlap on the GPU (different streams or contexts of one device) would race on it.
+constexpr int64_t kLstmStaticFloats = 1 << 20;
+static __device__ __align__(256) float g_lstm_static_scratch[kLstmStaticFloats];
+
+static float* g_lstm_static_ptr[64] = {};  // per-device address of the array, filled on first use
+
+extern "C" int wdc_lstm_static(wdc_context* ctx, const float* X, const float* W, const float* R,
+                               const float* bias, const float* h0, const float* c0, float* Y, float* Yh,
+                               float* Yc, int64_t T, int64_t Bt, int64_t I, int64_t H) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_lstm_static: null context");
+  WDC_REQUIRE(ctx, T >= 0 && Bt > 0 && I > 0 && H > 0, "wdc_lstm_static: bad shape");
+  WDC_REQUIRE(ctx, X && W && R && Yh && Yc && (T == 0 || Y), "wdc_lstm_static: null buffer");
+  if (Bt * 4 * H > kLstmStaticFloats)
+    return wdc_fail(ctx, WDC_ERR_UNSUPPORTED,
+                    "wdc_lstm_static: batch * 4 * hidden_size = %lld exceeds the static scratch of %lld floats; "
+                    "use wdc_lstm",
+                    (long long)(Bt * 4 * H), (long long)kLstmStaticFloats);
+  WDC_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, "wdc_lstm_static: device index out of range");
+  DeviceGuard g(ctx->device);
+  float* G = g_lstm_static_ptr[ctx->device];
+  if (!G) {
+    WDC_CUDA(ctx, cudaGetSymbolAddress((void**)&G, g_lstm_static_scratch));
+    g_lstm_static_ptr[ctx->device] = G;
+  }
+  int s;
+  if (h0) s = wdc_copy(ctx, Yh, h0, Bt * H * 4);
+  else s = wdc_fill_u32(ctx, Yh, 0u, Bt * H);
+  if (s == WDC_OK) {
+    if (c0) s = wdc_copy(ctx, Yc, c0, Bt * H * 4);
+    else s = wdc_fill_u32(ctx, Yc, 0u, Bt * H);
+  }
+  for (int64_t t = 0; t < T && s == WDC_OK; t++) {
+    wdc_gemm_desc d = {};
+    d.batch = 1; d.m = Bt; d.n = 4 * H; d.k = I;
+    d.sa0 = I; d.sa1 = 1; d.sb0 = 1; d.sb1 = I;   // G = X_t * W^T
+    d.alpha = 1.f; d.beta = 0.f;
+    s = wdc_simt_gemm(ctx, &d, X + t * Bt * I, W, nullptr, G);
+    if (s != WDC_OK) break;
+    d.k = H; d.sa0 = H; d.sb1 = H;                // G = h * R^T + G (each element read then written by one thread)
+    d.sc0 = 4 * H; d.sc1 = 1; d.beta = 1.f;
+    s = wdc_simt_gemm(ctx, &d, Yh, R, G, G);
+    if (s != WDC_OK) break;
+    lstm_gate_kernel<<<grid_for(ctx, Bt * H, 256, 4), 256, 0, ctx->stream>>>(G, bias, Yc, Yh, Y + t * Bt * H, Bt, H);
+    s = wdc_check_launch(ctx, "lstm_gate_kernel");
+  }
+  return s;
+}

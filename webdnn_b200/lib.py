@@ -98,6 +98,7 @@ SIGNATURES = {
     "wdc_strided_copy": (c_int, [c_void_p, c_void_p, c_void_p, c_int, I64P, I64P, c_int64, I64P, c_int64]),
     "wdc_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64]),
     "wdc_lstm": (c_int, [c_void_p] + [c_void_p] * 9 + [c_int64] * 4),
+    "wdc_lstm_static": (c_int, [c_void_p] + [c_void_p] * 9 + [c_int64] * 4),
 }
 
 _lib = None

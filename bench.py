@@ -111,6 +111,8 @@ def cpu_port_images_per_sec(n_images: int):
     """Times the CPU oracle (port of the reference's cpu backend) on ResNet-50, batch n_images."""
     from oracle import ops, ref_runner
     from webdnn_b200 import zoo
+    # torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use every host thread it can
+    ops.set_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     model = zoo.resnet50(n_images)
     x = zoo.make_input((n_images, 3, 224, 224))
     t0 = time.perf_counter()

@@ -62,6 +62,7 @@ constexpr int NBUF = 2;               // TMEM segment accumulators of 128 column
 constexpr int TMEM_A_COL0 = NBUF * 128;  // first column of the A stages
 constexpr int W_TILE_BYTES = 128 * BLOCK_K * 4;  // 16 KB (hi) + 16 KB (lo) per stage
 constexpr int PREFETCH = 2;           // K blocks of A held in registers per thread
+constexpr int KTAB = 512;             // K blocks whose gather offsets are tabulated in shared memory
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 struct TcProblem {
@@ -87,10 +88,19 @@ struct TcProblem {
   int* status;
 };
 
+// Gather recipe of one K block, the same for every row of every tile: computed once per launch so
+// that the producers' inner loop has no integer division.
+struct KEntry {
+  int off;       // element offset inside the image: (ky*dil_h*in_w + kx*dil_w)*ch_in + c0
+  short dy, dx;  // tap displacement, for the bounds check
+  int nchunks;   // valid 16-byte chunks of the block (8 unless the channel count ends inside it)
+};
+
 struct __align__(1024) SharedStorage {
   // weight tiles first: each must start on a 1024-byte boundary for the 128B swizzle
   unsigned char w_hi[STAGES][W_TILE_BYTES];
   unsigned char w_lo[STAGES][W_TILE_BYTES];
+  KEntry ktab[KTAB];
   float epi_stage[NUM_EPI_WARPS][32][20];  // per-warp transpose buffer: 32 rows x 16 columns (+4 pad)
   unsigned long long full_bar[STAGES];
   unsigned long long empty_bar[STAGES];
@@ -253,6 +263,25 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     ss->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  for (int kb = threadIdx.x; kb < p.kblocks && kb < KTAB; kb += NUM_THREADS) {
+    KEntry e;
+    if (p.c4) {
+      e.off = kb * p.dil_h * p.in_w * 4;
+      e.dy = (short)(kb * p.dil_h);
+      e.dx = 0;
+      e.nchunks = p.k_w;
+    } else {
+      const int tap = kb / p.cblocks;
+      const int c0 = (kb - tap * p.cblocks) * BLOCK_K;
+      const int ky = tap / p.k_w, kx = tap - ky * p.k_w;
+      e.off = (ky * p.dil_h * p.in_w + kx * p.dil_w) * p.ch_in + c0;
+      e.dy = (short)(ky * p.dil_h);
+      e.dx = (short)(kx * p.dil_w);
+      const int left = (p.ch_in - c0 + 3) >> 2;
+      e.nchunks = left < 8 ? left : 8;
+    }
+    ss->ktab[kb] = e;
+  }
   if (warp == MMA_WARP) {
     // all 512 columns: NBUF segment accumulators + STAGES x (A_hi, A_lo)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ss->tmem_base)),
@@ -278,16 +307,15 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     const uint32_t hw = (uint32_t)p.out_h * (uint32_t)p.out_w;
     const int64_t img_elems = (int64_t)p.in_h * p.in_w * p.ch_in;
     // load-side cursor
-    int64_t ld_tile_i = -1;           // index into this CTA's tile sequence whose row is cached
-    const float* rptr = nullptr;      // pixel (n, 0, 0, channel 0) of this thread's row, null past M
+    const float* rsrc = nullptr;      // address of input pixel (n, iy0, ix0, channel 0); null for rows past M
     int riy = 0, rix = 0;
-    int ld_kb = 0;
-    int64_t ld_tile_seq = 0;
+    int ld_kb = p.kblocks;            // forces the row set-up on the first call
+    int64_t ld_tile = (int64_t)blockIdx.x - gridDim.x;
     auto issue = [&](float4* dst) {
-      if (ld_tile_seq != ld_tile_i) {
-        ld_tile_i = ld_tile_seq;
-        const int64_t tile = blockIdx.x + ld_tile_seq * gridDim.x;
-        const int64_t m = (tile / p.tiles_n) * TILE_M + row;
+      if (ld_kb == p.kblocks) {       // next tile: locate this thread's output pixel
+        ld_kb = 0;
+        ld_tile += gridDim.x;
+        const int64_t m = (ld_tile / p.tiles_n) * TILE_M + row;
         if (m < p.M) {
           uint32_t n, rem;
           if (p.M <= 0x7fffffffll) {  // 32-bit division is several times cheaper
@@ -298,45 +326,56 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
             rem = (uint32_t)(m - (int64_t)n * hw);
           }
           const int oy = (int)(rem / (uint32_t)p.out_w), ox = (int)rem - oy * p.out_w;
-          rptr = x + (int64_t)n * img_elems;
           riy = oy * p.stride_h - p.pad_t;
           rix = ox * p.stride_w - p.pad_l;
+          rsrc = x + ((int64_t)n * img_elems + (int64_t)(riy * p.in_w + rix) * p.ch_in);
         } else {
-          rptr = nullptr;
+          rsrc = nullptr;
         }
       }
       int kb = ld_kb + rot;
       if (kb >= p.kblocks) kb -= p.kblocks;
+      ld_kb++;
+      KEntry e;
+      if (kb < KTAB) {
+        e = ss->ktab[kb];
+      } else {  // very long reductions: compute the entry instead of looking it up
+        const int tap = kb / p.cblocks;
+        const int c0 = (kb - tap * p.cblocks) * BLOCK_K;
+        const int ky = tap / p.k_w, kx = tap - ky * p.k_w;
+        e.off = (ky * p.dil_h * p.in_w + kx * p.dil_w) * p.ch_in + c0;
+        e.dy = (short)(ky * p.dil_h);
+        e.dx = (short)(kx * p.dil_w);
+        const int left = (p.ch_in - c0 + 3) >> 2;
+        e.nchunks = left < 8 ? left : 8;
+      }
+      const int iy = riy + e.dy;
+      const bool rowok = !(p.dbg & 1) && rsrc != nullptr && (unsigned)iy < (unsigned)p.in_h;
+      const float* src = rsrc + e.off;
       if (p.c4) {
-        // one K block = one filter row: chunk j is tap kx = j (4 channels of one pixel)
-        const int iy = riy + kb * p.dil_h;
-        const bool rok = !(p.dbg & 1) && rptr != nullptr && (unsigned)iy < (unsigned)p.in_h;
+        // one K block = one filter row: chunk j is tap kx = j (the 4 channels of one pixel)
 #pragma unroll
         for (int j = 0; j < 8; j++) {
           const int ix = rix + j * p.dil_w;
           float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (rok && j < p.k_w && (unsigned)ix < (unsigned)p.in_w)
-            v = __ldg(reinterpret_cast<const float4*>(rptr + (iy * p.in_w + ix) * 4));
+          if (rowok && j < e.nchunks && (unsigned)ix < (unsigned)p.in_w)
+            v = __ldg(reinterpret_cast<const float4*>(src + j * p.dil_w * 4));
           dst[j] = v;
         }
       } else {
-        const int tap = kb / p.cblocks;
-        const int c0 = (kb - tap * p.cblocks) * BLOCK_K;
-        const int ky = tap / p.k_w, kx = tap - ky * p.k_w;
-        const int iy = riy + ky * p.dil_h, ix = rix + kx * p.dil_w;
-        const bool rok = !(p.dbg & 1) && rptr != nullptr && (unsigned)iy < (unsigned)p.in_h &&
-                         (unsigned)ix < (unsigned)p.in_w;
-        const float* src = rptr + ((iy * p.in_w + ix) * p.ch_in + c0);
+        const int ix = rix + e.dx;
+        const bool ok2 = rowok && (unsigned)ix < (unsigned)p.in_w;
+        if (ok2 && e.nchunks == 8) {
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (rok && c0 + j * 4 < p.ch_in) v = __ldg(reinterpret_cast<const float4*>(src + j * 4));
-          dst[j] = v;
+          for (int j = 0; j < 8; j++) dst[j] = __ldg(reinterpret_cast<const float4*>(src) + j);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (ok2 && j < e.nchunks) v = __ldg(reinterpret_cast<const float4*>(src) + j);
+            dst[j] = v;
+          }
         }
-      }
-      if (++ld_kb == p.kblocks) {
-        ld_kb = 0;
-        ld_tile_seq++;
       }
     };
     float4 ring[PREFETCH][8];

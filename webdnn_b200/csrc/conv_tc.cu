@@ -54,6 +54,8 @@ constexpr int STAGES = 4;
 constexpr int NUM_A_WARPS = 4;
 constexpr int TMA_WARP = 4;
 constexpr int MMA_WARP = 5;
+constexpr int ATMA_WARP = 6;          // issues the im2col tile loads of A (kTmaA kernels only)
+constexpr int A_TILE_BYTES = TILE_M * BLOCK_K * 4;  // 16 KB of raw fp32 A per stage
 constexpr int EPI_WARP0 = 8;
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_THREADS = 16 * 32;
@@ -70,7 +72,7 @@ struct TcProblem {
   int64_t M;          // batch * out_h * out_w
   int N;              // output channels
   int K;              // k_h * k_w * ch_in
-  int ch_in, in_h, in_w, out_h, out_w, k_w;
+  int ch_in, in_h, in_w, out_h, out_w, k_h, k_w;
   int stride_h, stride_w, pad_t, pad_l, dil_h, dil_w;
   int kblocks;        // ceil(K / 32)
   int cblocks;        // K blocks per filter tap = ceil(ch_in / 32)
@@ -100,12 +102,17 @@ struct __align__(1024) SharedStorage {
   // weight tiles first: each must start on a 1024-byte boundary for the 128B swizzle
   unsigned char w_hi[STAGES][W_TILE_BYTES];
   unsigned char w_lo[STAGES][W_TILE_BYTES];
-  KEntry ktab[KTAB];
+  union {
+    unsigned char a_raw[STAGES][A_TILE_BYTES];  // kTmaA: raw A tiles, 128B-swizzled rows of 32 floats
+    KEntry ktab[KTAB];                          // gather kernels: per-K-block gather recipes
+  };
   float epi_stage[NUM_EPI_WARPS][32][20];  // per-warp transpose buffer: 32 rows x 16 columns (+4 pad)
   unsigned long long full_bar[STAGES];
   unsigned long long empty_bar[STAGES];
   unsigned long long seg_full_bar[NBUF];
   unsigned long long seg_empty_bar[NBUF];
+  unsigned long long a_full_bar[STAGES];
+  unsigned long long a_empty_bar[STAGES];
   unsigned int tmem_base;
   volatile int abort_flag;
 };
@@ -221,6 +228,21 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "r"(smem_u32(smem_dst)), "l"((unsigned long long)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+// im2col-mode tile load of an NHWC tensor: TILE_M pixels x BLOCK_K channels starting at base pixel
+// (w, h, n) and channel c, each pixel displaced by the filter tap (off_w, off_h).  The base pixel
+// walks the bounding box of the tensor map W-first with the convolution's strides; positions that
+// fall outside the image (padding) or past the last image read as zero.
+__device__ __forceinline__ void tma_load_im2col(void* smem_dst, const CUtensorMap* map, unsigned long long* bar,
+                                                int c, int w, int h, int n, int off_w, int off_h) {
+  const unsigned short ow = (unsigned short)off_w, oh = (unsigned short)off_h;
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+      :
+      : "r"(smem_u32(smem_dst)), "l"((unsigned long long)map), "r"(smem_u32(bar)), "r"(c), "r"(w), "r"(h), "r"(n),
+        "h"(ow), "h"(oh)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   uint32_t* r = reinterpret_cast<uint32_t*>(v);
   asm volatile(
@@ -242,10 +264,14 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const float* v) {
       : "memory");
 }
 
+// kTmaA = true: A tiles arrive by im2col TMA in shared memory (map_a) and the producer warps only
+// split them into TMEM.  kTmaA = false: the producer warps gather A from global memory themselves
+// (first-layer mode with 4 channels per pixel, and geometries an im2col tensor map cannot express).
+template <bool kTmaA>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x,
                 const __grid_constant__ CUtensorMap map_w_hi, const __grid_constant__ CUtensorMap map_w_lo,
-                float* __restrict__ y) {
+                const __grid_constant__ CUtensorMap map_a, float* __restrict__ y) {
   extern __shared__ unsigned char smem_raw[];
   SharedStorage* ss = reinterpret_cast<SharedStorage*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -255,6 +281,8 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     for (int s = 0; s < STAGES; s++) {
       mbar_init(&ss->full_bar[s], NUM_A_WARPS + 1);
       mbar_init(&ss->empty_bar[s], 1);
+      mbar_init(&ss->a_full_bar[s], 1);
+      mbar_init(&ss->a_empty_bar[s], NUM_A_WARPS);
     }
     for (int b = 0; b < NBUF; b++) {
       mbar_init(&ss->seg_full_bar[b], 1);
@@ -263,7 +291,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     ss->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (int kb = threadIdx.x; kb < p.kblocks && kb < KTAB; kb += NUM_THREADS) {
+  for (int kb = threadIdx.x; !kTmaA && kb < p.kblocks && kb < KTAB; kb += NUM_THREADS) {
     KEntry e;
     if (p.c4) {
       e.off = kb * p.dil_h * p.in_w * 4;
@@ -296,8 +324,91 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
   // same weight tiles, do not ask the same L2 lines at the same moment.
   const int rot = (int)(((int64_t)blockIdx.x * p.kblocks) / gridDim.x);
 
-  if (warp < NUM_A_WARPS) {
-    // ===================================================================== A producers
+  if (kTmaA && warp < NUM_A_WARPS) {
+    // ===================================================================== A producers (split only)
+    // Thread (w, l) owns row 32w+l of the tile = TMEM lane.  Per K block: read the row's 32 raw
+    // values from the swizzled shared-memory tile, write them unchanged as the high operand (the
+    // tensor core ignores the low 13 bits of a tf32 operand, i.e. it truncates) and
+    // lo = x - truncate(x), exact in fp32, as the low operand.
+    const int row = threadIdx.x;
+    const int64_t my_tiles = (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+    const int64_t items = my_tiles * p.kblocks;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)TMEM_A_COL0;
+    const uint32_t row_off = (uint32_t)row * 128u;
+    const uint32_t sw = (uint32_t)(row & 7);
+    int stage = 0;
+    uint32_t phase = 0;
+    for (int64_t g = 0; g < items; g++) {
+      if (!mbar_wait(&ss->a_full_bar[stage], phase, ss, p.status, 11)) break;
+      float4 v[8];
+      const unsigned char* tile = ss->a_raw[stage] + row_off;
+#pragma unroll
+      for (int j = 0; j < 8; j++) v[j] = *reinterpret_cast<const float4*>(tile + (((uint32_t)j ^ sw) << 4));
+      if (!mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 12)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a_hi = lane_base + (uint32_t)(stage * 64);
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        float hi[16], lo[16];
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+          const float4 q = v[h * 4 + c];
+          const float e[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int t = 0; t < 4; t++) {
+            hi[c * 4 + t] = e[t];
+            lo[c * 4 + t] = e[t] - __uint_as_float(__float_as_uint(e[t]) & 0xffffe000u);
+          }
+        }
+        tmem_st16(a_hi + (uint32_t)(h * 16), hi);
+        tmem_st16(a_hi + 32u + (uint32_t)(h * 16), lo);
+      }
+      // the shared-memory tile has been read into registers: hand the slot back to the loader
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ss->a_empty_bar[stage]);
+      asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ss->full_bar[stage]);
+      if (++stage == STAGES) { stage = 0; phase ^= 1; }
+    }
+  } else if (kTmaA && warp == ATMA_WARP) {
+    // ===================================================================== A loader (im2col TMA)
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t hw = (uint32_t)p.out_h * (uint32_t)p.out_w;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        // base pixel of the tile's first row
+        const int64_t m0 = (tile / p.tiles_n) * TILE_M;
+        const int64_t n = m0 / hw;
+        const uint32_t rem = (uint32_t)(m0 - n * hw);
+        const int oy = (int)(rem / (uint32_t)p.out_w), ox = (int)rem - oy * p.out_w;
+        const int cw = ox * p.stride_w - p.pad_l, ch = oy * p.stride_h - p.pad_t;
+        // first K block of this CTA's rotation
+        const int tap = rot / p.cblocks;
+        int c0 = (rot - tap * p.cblocks) * BLOCK_K;
+        int ky = tap / p.k_w, kx = tap - ky * p.k_w;
+        for (int kb = 0; kb < p.kblocks; kb++) {
+          if (!mbar_wait(&ss->a_empty_bar[stage], phase ^ 1, ss, p.status, 22)) { ok = false; break; }
+          mbar_arrive_expect_tx(&ss->a_full_bar[stage], (uint32_t)A_TILE_BYTES);
+          tma_load_im2col(ss->a_raw[stage], &map_a, &ss->a_full_bar[stage], c0, cw, ch, (int)n, kx * p.dil_w,
+                          ky * p.dil_h);
+          c0 += BLOCK_K;
+          if (c0 >= p.ch_in) {
+            c0 = 0;
+            if (++kx == p.k_w) {
+              kx = 0;
+              if (++ky == p.k_h) ky = 0;
+            }
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (!kTmaA && warp < NUM_A_WARPS) {
+    // ===================================================================== A producers (gather)
     // Work items are (tile, K block) pairs in the order the MMA warp consumes them.  Loads run
     // PREFETCH items ahead of the TMEM stores and cross tile boundaries, so the global load latency
     // is paid once per CTA, not once per tile.
@@ -675,6 +786,11 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const int*, const int*, cuuint32_t, cuuint32_t,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
 struct WeightEntry {
   float* hi = nullptr;
   float* lo = nullptr;
@@ -685,6 +801,7 @@ struct WeightEntry {
 
 struct TcState {
   EncodeTiledFn encode = nullptr;
+  EncodeIm2colFn encode_im2col = nullptr;  // may stay null: then every launch gathers A itself
   bool unavailable = false;
   bool attr_set = false;
   std::map<const void*, WeightEntry> weights;
@@ -766,10 +883,17 @@ bool tc_ready(wdc_context* ctx) {
       return false;
     }
     st->encode = (EncodeTiledFn)fn;
+    fn = nullptr;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q);
+    if (e == cudaSuccess && q == cudaDriverEntryPointSuccess && fn) st->encode_im2col = (EncodeIm2colFn)fn;
+    else cudaGetLastError();
   }
   if (!st->attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(tc_igemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(tc_igemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)sizeof(SharedStorage) + 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tc_igemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)sizeof(SharedStorage) + 1024);
     if (e != cudaSuccess) {
       cudaGetLastError();
       st->unavailable = true;
@@ -778,6 +902,33 @@ bool tc_ready(wdc_context* ctx) {
     st->attr_set = true;
   }
   return true;
+}
+
+// Describes the NHWC input as an im2col tensor map: box = TILE_M pixels x BLOCK_K channels, bounding
+// box = the positions the filter's first tap takes (from -pad to the position of the last output
+// pixel), traversal strides = the convolution's strides.  Returns false when the geometry does not
+// fit the map's fields; the caller then launches the gathering kernel.
+bool encode_a_map(TcState* st, const TcProblem& p, const float* x, CUtensorMap* map) {
+  if (!st->encode_im2col || p.c4 || (p.dbg & 32)) return false;
+  const int64_t hw = (int64_t)p.out_h * p.out_w;
+  const int64_t images = (p.M + hw - 1) / hw;
+  const int lower[2] = {-p.pad_l, -p.pad_t};
+  const int upper[2] = {-p.pad_l + (p.out_w - 1) * p.stride_w - (p.in_w - 1),
+                        -p.pad_t + (p.out_h - 1) * p.stride_h - (p.in_h - 1)};
+  for (int i = 0; i < 2; i++)
+    if (lower[i] < -128 || lower[i] > 127 || upper[i] < -128 || upper[i] > 127) return false;
+  if (p.stride_w < 1 || p.stride_w > 8 || p.stride_h < 1 || p.stride_h > 8) return false;
+  if ((p.k_w - 1) * p.dil_w > 255 || (p.k_h - 1) * p.dil_h > 255) return false;
+  if ((p.ch_in & 3) || images >= (1ll << 31)) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)p.ch_in, (cuuint64_t)p.in_w, (cuuint64_t)p.in_h, (cuuint64_t)images};
+  cuuint64_t strides[3] = {(cuuint64_t)p.ch_in * 4, (cuuint64_t)p.ch_in * 4 * p.in_w,
+                           (cuuint64_t)p.ch_in * 4 * p.in_w * p.in_h};
+  if (strides[2] >= (1ull << 40)) return false;
+  cuuint32_t estr[4] = {1, (cuuint32_t)p.stride_w, (cuuint32_t)p.stride_h, 1};
+  CUresult r = st->encode_im2col(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)x, dims, strides, lower, upper,
+                                 BLOCK_K, TILE_M, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
 }
 
 int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, float* y, int c4_kw = 0,
@@ -800,7 +951,13 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
   }
   int64_t tiles = p.tiles_m * p.tiles_n;
   int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
-  tc_igemm_kernel<<<grid, NUM_THREADS, sizeof(SharedStorage) + 1024, ctx->stream>>>(p, x, we->map_hi, we->map_lo, y);
+  CUtensorMap map_a;
+  if (encode_a_map(tc_state(ctx), p, x, &map_a))
+    tc_igemm_kernel<true><<<grid, NUM_THREADS, sizeof(SharedStorage) + 1024, ctx->stream>>>(p, x, we->map_hi,
+                                                                                            we->map_lo, map_a, y);
+  else
+    tc_igemm_kernel<false><<<grid, NUM_THREADS, sizeof(SharedStorage) + 1024, ctx->stream>>>(p, x, we->map_hi,
+                                                                                             we->map_lo, we->map_hi, y);
   ctx->n_tc_launch++;
   return wdc_check_launch(ctx, "tc_igemm_kernel");
 }
@@ -839,7 +996,7 @@ int wdc_tc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, cons
   p.N = (int)d->ch_out;
   p.K = (int)K;
   p.ch_in = (int)d->ch_in; p.in_h = (int)d->in_h; p.in_w = (int)d->in_w;
-  p.out_h = (int)d->out_h; p.out_w = (int)d->out_w; p.k_w = (int)d->k_w;
+  p.out_h = (int)d->out_h; p.out_w = (int)d->out_w; p.k_h = (int)d->k_h; p.k_w = (int)d->k_w;
   p.stride_h = (int)d->stride_h; p.stride_w = (int)d->stride_w; p.pad_t = (int)d->pad_t; p.pad_l = (int)d->pad_l;
   p.dil_h = (int)d->dil_h; p.dil_w = (int)d->dil_w;
   p.cblocks = (int)(d->ch_in / BLOCK_K);
@@ -887,7 +1044,7 @@ int wdc_tc_gemm(wdc_context* ctx, const wdc_gemm_desc* d, const float* A, const 
   p.M = d->m;
   p.N = (int)d->n;
   p.K = (int)d->k;
-  p.ch_in = (int)d->k; p.in_h = 1; p.in_w = 1; p.out_h = 1; p.out_w = 1; p.k_w = 1;
+  p.ch_in = (int)d->k; p.in_h = 1; p.in_w = 1; p.out_h = 1; p.out_w = 1; p.k_h = 1; p.k_w = 1;
   p.stride_h = p.stride_w = 1; p.dil_h = p.dil_w = 1;
   p.cblocks = (int)((d->k + BLOCK_K - 1) / BLOCK_K);
   p.shift = shift; p.residual = residual; p.res_stride = res_stride;

@@ -50,7 +50,8 @@ namespace {
 
 constexpr int TILE_M = 128;
 constexpr int BLOCK_K = 32;           // fp32 elements per K block = one 128-byte swizzle row of W
-constexpr int STAGES = 4;
+constexpr int STAGES = 3;             // W tiles in shared memory and A (hi, lo) column groups in TMEM
+constexpr int A_STAGES = 3;           // raw A tiles in shared memory (kTmaA)
 constexpr int NUM_A_WARPS = 4;
 constexpr int TMA_WARP = 4;
 constexpr int MMA_WARP = 5;
@@ -61,6 +62,7 @@ constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_THREADS = 16 * 32;
 constexpr int SEG_KBLOCKS = 4;        // K blocks accumulated in TMEM before the partial sum is drained
 constexpr int NBUF = 2;               // TMEM segment accumulators of 128 columns
+constexpr int EPI_BUF_BYTES = 32 * 32 * 4;   // epilogue staging: 32 rows x 32 columns per buffer, 2 per warp
 constexpr int TMEM_A_COL0 = NBUF * 128;  // first column of the A stages
 constexpr int W_TILE_BYTES = 128 * BLOCK_K * 4;  // 16 KB (hi) + 16 KB (lo) per stage
 constexpr int PREFETCH = 2;           // K blocks of A held in registers per thread
@@ -77,6 +79,7 @@ struct TcProblem {
   int kblocks;        // ceil(K / 32)
   int cblocks;        // K blocks per filter tap = ceil(ch_in / 32)
   int tile_n;         // 32, 64 or 128
+  int tma_epi;        // 1: residual tiles and output tiles move by TMA (map_res, map_y)
   int c4;             // 1: input has 4 channels per pixel, one K block per filter row, chunk j = tap kx
   int64_t tiles_m, tiles_n;
   // epilogue
@@ -103,16 +106,22 @@ struct __align__(1024) SharedStorage {
   unsigned char w_hi[STAGES][W_TILE_BYTES];
   unsigned char w_lo[STAGES][W_TILE_BYTES];
   union {
-    unsigned char a_raw[STAGES][A_TILE_BYTES];  // kTmaA: raw A tiles, 128B-swizzled rows of 32 floats
+    unsigned char a_raw[A_STAGES][A_TILE_BYTES];  // kTmaA: raw A tiles, 128B-swizzled rows of 32 floats
     KEntry ktab[KTAB];                          // gather kernels: per-K-block gather recipes
   };
-  float epi_stage[NUM_EPI_WARPS][32][20];  // per-warp transpose buffer: 32 rows x 16 columns (+4 pad)
+  union {
+    unsigned char epi_buf[NUM_EPI_WARPS][2][EPI_BUF_BYTES];  // TMA epilogue: residual in, result out
+    float epi_stage[NUM_EPI_WARPS][32][20];  // plain epilogue: per-warp transpose buffer, 32 rows x 16 columns (+4 pad)
+  };
+  float epi_scale[NUM_EPI_WARPS][64];        // per-column multiplier and addend of the warp's columns
+  float epi_shift[NUM_EPI_WARPS][64];
   unsigned long long full_bar[STAGES];
   unsigned long long empty_bar[STAGES];
   unsigned long long seg_full_bar[NBUF];
   unsigned long long seg_empty_bar[NBUF];
-  unsigned long long a_full_bar[STAGES];
-  unsigned long long a_empty_bar[STAGES];
+  unsigned long long a_full_bar[A_STAGES];
+  unsigned long long a_empty_bar[A_STAGES];
+  unsigned long long res_bar[NUM_EPI_WARPS][2];
   unsigned int tmem_base;
   volatile int abort_flag;
 };
@@ -228,6 +237,12 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "r"(smem_u32(smem_dst)), "l"((unsigned long long)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               :
+               : "l"((unsigned long long)map), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
 // im2col-mode tile load of an NHWC tensor: TILE_M pixels x BLOCK_K channels starting at base pixel
 // (w, h, n) and channel c, each pixel displaced by the filter tap (off_w, off_h).  The base pixel
 // walks the bounding box of the tensor map W-first with the convolution's strides; positions that
@@ -271,7 +286,8 @@ template <bool kTmaA>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x,
                 const __grid_constant__ CUtensorMap map_w_hi, const __grid_constant__ CUtensorMap map_w_lo,
-                const __grid_constant__ CUtensorMap map_a, float* __restrict__ y) {
+                const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_y,
+                const __grid_constant__ CUtensorMap map_res, float* __restrict__ y) {
   extern __shared__ unsigned char smem_raw[];
   SharedStorage* ss = reinterpret_cast<SharedStorage*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -281,8 +297,14 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     for (int s = 0; s < STAGES; s++) {
       mbar_init(&ss->full_bar[s], NUM_A_WARPS + 1);
       mbar_init(&ss->empty_bar[s], 1);
+    }
+    for (int s = 0; s < A_STAGES; s++) {
       mbar_init(&ss->a_full_bar[s], 1);
       mbar_init(&ss->a_empty_bar[s], NUM_A_WARPS);
+    }
+    for (int w = 0; w < NUM_EPI_WARPS; w++) {
+      mbar_init(&ss->res_bar[w][0], 1);
+      mbar_init(&ss->res_bar[w][1], 1);
     }
     for (int b = 0; b < NBUF; b++) {
       mbar_init(&ss->seg_full_bar[b], 1);
@@ -336,12 +358,12 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)TMEM_A_COL0;
     const uint32_t row_off = (uint32_t)row * 128u;
     const uint32_t sw = (uint32_t)(row & 7);
-    int stage = 0;
-    uint32_t phase = 0;
+    int stage = 0, as = 0;
+    uint32_t phase = 0, aphase = 0;
     for (int64_t g = 0; g < items; g++) {
-      if (!mbar_wait(&ss->a_full_bar[stage], phase, ss, p.status, 11)) break;
+      if (!mbar_wait(&ss->a_full_bar[as], aphase, ss, p.status, 11)) break;
       float4 v[8];
-      const unsigned char* tile = ss->a_raw[stage] + row_off;
+      const unsigned char* tile = ss->a_raw[as] + row_off;
 #pragma unroll
       for (int j = 0; j < 8; j++) v[j] = *reinterpret_cast<const float4*>(tile + (((uint32_t)j ^ sw) << 4));
       if (!mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 12)) break;
@@ -365,12 +387,13 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       }
       // the shared-memory tile has been read into registers: hand the slot back to the loader
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ss->a_empty_bar[stage]);
+      if (lane == 0) mbar_arrive(&ss->a_empty_bar[as]);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&ss->full_bar[stage]);
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      if (++as == A_STAGES) { as = 0; aphase ^= 1; }
     }
   } else if (kTmaA && warp == ATMA_WARP) {
     // ===================================================================== A loader (im2col TMA)
@@ -403,7 +426,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
               if (++ky == p.k_h) ky = 0;
             }
           }
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == A_STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -609,16 +632,136 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     const int half = ew >> 2;                     // which half of the tile's columns
     const int ncols = p.tile_n >> 1;              // 16, 32 or 64 columns per warp
     const int col0 = half * ncols;
-    const int nchunks = ncols >> 4;
     const int nseg = (p.kblocks + SEG_KBLOCKS - 1) / SEG_KBLOCKS;
+    int64_t seg = 0;
+    bool ok = true;
+    if (p.tma_epi) {
+      // ------------------------------------------------------------------ epilogue through TMA
+      // The warp's 32 rows x ncols columns leave in chunks of 32 rows x cw columns.  Per chunk: the
+      // residual tile (if any) has been loaded by TMA into one of the warp's two staging buffers;
+      // lane r reads row r of it, applies scale/shift, residual and Relu to its accumulators, writes
+      // the result over the residual and one lane hands the buffer to a TMA store, which clips at
+      // the matrix edges.  The residual of the following chunk (of this or of the next tile) is
+      // requested right after, into the other buffer.
+      const int cw = ncols < 32 ? ncols : 32;
+      const int nch = ncols / cw;                       // 1 or 2
+      const uint32_t chunk_bytes = 32u * (uint32_t)cw * 4u;
+      const uint32_t swz = cw == 32 ? (uint32_t)(lane & 7) : 0u;   // 128B swizzle only for 128-byte rows
+      const uint32_t row_off = (uint32_t)lane * (uint32_t)cw * 4u;
+      const bool use_res = p.residual != nullptr && !(p.dbg & 2);
+      float* sc_s = ss->epi_scale[ew];
+      float* sh_s = ss->epi_shift[ew];
+      int64_t k = 0;                                    // chunks handled by this warp so far
+      if (use_res && lane == 0 && (int64_t)blockIdx.x < total_tiles) {
+        const int64_t t0 = blockIdx.x;
+        mbar_arrive_expect_tx(&ss->res_bar[ew][0], chunk_bytes);
+        tma_load_2d(ss->epi_buf[ew][0], &map_res, &ss->res_bar[ew][0], (int)(t0 % p.tiles_n) * p.tile_n + col0,
+                    (int)((t0 / p.tiles_n) * TILE_M + q * 32));
+      }
+      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int64_t mrow0 = (tile / p.tiles_n) * TILE_M + q * 32;   // first row of this warp
+        const int nbase = (int)(tile % p.tiles_n) * p.tile_n + col0;
+        for (int i = lane; i < ncols; i += 32) {
+          const int col = nbase + i;
+          float a = p.alpha, b = 0.f;
+          if (col < p.N) {
+            if (p.scale) a = __ldg(p.scale + col);
+            if (p.shift) b = p.shift_mul * __ldg(p.shift + col);
+          }
+          sc_s[i] = a;
+          sh_s[i] = b;
+        }
+        float acc[64];
+#pragma unroll
+        for (int j = 0; j < 64; j++) acc[j] = 0.f;
+        for (int s = 0; s < nseg && ok; s++, seg++) {
+          const int buf = (int)(seg % NBUF);
+          ok = mbar_wait(&ss->seg_full_bar[buf], (uint32_t)((seg / NBUF) & 1), ss, p.status, 42);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 128 + col0);
+#pragma unroll
+          for (int c = 0; c < 4; c++) {
+            if (c * 16 < ncols) {
+              float v[16];
+              tmem_ld16(taddr + (uint32_t)(c * 16), v);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+              for (int j = 0; j < 16; j++) acc[c * 16 + j] += v[j];
+            }
+          }
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ss->seg_empty_bar[buf]);
+        }
+        if (!ok) break;
+#pragma unroll
+        for (int c = 0; c < 2; c++) {
+          if (c < nch && ok) {
+            const int b = (int)(k & 1);
+            unsigned char* sbuf = ss->epi_buf[ew][b];
+            // buffer b is free: with a residual, its load was issued after the store that last read
+            // the buffer had finished; without, lane 0 has waited for that store before this point
+            if (use_res) ok = mbar_wait(&ss->res_bar[ew][b], (uint32_t)((k >> 1) & 1), ss, p.status, 43);
+            __syncwarp();
+            if (ok) {
+#pragma unroll
+              for (int j = 0; j < 8; j++) {
+                if (j * 4 < cw) {
+                  float4* cell = reinterpret_cast<float4*>(sbuf + row_off + (((uint32_t)j ^ swz) << 4));
+                  const float4 a4 = *reinterpret_cast<const float4*>(&sc_s[c * 32 + j * 4]);
+                  const float4 b4 = *reinterpret_cast<const float4*>(&sh_s[c * 32 + j * 4]);
+                  float o[4] = {fmaf(acc[c * 32 + j * 4 + 0], a4.x, b4.x), fmaf(acc[c * 32 + j * 4 + 1], a4.y, b4.y),
+                                fmaf(acc[c * 32 + j * 4 + 2], a4.z, b4.z), fmaf(acc[c * 32 + j * 4 + 3], a4.w, b4.w)};
+                  if (use_res) {
+                    const float4 r4 = *cell;
+                    o[0] = fmaf(p.res_mul, r4.x, o[0]);
+                    o[1] = fmaf(p.res_mul, r4.y, o[1]);
+                    o[2] = fmaf(p.res_mul, r4.z, o[2]);
+                    o[3] = fmaf(p.res_mul, r4.w, o[3]);
+                  }
+                  if (p.relu) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) o[e] = o[e] > 0.f ? o[e] : (o[e] == o[e] ? 0.f : o[e]);
+                  }
+                  *cell = make_float4(o[0], o[1], o[2], o[3]);
+                }
+              }
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0) {
+                const int col = nbase + c * 32;
+                if (!(p.dbg & 2) && mrow0 < p.M && col < p.N) tma_store_2d(&map_y, sbuf, col, (int)mrow0);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the other buffer's store has read it
+                if (use_res) {
+                  int64_t nt = tile;
+                  int nc = c + 1;
+                  if (nc == nch) { nc = 0; nt += gridDim.x; }
+                  if (nt < total_tiles) {
+                    mbar_arrive_expect_tx(&ss->res_bar[ew][b ^ 1], chunk_bytes);
+                    tma_load_2d(ss->epi_buf[ew][b ^ 1], &map_res, &ss->res_bar[ew][b ^ 1],
+                                (int)(nt % p.tiles_n) * p.tile_n + col0 + nc * 32,
+                                (int)((nt / p.tiles_n) * TILE_M + q * 32));
+                  }
+                }
+              }
+              k++;
+            }
+          }
+        }
+        __syncwarp();   // scale/shift of this tile have been read by every lane
+      }
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    } else {
+      // ------------------------------------------------------------------ plain epilogue
+    const int nchunks = ncols >> 4;
     float (*stg)[20] = ss->epi_stage[ew];
     // After the transpose through shared memory a lane owns 4 consecutive columns of 4 rows, so that a
     // warp-wide access touches 8 rows x 64 contiguous bytes instead of 32 rows x 16 bytes.
     const int tr = lane >> 2;                     // rows tr, tr+8, tr+16, tr+24 of the warp's 32
     const int tc = (lane & 3) * 4;                // first of this lane's 4 columns inside a 16-column chunk
     const bool vec = (p.N & 3) == 0;
-    int64_t seg = 0;
-    bool ok = true;
     for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int64_t mrow0 = (tile / p.tiles_n) * TILE_M + q * 32;   // first row of this warp
       const int nbase = (int)(tile % p.tiles_n) * p.tile_n + col0;
@@ -728,6 +871,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         }
       }
     }
+    }
   }
 
   // ------------------------------------------------------------------------------- teardown
@@ -822,6 +966,21 @@ int encode_map(TcState* st, CUtensorMap* map, float* base, int64_t rows, int64_t
   CUresult r = st->encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+// [rows, cols] fp32 matrix with a row pitch of `pitch` elements, cut into boxes of 32 rows x cw columns
+// (128B-swizzled when a box row is 128 bytes).
+int encode_rows_map(TcState* st, CUtensorMap* map, const float* base, int64_t rows, int64_t cols, int64_t pitch,
+                    int cw) {
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch * 4};
+  cuuint32_t box[2] = {(cuuint32_t)cw, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = st->encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          cw == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : (int)r;
 }
 
@@ -951,13 +1110,24 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
   }
   int64_t tiles = p.tiles_m * p.tiles_n;
   int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
+  TcState* st = tc_state(ctx);
+  // output and residual as [M, N] matrices cut into 32-row x cw-column boxes for the epilogue warps
+  CUtensorMap map_y = we->map_hi, map_res = we->map_hi;
+  {
+    const int ncols = p.tile_n / 2, cw = ncols < 32 ? ncols : 32;
+    bool can = (p.N % 4 == 0) && p.M < (1ll << 31) && !(p.dbg & 64) &&
+               encode_rows_map(st, &map_y, y, p.M, p.N, p.N, cw) == 0;
+    if (can && p.residual)
+      can = p.res_stride % 4 == 0 && encode_rows_map(st, &map_res, p.residual, p.M, p.N, p.res_stride, cw) == 0;
+    p.tma_epi = can ? 1 : 0;
+  }
   CUtensorMap map_a;
-  if (encode_a_map(tc_state(ctx), p, x, &map_a))
-    tc_igemm_kernel<true><<<grid, NUM_THREADS, sizeof(SharedStorage) + 1024, ctx->stream>>>(p, x, we->map_hi,
-                                                                                            we->map_lo, map_a, y);
+  const size_t smem = sizeof(SharedStorage) + 1024;
+  if (encode_a_map(st, p, x, &map_a))
+    tc_igemm_kernel<true><<<grid, NUM_THREADS, smem, ctx->stream>>>(p, x, we->map_hi, we->map_lo, map_a, map_y, map_res, y);
   else
-    tc_igemm_kernel<false><<<grid, NUM_THREADS, sizeof(SharedStorage) + 1024, ctx->stream>>>(p, x, we->map_hi,
-                                                                                             we->map_lo, we->map_hi, y);
+    tc_igemm_kernel<false><<<grid, NUM_THREADS, smem, ctx->stream>>>(p, x, we->map_hi, we->map_lo, we->map_hi, map_y,
+                                                                     map_res, y);
   ctx->n_tc_launch++;
   return wdc_check_launch(ctx, "tc_igemm_kernel");
 }

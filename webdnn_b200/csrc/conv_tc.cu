@@ -332,6 +332,13 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     }
     ss->ktab[kb] = e;
   }
+  if (kTmaA && p.c4) {
+    // 4-channel mode: planes of taps past the filter width are never loaded; their weights are zero,
+    // so the operand only has to be finite
+    for (int i = threadIdx.x; i < A_STAGES * A_TILE_BYTES / 16; i += NUM_THREADS)
+      reinterpret_cast<float4*>(ss->a_raw[0])[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
   if (warp == MMA_WARP) {
     // all 512 columns: NBUF segment accumulators + STAGES x (A_hi, A_lo)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&ss->tmem_base)),
@@ -356,7 +363,9 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     const int64_t my_tiles = (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
     const int64_t items = my_tiles * p.kblocks;
     const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)TMEM_A_COL0;
-    const uint32_t row_off = (uint32_t)row * 128u;
+    // normal mode: 128-byte rows, 16-byte chunks XOR-swizzled by the row; 4-channel mode: 8 planes
+    // (one per filter tap of the row) of 128 rows x 16 bytes
+    const uint32_t row_off = (uint32_t)row * (p.c4 ? 16u : 128u);
     const uint32_t sw = (uint32_t)(row & 7);
     int stage = 0, as = 0;
     uint32_t phase = 0, aphase = 0;
@@ -365,7 +374,8 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       float4 v[8];
       const unsigned char* tile = ss->a_raw[as] + row_off;
 #pragma unroll
-      for (int j = 0; j < 8; j++) v[j] = *reinterpret_cast<const float4*>(tile + (((uint32_t)j ^ sw) << 4));
+      for (int j = 0; j < 8; j++)
+        v[j] = *reinterpret_cast<const float4*>(tile + (p.c4 ? (uint32_t)j * (TILE_M * 16u) : (((uint32_t)j ^ sw) << 4)));
       if (!mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 12)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t a_hi = lane_base + (uint32_t)(stage * 64);
@@ -413,17 +423,27 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         const int tap = rot / p.cblocks;
         int c0 = (rot - tap * p.cblocks) * BLOCK_K;
         int ky = tap / p.k_w, kx = tap - ky * p.k_w;
+        if (p.c4) ky = rot;
         for (int kb = 0; kb < p.kblocks; kb++) {
           if (!mbar_wait(&ss->a_empty_bar[stage], phase ^ 1, ss, p.status, 22)) { ok = false; break; }
-          mbar_arrive_expect_tx(&ss->a_full_bar[stage], (uint32_t)A_TILE_BYTES);
-          tma_load_im2col(ss->a_raw[stage], &map_a, &ss->a_full_bar[stage], c0, cw, ch, (int)n, kx * p.dil_w,
-                          ky * p.dil_h);
-          c0 += BLOCK_K;
-          if (c0 >= p.ch_in) {
-            c0 = 0;
-            if (++kx == p.k_w) {
-              kx = 0;
-              if (++ky == p.k_h) ky = 0;
+          if (p.c4) {
+            // K block = filter row ky; one load of 128 pixels x 4 channels per tap of the row
+            mbar_arrive_expect_tx(&ss->a_full_bar[stage], (uint32_t)(p.k_w * TILE_M * 16));
+            for (int j = 0; j < p.k_w; j++)
+              tma_load_im2col(ss->a_raw[stage] + j * (TILE_M * 16), &map_a, &ss->a_full_bar[stage], 0, cw, ch, (int)n,
+                              j * p.dil_w, ky * p.dil_h);
+            if (++ky == p.k_h) ky = 0;
+          } else {
+            mbar_arrive_expect_tx(&ss->a_full_bar[stage], (uint32_t)A_TILE_BYTES);
+            tma_load_im2col(ss->a_raw[stage], &map_a, &ss->a_full_bar[stage], c0, cw, ch, (int)n, kx * p.dil_w,
+                            ky * p.dil_h);
+            c0 += BLOCK_K;
+            if (c0 >= p.ch_in) {
+              c0 = 0;
+              if (++kx == p.k_w) {
+                kx = 0;
+                if (++ky == p.k_h) ky = 0;
+              }
             }
           }
           if (++stage == A_STAGES) { stage = 0; phase ^= 1; }
@@ -1068,7 +1088,8 @@ bool tc_ready(wdc_context* ctx) {
 // pixel), traversal strides = the convolution's strides.  Returns false when the geometry does not
 // fit the map's fields; the caller then launches the gathering kernel.
 bool encode_a_map(TcState* st, const TcProblem& p, const float* x, CUtensorMap* map) {
-  if (!st->encode_im2col || p.c4 || (p.dbg & 32)) return false;
+  if (!st->encode_im2col || (p.dbg & 32)) return false;
+  if (p.c4 && p.k_w > 8) return false;
   const int64_t hw = (int64_t)p.out_h * p.out_w;
   const int64_t images = (p.M + hw - 1) / hw;
   const int lower[2] = {-p.pad_l, -p.pad_t};
@@ -1085,7 +1106,8 @@ bool encode_a_map(TcState* st, const TcProblem& p, const float* x, CUtensorMap* 
   if (strides[2] >= (1ull << 40)) return false;
   cuuint32_t estr[4] = {1, (cuuint32_t)p.stride_w, (cuuint32_t)p.stride_h, 1};
   CUresult r = st->encode_im2col(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)x, dims, strides, lower, upper,
-                                 BLOCK_K, TILE_M, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 p.c4 ? 4 : BLOCK_K, TILE_M, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 p.c4 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }

@@ -16,22 +16,32 @@ import numpy as np
 from .backend import CPUTensor, WebDNNCudaContext
 from .lib import ConvDesc
 
-# name, ch_in, ch_out, input size, kernel, stride, pad, residual
+# name, ch_in, ch_out, input size, kernel, stride, pad, residual, occurrences in ResNet-50 v1.5
 LAYERS = [
-    ("stem 7x7 3->64 s2", 3, 64, 224, 7, 2, 3, 0),
-    ("l1.c1 1x1 64->64", 64, 64, 56, 1, 1, 0, 0),
-    ("l1.c2 3x3 64->64", 64, 64, 56, 3, 1, 1, 0),
-    ("l1.c3 1x1 64->256 +res", 64, 256, 56, 1, 1, 0, 1),
-    ("l1.c1b 1x1 256->64", 256, 64, 56, 1, 1, 0, 0),
-    ("l2.c2 3x3 128->128 s2", 128, 128, 56, 3, 2, 1, 0),
-    ("l2.c2b 3x3 128->128", 128, 128, 28, 3, 1, 1, 0),
-    ("l2.c3 1x1 128->512 +res", 128, 512, 28, 1, 1, 0, 1),
-    ("l3.c1 1x1 1024->256", 1024, 256, 14, 1, 1, 0, 0),
-    ("l3.c2 3x3 256->256", 256, 256, 14, 3, 1, 1, 0),
-    ("l3.c3 1x1 256->1024 +res", 256, 1024, 14, 1, 1, 0, 1),
-    ("l4.c1 1x1 2048->512", 2048, 512, 7, 1, 1, 0, 0),
-    ("l4.c2 3x3 512->512", 512, 512, 7, 3, 1, 1, 0),
-    ("l4.c3 1x1 512->2048 +res", 512, 2048, 7, 1, 1, 0, 1),
+    ("stem 7x7 3->64 s2", 3, 64, 224, 7, 2, 3, 0, 1),
+    ("l1.c1 1x1 64->64", 64, 64, 56, 1, 1, 0, 0, 1),
+    ("l1.c2 3x3 64->64", 64, 64, 56, 3, 1, 1, 0, 3),
+    ("l1.c3 1x1 64->256 +res", 64, 256, 56, 1, 1, 0, 1, 3),
+    ("l1.ds 1x1 64->256", 64, 256, 56, 1, 1, 0, 0, 1),
+    ("l1.c1b 1x1 256->64", 256, 64, 56, 1, 1, 0, 0, 2),
+    ("l2.c1 1x1 256->128 @56", 256, 128, 56, 1, 1, 0, 0, 1),
+    ("l2.c2 3x3 128->128 s2", 128, 128, 56, 3, 2, 1, 0, 1),
+    ("l2.c2b 3x3 128->128", 128, 128, 28, 3, 1, 1, 0, 3),
+    ("l2.c3 1x1 128->512 +res", 128, 512, 28, 1, 1, 0, 1, 4),
+    ("l2.ds 1x1 256->512 s2", 256, 512, 56, 1, 2, 0, 0, 1),
+    ("l2.c1b 1x1 512->128", 512, 128, 28, 1, 1, 0, 0, 3),
+    ("l3.c1a 1x1 512->256 @28", 512, 256, 28, 1, 1, 0, 0, 1),
+    ("l3.c2a 3x3 256->256 s2", 256, 256, 28, 3, 2, 1, 0, 1),
+    ("l3.c1 1x1 1024->256", 1024, 256, 14, 1, 1, 0, 0, 5),
+    ("l3.c2 3x3 256->256", 256, 256, 14, 3, 1, 1, 0, 5),
+    ("l3.c3 1x1 256->1024 +res", 256, 1024, 14, 1, 1, 0, 1, 6),
+    ("l3.ds 1x1 512->1024 s2", 512, 1024, 28, 1, 2, 0, 0, 1),
+    ("l4.c1a 1x1 1024->512 @14", 1024, 512, 14, 1, 1, 0, 0, 1),
+    ("l4.c2a 3x3 512->512 s2", 512, 512, 14, 3, 2, 1, 0, 1),
+    ("l4.c1 1x1 2048->512", 2048, 512, 7, 1, 1, 0, 0, 2),
+    ("l4.c2 3x3 512->512", 512, 512, 7, 3, 1, 1, 0, 2),
+    ("l4.c3 1x1 512->2048 +res", 512, 2048, 7, 1, 1, 0, 1, 3),
+    ("l4.ds 1x1 1024->2048 s2", 1024, 2048, 14, 1, 2, 0, 0, 1),
 ]
 
 
@@ -47,7 +57,8 @@ def main() -> None:
     ctx.initialize()
     B = args.batch
     total = 0.0
-    for name, cin, cout, hw, k, s, pad, res in LAYERS:
+    weighted = 0.0
+    for name, cin, cout, hw, k, s, pad, res, count in LAYERS:
         if only and not any(name.startswith(o) for o in only):
             continue
         oh = (hw + 2 * pad - k) // s + 1
@@ -72,12 +83,13 @@ def main() -> None:
         flops = fl / args.reps
         nbytes = 4 * (x.length + y.length * (2 if res else 1) + w.length)
         total += ms
+        weighted += ms * count
         print(f"{name:28s} {ms * 1e3:8.1f} us  {flops / ms / 1e9:7.1f} TFLOP/s algorithmic "
               f"({3 * flops / ms / 1e9 / args.tf32_peak * 100:5.1f}% of TF32 issue)  {nbytes / ms / 1e6:7.0f} GB/s "
-              f"of algorithmic bytes")
+              f"of algorithmic bytes  x{count}")
         for t in (x, w, sc, sh, y) + ((r,) if r else ()):
             t.dispose()
-    print(f"sum {total:.3f} ms")
+    print(f"sum {total:.3f} ms; weighted by occurrences in the network {weighted:.3f} ms")
     ctx.close()
 
 

@@ -42,7 +42,9 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <cstring>
 #include <map>
+#include <set>
 
 #include "common.cuh"
 
@@ -81,7 +83,7 @@ struct TcProblem {
   int tile_n;         // 32, 64 or 128
   int tma_epi;        // 1: residual tiles and output tiles move by TMA (map_res, map_y)
   int c4;             // 1: input has 4 channels per pixel, one K block per filter row, chunk j = tap kx
-  int64_t tiles_m, tiles_n;
+  int tiles_m, tiles_n;   // their product fits 31 bits (checked on the host)
   // epilogue
   const float* scale;     // per channel or null
   const float* shift;     // per channel or null
@@ -113,8 +115,6 @@ struct __align__(1024) SharedStorage {
     unsigned char epi_buf[NUM_EPI_WARPS][2][EPI_BUF_BYTES];  // TMA epilogue: residual in, result out
     float epi_stage[NUM_EPI_WARPS][32][20];  // plain epilogue: per-warp transpose buffer, 32 rows x 16 columns (+4 pad)
   };
-  float epi_scale[NUM_EPI_WARPS][64];        // per-column multiplier and addend of the warp's columns
-  float epi_shift[NUM_EPI_WARPS][64];
   unsigned long long full_bar[STAGES];
   unsigned long long empty_bar[STAGES];
   unsigned long long seg_full_bar[NBUF];
@@ -291,7 +291,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
   extern __shared__ unsigned char smem_raw[];
   SharedStorage* ss = reinterpret_cast<SharedStorage*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t total_tiles = p.tiles_m * p.tiles_n;
+  const int total_tiles = p.tiles_m * p.tiles_n;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
@@ -360,7 +360,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     // tensor core ignores the low 13 bits of a tf32 operand, i.e. it truncates) and
     // lo = x - truncate(x), exact in fp32, as the low operand.
     const int row = threadIdx.x;
-    const int64_t my_tiles = (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+    const int64_t my_tiles = (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int64_t items = my_tiles * p.kblocks;
     const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)TMEM_A_COL0;
     // normal mode: 128-byte rows, 16-byte chunks XOR-swizzled by the row; 4-channel mode: 8 planes
@@ -407,14 +407,15 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     }
   } else if (kTmaA && warp == ATMA_WARP) {
     // ===================================================================== A loader (im2col TMA)
-    if (elect_one()) {
+    // One lane issues the loads; in 4-channel mode lane j issues the load of tap j of the filter row.
+    if (p.c4 ? lane < 8 : lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       const uint32_t hw = (uint32_t)p.out_h * (uint32_t)p.out_w;
       bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         // base pixel of the tile's first row
-        const int64_t m0 = (tile / p.tiles_n) * TILE_M;
+        const int64_t m0 = (int64_t)(tile / p.tiles_n) * TILE_M;
         const int64_t n = m0 / hw;
         const uint32_t rem = (uint32_t)(m0 - n * hw);
         const int oy = (int)(rem / (uint32_t)p.out_w), ox = (int)rem - oy * p.out_w;
@@ -428,10 +429,11 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
           if (!mbar_wait(&ss->a_empty_bar[stage], phase ^ 1, ss, p.status, 22)) { ok = false; break; }
           if (p.c4) {
             // K block = filter row ky; one load of 128 pixels x 4 channels per tap of the row
-            mbar_arrive_expect_tx(&ss->a_full_bar[stage], (uint32_t)(p.k_w * TILE_M * 16));
-            for (int j = 0; j < p.k_w; j++)
-              tma_load_im2col(ss->a_raw[stage] + j * (TILE_M * 16), &map_a, &ss->a_full_bar[stage], 0, cw, ch, (int)n,
-                              j * p.dil_w, ky * p.dil_h);
+            if (lane == 0) mbar_arrive_expect_tx(&ss->a_full_bar[stage], (uint32_t)(p.k_w * TILE_M * 16));
+            __syncwarp(0xffu);
+            if (lane < p.k_w)
+              tma_load_im2col(ss->a_raw[stage] + lane * (TILE_M * 16), &map_a, &ss->a_full_bar[stage], 0, cw, ch,
+                              (int)n, lane * p.dil_w, ky * p.dil_h);
             if (++ky == p.k_h) ky = 0;
           } else {
             mbar_arrive_expect_tx(&ss->a_full_bar[stage], (uint32_t)A_TILE_BYTES);
@@ -456,7 +458,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     // PREFETCH items ahead of the TMEM stores and cross tile boundaries, so the global load latency
     // is paid once per CTA, not once per tile.
     const int row = threadIdx.x;      // 0..127: tile row and TMEM lane of this thread
-    const int64_t my_tiles = (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+    const int64_t my_tiles = (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
     const int64_t items = my_tiles * p.kblocks;
     const uint32_t hw = (uint32_t)p.out_h * (uint32_t)p.out_w;
     const int64_t img_elems = (int64_t)p.in_h * p.in_w * p.ch_in;
@@ -464,12 +466,12 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     const float* rsrc = nullptr;      // address of input pixel (n, iy0, ix0, channel 0); null for rows past M
     int riy = 0, rix = 0;
     int ld_kb = p.kblocks;            // forces the row set-up on the first call
-    int64_t ld_tile = (int64_t)blockIdx.x - gridDim.x;
+    int ld_tile = (int)blockIdx.x - (int)gridDim.x;
     auto issue = [&](float4* dst) {
       if (ld_kb == p.kblocks) {       // next tile: locate this thread's output pixel
         ld_kb = 0;
         ld_tile += gridDim.x;
-        const int64_t m = (ld_tile / p.tiles_n) * TILE_M + row;
+        const int64_t m = (int64_t)(ld_tile / p.tiles_n) * TILE_M + row;
         if (m < p.M) {
           uint32_t n, rem;
           if (p.M <= 0x7fffffffll) {  // 32-bit division is several times cheaper
@@ -589,7 +591,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       uint32_t phase = 0;
       const uint32_t bytes = 2u * (uint32_t)p.tile_n * BLOCK_K * 4u;
       bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int n0 = (int)(tile % p.tiles_n) * p.tile_n;
         for (int kb = 0; kb < p.kblocks; kb++) {
           if (!mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 21)) { ok = false; break; }
@@ -610,7 +612,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       const uint32_t idesc = make_idesc(p.tile_n);
       int64_t seg = 0;  // segments issued by this CTA so far
       bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         uint32_t d_tmem = 0;
         int buf = 0;
         for (int kb = 0; kb < p.kblocks; kb++) {
@@ -669,31 +671,29 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       const uint32_t swz = cw == 32 ? (uint32_t)(lane & 7) : 0u;   // 128B swizzle only for 128-byte rows
       const uint32_t row_off = (uint32_t)lane * (uint32_t)cw * 4u;
       const bool use_res = p.residual != nullptr && !(p.dbg & 2);
-      float* sc_s = ss->epi_scale[ew];
-      float* sh_s = ss->epi_shift[ew];
       int64_t k = 0;                                    // chunks handled by this warp so far
-      if (use_res && lane == 0 && (int64_t)blockIdx.x < total_tiles) {
-        const int64_t t0 = blockIdx.x;
+      if (use_res && lane == 0 && (int)blockIdx.x < total_tiles) {
+        const int t0 = blockIdx.x;
         mbar_arrive_expect_tx(&ss->res_bar[ew][0], chunk_bytes);
         tma_load_2d(ss->epi_buf[ew][0], &map_res, &ss->res_bar[ew][0], (int)(t0 % p.tiles_n) * p.tile_n + col0,
                     (int)((t0 / p.tiles_n) * TILE_M + q * 32));
       }
-      for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int64_t mrow0 = (tile / p.tiles_n) * TILE_M + q * 32;   // first row of this warp
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int64_t mrow0 = (int64_t)(tile / p.tiles_n) * TILE_M + q * 32;   // first row of this warp
         const int nbase = (int)(tile % p.tiles_n) * p.tile_n + col0;
-        for (int i = lane; i < ncols; i += 32) {
-          const int col = nbase + i;
-          float a = p.alpha, b = 0.f;
-          if (col < p.N) {
-            if (p.scale) a = __ldg(p.scale + col);
-            if (p.shift) b = p.shift_mul * __ldg(p.shift + col);
-          }
-          sc_s[i] = a;
-          sh_s[i] = b;
-        }
+        // The accumulators start at the per-column addend (bias / folded BatchNormalization shift); the
+        // per-column multiplier is already in the weights.  Warp-uniform 16-byte loads, in flight while
+        // the first segment is computed.
         float acc[64];
 #pragma unroll
-        for (int j = 0; j < 64; j++) acc[j] = 0.f;
+        for (int j = 0; j < 64; j += 4) {
+          float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (p.shift && j < ncols && nbase + j < p.N) b4 = __ldg(reinterpret_cast<const float4*>(p.shift + nbase + j));
+          acc[j] = p.shift_mul * b4.x;
+          acc[j + 1] = p.shift_mul * b4.y;
+          acc[j + 2] = p.shift_mul * b4.z;
+          acc[j + 3] = p.shift_mul * b4.w;
+        }
         for (int s = 0; s < nseg && ok; s++, seg++) {
           const int buf = (int)(seg % NBUF);
           ok = mbar_wait(&ss->seg_full_bar[buf], (uint32_t)((seg / NBUF) & 1), ss, p.status, 42);
@@ -725,26 +725,34 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
             if (use_res) ok = mbar_wait(&ss->res_bar[ew][b], (uint32_t)((k >> 1) & 1), ss, p.status, 43);
             __syncwarp();
             if (ok) {
+              // 4 cells (16 columns) at a time: residual reads first, then arithmetic and writes, so
+              // that the shared-memory reads of a batch do not queue behind the writes one by one.
 #pragma unroll
-              for (int j = 0; j < 8; j++) {
-                if (j * 4 < cw) {
-                  float4* cell = reinterpret_cast<float4*>(sbuf + row_off + (((uint32_t)j ^ swz) << 4));
-                  const float4 a4 = *reinterpret_cast<const float4*>(&sc_s[c * 32 + j * 4]);
-                  const float4 b4 = *reinterpret_cast<const float4*>(&sh_s[c * 32 + j * 4]);
-                  float o[4] = {fmaf(acc[c * 32 + j * 4 + 0], a4.x, b4.x), fmaf(acc[c * 32 + j * 4 + 1], a4.y, b4.y),
-                                fmaf(acc[c * 32 + j * 4 + 2], a4.z, b4.z), fmaf(acc[c * 32 + j * 4 + 3], a4.w, b4.w)};
+              for (int jb = 0; jb < 8; jb += 4) {
+                if (jb * 4 < cw) {
+                  float4 r4[4];
                   if (use_res) {
-                    const float4 r4 = *cell;
-                    o[0] = fmaf(p.res_mul, r4.x, o[0]);
-                    o[1] = fmaf(p.res_mul, r4.y, o[1]);
-                    o[2] = fmaf(p.res_mul, r4.z, o[2]);
-                    o[3] = fmaf(p.res_mul, r4.w, o[3]);
-                  }
-                  if (p.relu) {
 #pragma unroll
-                    for (int e = 0; e < 4; e++) o[e] = o[e] > 0.f ? o[e] : (o[e] == o[e] ? 0.f : o[e]);
+                    for (int j = 0; j < 4; j++)
+                      r4[j] = *reinterpret_cast<const float4*>(sbuf + row_off + (((uint32_t)(jb + j) ^ swz) << 4));
                   }
-                  *cell = make_float4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+                  for (int j = 0; j < 4; j++) {
+                    const float* av = &acc[c * 32 + (jb + j) * 4];
+                    float o[4] = {av[0], av[1], av[2], av[3]};
+                    if (use_res) {
+                      o[0] = fmaf(p.res_mul, r4[j].x, o[0]);
+                      o[1] = fmaf(p.res_mul, r4[j].y, o[1]);
+                      o[2] = fmaf(p.res_mul, r4[j].z, o[2]);
+                      o[3] = fmaf(p.res_mul, r4[j].w, o[3]);
+                    }
+                    if (p.relu) {
+#pragma unroll
+                      for (int e = 0; e < 4; e++) o[e] = o[e] > 0.f ? o[e] : (o[e] == o[e] ? 0.f : o[e]);
+                    }
+                    *reinterpret_cast<float4*>(sbuf + row_off + (((uint32_t)(jb + j) ^ swz) << 4)) =
+                        make_float4(o[0], o[1], o[2], o[3]);
+                  }
                 }
               }
               asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -755,7 +763,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the other buffer's store has read it
                 if (use_res) {
-                  int64_t nt = tile;
+                  int nt = tile;
                   int nc = c + 1;
                   if (nc == nch) { nc = 0; nt += gridDim.x; }
                   if (nt < total_tiles) {
@@ -770,7 +778,6 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
             }
           }
         }
-        __syncwarp();   // scale/shift of this tile have been read by every lane
       }
       if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     } else {
@@ -782,8 +789,8 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     const int tr = lane >> 2;                     // rows tr, tr+8, tr+16, tr+24 of the warp's 32
     const int tc = (lane & 3) * 4;                // first of this lane's 4 columns inside a 16-column chunk
     const bool vec = (p.N & 3) == 0;
-    for (int64_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      const int64_t mrow0 = (tile / p.tiles_n) * TILE_M + q * 32;   // first row of this warp
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int64_t mrow0 = (int64_t)(tile / p.tiles_n) * TILE_M + q * 32;   // first row of this warp
       const int nbase = (int)(tile % p.tiles_n) * p.tile_n + col0;
       float acc[64];
 #pragma unroll
@@ -904,12 +911,14 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
 }
 
 // ---------------------------------------------------------------------------- host side
+// Row r of the weight matrix is multiplied by alpha * scale[r] (scale null = 1) before the split, so
+// that the kernel's epilogue has no per-channel multiply left.
 __global__ void split_tf32_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo,
-                                  int64_t n) {
+                                  int64_t n, int64_t k, const float* __restrict__ scale, float alpha) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t step = (int64_t)gridDim.x * blockDim.x;
   for (; i < n; i += step) {
-    float v = w[i];
+    float v = w[i] * (scale ? alpha * scale[i / k] : alpha);
     float h = to_tf32(v);
     hi[i] = h;
     lo[i] = to_tf32(v - h);
@@ -932,7 +941,8 @@ __global__ void pad_channels4_kernel(const float* __restrict__ x, float* __restr
 }
 // w [n][k_h][k_w][cin] -> hi/lo of [n][k_h][8][4] (zero where kx >= k_w or c >= cin)
 __global__ void split_tf32_c4_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo,
-                                     int64_t rows, int k_h, int k_w, int cin) {
+                                     int64_t rows, int k_h, int k_w, int cin, const float* __restrict__ scale,
+                                     float alpha) {
   int64_t total = rows * k_h * 32;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t step = (int64_t)gridDim.x * blockDim.x;
@@ -940,6 +950,7 @@ __global__ void split_tf32_c4_kernel(const float* __restrict__ w, float* __restr
     int c = (int)(i & 3), kx = (int)((i >> 2) & 7);
     int64_t r = i >> 5;  // n * k_h + ky
     float v = (kx < k_w && c < cin) ? w[(r * k_w + kx) * cin + c] : 0.f;
+    v *= scale ? alpha * scale[r / k_h] : alpha;
     float h = to_tf32(v);
     hi[i] = h;
     lo[i] = to_tf32(v - h);
@@ -955,6 +966,17 @@ typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+struct WeightKey {
+  const void* w;
+  const void* scale;
+  uint32_t alpha_bits;
+  bool operator<(const WeightKey& o) const {
+    if (w != o.w) return w < o.w;
+    if (scale != o.scale) return scale < o.scale;
+    return alpha_bits < o.alpha_bits;
+  }
+};
+
 struct WeightEntry {
   float* hi = nullptr;
   float* lo = nullptr;
@@ -968,7 +990,8 @@ struct TcState {
   EncodeIm2colFn encode_im2col = nullptr;  // may stay null: then every launch gathers A itself
   bool unavailable = false;
   bool attr_set = false;
-  std::map<const void*, WeightEntry> weights;
+  std::map<WeightKey, WeightEntry> weights;
+  std::set<const void*> scales;  // buffers used as a key's scale: a write to one evicts those entries
 };
 
 TcState* tc_state(wdc_context* ctx) {
@@ -1005,10 +1028,12 @@ int encode_rows_map(TcState* st, CUtensorMap* map, const float* base, int64_t ro
 }
 
 // Looks up (or builds) the hi/lo split and the tensor maps of a [rows, k] K-major weight matrix.
-int get_weight(wdc_context* ctx, const float* w, int64_t rows, int64_t k, WeightEntry** out, int c4_kh = 0,
-               int c4_kw = 0, int c4_cin = 0) {
+int get_weight(wdc_context* ctx, const float* w, const float* scale, float alpha, int64_t rows, int64_t k,
+               WeightEntry** out, int c4_kh = 0, int c4_kw = 0, int c4_cin = 0) {
   TcState* st = tc_state(ctx);
-  auto it = st->weights.find(w);
+  WeightKey key = {w, scale, 0};
+  memcpy(&key.alpha_bits, &alpha, 4);
+  auto it = st->weights.find(key);
   if (it != st->weights.end() && it->second.rows == rows && it->second.k == k) {
     *out = &it->second;
     return WDC_OK;
@@ -1031,9 +1056,9 @@ int get_weight(wdc_context* ctx, const float* w, int64_t rows, int64_t k, Weight
   }
   if (c4_kh)
     split_tf32_c4_kernel<<<grid_for(ctx, rows * k, 256, 8), 256, 0, ctx->stream>>>(w, e.hi, e.lo, rows, c4_kh, c4_kw,
-                                                                                    c4_cin);
+                                                                                    c4_cin, scale, alpha);
   else
-    split_tf32_kernel<<<grid_for(ctx, rows * k, 256, 8), 256, 0, ctx->stream>>>(w, e.hi, e.lo, rows * k);
+    split_tf32_kernel<<<grid_for(ctx, rows * k, 256, 8), 256, 0, ctx->stream>>>(w, e.hi, e.lo, rows * k, k, scale, alpha);
   s = wdc_check_launch(ctx, "split_tf32_kernel");
   int r1 = encode_map(st, &e.map_hi, e.hi, rows, k, e.tile_n);
   int r2 = encode_map(st, &e.map_lo, e.lo, rows, k, e.tile_n);
@@ -1044,7 +1069,8 @@ int get_weight(wdc_context* ctx, const float* w, int64_t rows, int64_t k, Weight
     return wdc_fail(ctx, WDC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d, %d) for a [%lld, %lld] weight", r1, r2,
                     (long long)rows, (long long)k);
   }
-  auto ins = st->weights.emplace(w, e);
+  auto ins = st->weights.emplace(key, e);
+  if (scale) st->scales.insert(scale);
   *out = &ins.first->second;
   return WDC_OK;
 }
@@ -1115,11 +1141,14 @@ bool encode_a_map(TcState* st, const TcProblem& p, const float* x, CUtensorMap* 
 int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, float* y, int c4_kw = 0,
               int c4_cin = 0) {
   WeightEntry* we = nullptr;
-  int s = get_weight(ctx, w, p.N, p.K, &we, p.c4 ? p.K / 32 : 0, c4_kw, c4_cin);
+  int s = get_weight(ctx, w, p.scale, p.alpha, p.N, p.K, &we, p.c4 ? p.K / 32 : 0, c4_kw, c4_cin);
   if (s != WDC_OK) return s;
+  p.scale = nullptr;  // folded into the split weights
+  p.alpha = 1.f;
   p.tile_n = we->tile_n;
-  p.tiles_m = ceil_div64(p.M, TILE_M);
-  p.tiles_n = ceil_div64(p.N, p.tile_n);
+  if (ceil_div64(p.M, TILE_M) * ceil_div64(p.N, we->tile_n) >= (1ll << 31) - 65536) return WDC_ERR_UNSUPPORTED;
+  p.tiles_m = (int)ceil_div64(p.M, TILE_M);
+  p.tiles_n = (int)ceil_div64(p.N, p.tile_n);
   p.kblocks = (p.K + BLOCK_K - 1) / BLOCK_K;
   p.status = ctx->status_word;
   {
@@ -1130,14 +1159,14 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
     }
     p.dbg = dbg;
   }
-  int64_t tiles = p.tiles_m * p.tiles_n;
+  int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   TcState* st = tc_state(ctx);
   // output and residual as [M, N] matrices cut into 32-row x cw-column boxes for the epilogue warps
   CUtensorMap map_y = we->map_hi, map_res = we->map_hi;
   {
     const int ncols = p.tile_n / 2, cw = ncols < 32 ? ncols : 32;
-    bool can = (p.N % 4 == 0) && p.M < (1ll << 31) && !(p.dbg & 64) &&
+    bool can = (p.N % 4 == 0) && p.M < (1ll << 31) && !(p.dbg & 64) && (((uintptr_t)p.scale | (uintptr_t)p.shift) & 15) == 0 &&
                encode_rows_map(st, &map_y, y, p.M, p.N, p.N, cw) == 0;
     if (can && p.residual)
       can = p.res_stride % 4 == 0 && encode_rows_map(st, &map_res, p.residual, p.M, p.N, p.res_stride, cw) == 0;
@@ -1161,12 +1190,24 @@ bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 void wdc_tc_evict(wdc_context* ctx, const void* ptr) {
   if (!ctx->tc_state) return;
   TcState* st = (TcState*)ctx->tc_state;
-  auto it = st->weights.find(ptr);
-  if (it == st->weights.end()) return;
-  WeightEntry e = it->second;
-  st->weights.erase(it);
-  wdc_free(ctx, e.hi);
-  wdc_free(ctx, e.lo);
+  // entries built from this buffer, as weights or as the per-channel scale
+  for (auto it = st->weights.lower_bound(WeightKey{ptr, nullptr, 0}); it != st->weights.end() && it->first.w == ptr;) {
+    WeightEntry e = it->second;
+    it = st->weights.erase(it);
+    wdc_free(ctx, e.hi);
+    wdc_free(ctx, e.lo);
+  }
+  if (st->scales.count(ptr)) {
+    for (auto it = st->weights.begin(); it != st->weights.end();) {
+      if (it->first.scale == ptr) {
+        WeightEntry e = it->second;
+        it = st->weights.erase(it);
+        wdc_free(ctx, e.hi);
+        wdc_free(ctx, e.lo);
+      } else ++it;
+    }
+    st->scales.erase(ptr);
+  }
 }
 
 void wdc_tc_destroy(wdc_context* ctx) {

@@ -68,6 +68,7 @@ constexpr int EPI_BUF_BYTES = 32 * 32 * 4;   // epilogue staging: 32 rows x 32 c
 constexpr int TMEM_A_COL0 = NBUF * 128;  // first column of the A stages
 constexpr int W_TILE_BYTES = 128 * BLOCK_K * 4;  // 16 KB (hi) + 16 KB (lo) per stage
 constexpr int PREFETCH = 2;           // K blocks of A held in registers per thread
+constexpr int SHIFT_TAB = 2048;        // per-column addends kept in shared memory when N fits
 constexpr int KTAB = 512;             // K blocks whose gather offsets are tabulated in shared memory
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
@@ -115,6 +116,7 @@ struct __align__(1024) SharedStorage {
     unsigned char epi_buf[NUM_EPI_WARPS][2][EPI_BUF_BYTES];  // TMA epilogue: residual in, result out
     float epi_stage[NUM_EPI_WARPS][32][20];  // plain epilogue: per-warp transpose buffer, 32 rows x 16 columns (+4 pad)
   };
+  float shift_tab[SHIFT_TAB];                // shift_mul * shift[col] (TMA epilogue, N <= SHIFT_TAB)
   unsigned long long full_bar[STAGES];
   unsigned long long empty_bar[STAGES];
   unsigned long long seg_full_bar[NBUF];
@@ -191,6 +193,12 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+// max(x, 0) that keeps a NaN input (Math.max semantics), one instruction
+__device__ __forceinline__ float relu_nan(float x) {
+  float r;
+  asm("max.NaN.f32 %0, %1, 0f00000000;" : "=f"(r) : "f"(x));
+  return r;
+}
 __device__ __forceinline__ float to_tf32(float x) {
   uint32_t r;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
@@ -332,6 +340,8 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     }
     ss->ktab[kb] = e;
   }
+  if (p.tma_epi && p.shift && p.N <= SHIFT_TAB)
+    for (int i = threadIdx.x; i < p.N; i += NUM_THREADS) ss->shift_tab[i] = p.shift_mul * __ldg(p.shift + i);
   if (kTmaA && p.c4) {
     // 4-channel mode: planes of taps past the filter width are never loaded; their weights are zero,
     // so the operand only has to be finite
@@ -682,17 +692,24 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         const int64_t mrow0 = (int64_t)(tile / p.tiles_n) * TILE_M + q * 32;   // first row of this warp
         const int nbase = (int)(tile % p.tiles_n) * p.tile_n + col0;
         // The accumulators start at the per-column addend (bias / folded BatchNormalization shift); the
-        // per-column multiplier is already in the weights.  Warp-uniform 16-byte loads, in flight while
-        // the first segment is computed.
+        // per-column multiplier is already in the weights.  Warp-uniform 16-byte loads from the table in
+        // shared memory (from global memory when N exceeds the table).
         float acc[64];
 #pragma unroll
         for (int j = 0; j < 64; j += 4) {
           float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (p.shift && j < ncols && nbase + j < p.N) b4 = __ldg(reinterpret_cast<const float4*>(p.shift + nbase + j));
-          acc[j] = p.shift_mul * b4.x;
-          acc[j + 1] = p.shift_mul * b4.y;
-          acc[j + 2] = p.shift_mul * b4.z;
-          acc[j + 3] = p.shift_mul * b4.w;
+          if (p.shift && j < ncols && nbase + j < p.N) {
+            if (p.N <= SHIFT_TAB) {
+              b4 = *reinterpret_cast<const float4*>(&ss->shift_tab[nbase + j]);
+            } else {
+              b4 = __ldg(reinterpret_cast<const float4*>(p.shift + nbase + j));
+              b4.x *= p.shift_mul; b4.y *= p.shift_mul; b4.z *= p.shift_mul; b4.w *= p.shift_mul;
+            }
+          }
+          acc[j] = b4.x;
+          acc[j + 1] = b4.y;
+          acc[j + 2] = b4.z;
+          acc[j + 3] = b4.w;
         }
         for (int s = 0; s < nseg && ok; s++, seg++) {
           const int buf = (int)(seg % NBUF);
@@ -748,7 +765,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
                     }
                     if (p.relu) {
 #pragma unroll
-                      for (int e = 0; e < 4; e++) o[e] = o[e] > 0.f ? o[e] : (o[e] == o[e] ? 0.f : o[e]);
+                      for (int e = 0; e < 4; e++) o[e] = relu_nan(o[e]);
                     }
                     *reinterpret_cast<float4*>(sbuf + row_off + (((uint32_t)(jb + j) ^ swz) << 4)) =
                         make_float4(o[0], o[1], o[2], o[3]);
@@ -880,7 +897,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
                 for (int e = 0; e < 4; e++) {
                   float t = fmaf(o[e], sc[e], sh[e]);
                   if (p.residual) t = fmaf(p.res_mul, rr[e], t);
-                  if (p.relu) t = t > 0.f ? t : (t == t ? 0.f : t);
+                  if (p.relu) t = relu_nan(t);
                   o[e] = t;
                 }
                 float* yp = y + m * (int64_t)p.N + col;

@@ -116,7 +116,7 @@ struct __align__(1024) SharedStorage {
     unsigned char epi_buf[NUM_EPI_WARPS][2][EPI_BUF_BYTES];  // TMA epilogue: residual in, result out
     float epi_stage[NUM_EPI_WARPS][32][20];  // plain epilogue: per-warp transpose buffer, 32 rows x 16 columns (+4 pad)
   };
-  float shift_tab[SHIFT_TAB];                // shift_mul * shift[col] (TMA epilogue, N <= SHIFT_TAB)
+  float shift_tab[SHIFT_TAB + 128];          // shift_mul * shift[col], zero past N (TMA epilogue, N <= SHIFT_TAB)
   unsigned long long full_bar[STAGES];
   unsigned long long empty_bar[STAGES];
   unsigned long long seg_full_bar[NBUF];
@@ -340,8 +340,9 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     }
     ss->ktab[kb] = e;
   }
-  if (p.tma_epi && p.shift && p.N <= SHIFT_TAB)
-    for (int i = threadIdx.x; i < p.N; i += NUM_THREADS) ss->shift_tab[i] = p.shift_mul * __ldg(p.shift + i);
+  if (p.tma_epi && p.N <= SHIFT_TAB)
+    for (int i = threadIdx.x; i < SHIFT_TAB + 128; i += NUM_THREADS)
+      ss->shift_tab[i] = (p.shift && i < p.N) ? p.shift_mul * __ldg(p.shift + i) : 0.f;
   if (kTmaA && p.c4) {
     // 4-channel mode: planes of taps past the filter width are never loaded; their weights are zero,
     // so the operand only has to be finite
@@ -695,21 +696,29 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         // per-column multiplier is already in the weights.  Warp-uniform 16-byte loads from the table in
         // shared memory (from global memory when N exceeds the table).
         float acc[64];
+        if (p.N <= SHIFT_TAB) {
+          // branch-free: the table is zero past N, and 64 entries past any warp's first column exist
 #pragma unroll
-        for (int j = 0; j < 64; j += 4) {
-          float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (p.shift && j < ncols && nbase + j < p.N) {
-            if (p.N <= SHIFT_TAB) {
-              b4 = *reinterpret_cast<const float4*>(&ss->shift_tab[nbase + j]);
-            } else {
+          for (int j = 0; j < 64; j += 4) {
+            const float4 b4 = *reinterpret_cast<const float4*>(&ss->shift_tab[nbase + j]);
+            acc[j] = b4.x;
+            acc[j + 1] = b4.y;
+            acc[j + 2] = b4.z;
+            acc[j + 3] = b4.w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 64; j += 4) {
+            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p.shift && j < ncols && nbase + j < p.N) {
               b4 = __ldg(reinterpret_cast<const float4*>(p.shift + nbase + j));
               b4.x *= p.shift_mul; b4.y *= p.shift_mul; b4.z *= p.shift_mul; b4.w *= p.shift_mul;
             }
+            acc[j] = b4.x;
+            acc[j + 1] = b4.y;
+            acc[j + 2] = b4.z;
+            acc[j + 3] = b4.w;
           }
-          acc[j] = b4.x;
-          acc[j + 1] = b4.y;
-          acc[j + 2] = b4.z;
-          acc[j + 3] = b4.w;
         }
         for (int s = 0; s < nseg && ok; s++, seg++) {
           const int buf = (int)(seg % NBUF);

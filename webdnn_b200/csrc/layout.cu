@@ -57,6 +57,37 @@ __global__ void __launch_bounds__(256) transpose_tile_kernel(const uint32_t* __r
   }
 }
 
+// Same transpose when one side is narrow (fewer than 8 columns or rows, e.g. the 3 channels of an
+// image batch): one thread per position of the long axis, which is contiguous in src (narrow cols)
+// or in dst (narrow rows), so that side is coalesced per step and the other is covered by the
+// thread's short run of consecutive words.
+__global__ void __launch_bounds__(256) transpose_narrow_cols_kernel(const uint32_t* __restrict__ src,
+                                                                    uint32_t* __restrict__ dst, int64_t batch,
+                                                                    int64_t rows, int cols) {
+  int64_t n = batch * rows;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) {
+    int64_t b = i / rows, r = i - b * rows;
+    const uint32_t* s = src + b * rows * cols + r;
+    uint32_t* d = dst + i * cols;
+    for (int c = 0; c < cols; c++) d[c] = __ldg(s + (int64_t)c * rows);
+  }
+}
+__global__ void __launch_bounds__(256) transpose_narrow_rows_kernel(const uint32_t* __restrict__ src,
+                                                                    uint32_t* __restrict__ dst, int64_t batch,
+                                                                    int rows, int64_t cols) {
+  int64_t n = batch * cols;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < n; i += step) {
+    int64_t b = i / cols, c = i - b * cols;
+    const uint32_t* s = src + (b * cols + c) * rows;
+    uint32_t* d = dst + b * rows * cols + c;
+    for (int r = 0; r < rows; r++) d[(int64_t)r * cols] = __ldg(s + r);
+  }
+}
+
 extern "C" int wdc_strided_copy(wdc_context* ctx, const void* src, void* dst, int ndim,
                                 const int64_t* dims, const int64_t* sstr, int64_t src_off,
                                 const int64_t* dstr, int64_t dst_off) {
@@ -91,9 +122,18 @@ extern "C" int wdc_strided_copy(wdc_context* ctx, const void* src, void* dst, in
   if (m == 0 || (m == 1 && ms[0] == 1 && mt[0] == 1)) return wdc_copy(ctx, d, s, n * 4);
   // batched 2-D transpose: dst dense [b][r][c], src [b][c][r]
   if ((m == 2 || m == 3) && mt[m - 1] == 1 && mt[m - 2] == md[m - 1] && ms[m - 2] == 1 &&
-      ms[m - 1] == md[m - 2] && md[m - 1] >= 8 && md[m - 2] >= 8 &&
-      (m == 2 || (mt[0] == md[1] * md[2] && ms[0] == md[1] * md[2]))) {
+      ms[m - 1] == md[m - 2] && (m == 2 || (mt[0] == md[1] * md[2] && ms[0] == md[1] * md[2]))) {
     int64_t batch = m == 3 ? md[0] : 1, rows = md[m - 2], cols = md[m - 1];
+    if (cols < 8) {
+      transpose_narrow_cols_kernel<<<grid_for(ctx, batch * rows, 256, 8), 256, 0, ctx->stream>>>(s, d, batch, rows,
+                                                                                                 (int)cols);
+      return wdc_check_launch(ctx, "transpose_narrow_cols_kernel");
+    }
+    if (rows < 8) {
+      transpose_narrow_rows_kernel<<<grid_for(ctx, batch * cols, 256, 8), 256, 0, ctx->stream>>>(s, d, batch,
+                                                                                                 (int)rows, cols);
+      return wdc_check_launch(ctx, "transpose_narrow_rows_kernel");
+    }
     int64_t ntiles = batch * ((rows + 31) / 32) * ((cols + 31) / 32);
     int64_t cap = (int64_t)ctx->sm_count * 16;
     int grid = (int)(ntiles < cap ? ntiles : cap);

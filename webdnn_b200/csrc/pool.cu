@@ -70,6 +70,50 @@ __global__ void __launch_bounds__(256) pool2d_kernel(wdc_pool_desc d, const floa
   }
 }
 
+// Channels-last max pool with a window of at most 3x3 (dilation 1), dense NHWC on both sides, fewer
+// than 2^31 elements: 32-bit index arithmetic, and the window's loads are issued together (out-of-
+// image taps re-read the clamped pixel with a -inf substitute) before any comparison.
+// One thread = 4 channels of one output pixel.
+template <int KH, int KW>
+__global__ void __launch_bounds__(256) maxpool_cl_small_kernel(const float4* __restrict__ x, float4* __restrict__ y,
+                                                               int n_out, int chv, int in_h, int in_w, int out_h,
+                                                               int out_w, int stride_h, int stride_w, int pad_t,
+                                                               int pad_l) {
+  const int step = gridDim.x * blockDim.x;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_out; i += step) {
+    int rem = i;
+    const int c = rem % chv; rem /= chv;
+    const int ox = rem % out_w; rem /= out_w;
+    const int oy = rem % out_h;
+    const int b = rem / out_h;
+    const int iy0 = oy * stride_h - pad_t, ix0 = ox * stride_w - pad_l;
+    float4 v[KH * KW];
+    bool in[KH * KW];
+#pragma unroll
+    for (int ky = 0; ky < KH; ky++) {
+#pragma unroll
+      for (int kx = 0; kx < KW; kx++) {
+        const int iy = iy0 + ky, ix = ix0 + kx;
+        const bool ok = (unsigned)iy < (unsigned)in_h && (unsigned)ix < (unsigned)in_w;
+        const int cy = min(max(iy, 0), in_h - 1), cx = min(max(ix, 0), in_w - 1);
+        in[ky * KW + kx] = ok;
+        v[ky * KW + kx] = __ldg(x + ((size_t)(b * in_h + cy) * in_w + cx) * chv + c);
+      }
+    }
+    float4 m = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+#pragma unroll
+    for (int t = 0; t < KH * KW; t++) {
+      if (in[t]) {  // strict >, NaN never wins (maxpool.ts:96)
+        if (v[t].x > m.x) m.x = v[t].x;
+        if (v[t].y > m.y) m.y = v[t].y;
+        if (v[t].z > m.z) m.z = v[t].z;
+        if (v[t].w > m.w) m.w = v[t].w;
+      }
+    }
+    y[i] = m;
+  }
+}
+
 static int pool_common(wdc_context* ctx, const wdc_pool_desc* d, const float* x, float* y, bool is_max,
                        const char* who) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "%s: null context", who);
@@ -87,6 +131,19 @@ static int pool_common(wdc_context* ctx, const wdc_pool_desc* d, const float* x,
              d->xs_h % 4 == 0 && d->xs_w % 4 == 0 && d->ys_n % 4 == 0 && d->ys_h % 4 == 0 && d->ys_w % 4 == 0;
   int64_t items = vec ? n / 4 : n;
   int grid = grid_for(ctx, items, 256, 8);
+  const bool dense = d->xs_w == d->ch && d->xs_h == d->in_w * d->ch && d->xs_n == d->in_h * d->in_w * d->ch &&
+                     d->ys_w == d->ch && d->ys_h == d->out_w * d->ch && d->ys_n == d->out_h * d->out_w * d->ch;
+  if (is_max && vec && dense && d->dil_h == 1 && d->dil_w == 1 && d->k_h == d->k_w && (d->k_h == 2 || d->k_h == 3) &&
+      d->batch * d->in_h * d->in_w * d->ch < (1ll << 31) && n < (1ll << 31)) {
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    float4* y4 = reinterpret_cast<float4*>(y);
+#define WDC_POOL_ARGS (int)items, (int)(d->ch / 4), (int)d->in_h, (int)d->in_w, (int)d->out_h, (int)d->out_w, \
+                      (int)d->stride_h, (int)d->stride_w, (int)d->pad_t, (int)d->pad_l
+    if (d->k_h == 3) maxpool_cl_small_kernel<3, 3><<<grid, 256, 0, ctx->stream>>>(x4, y4, WDC_POOL_ARGS);
+    else maxpool_cl_small_kernel<2, 2><<<grid, 256, 0, ctx->stream>>>(x4, y4, WDC_POOL_ARGS);
+#undef WDC_POOL_ARGS
+    return wdc_check_launch(ctx, "maxpool_cl_small_kernel");
+  }
   if (is_max) {
     if (vec) pool2d_kernel<true, 4><<<grid, 256, 0, ctx->stream>>>(*d, x, y, 1);
     else pool2d_kernel<true, 1><<<grid, 256, 0, ctx->stream>>>(*d, x, y, cl ? 1 : 0);

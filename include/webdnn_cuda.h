@@ -49,6 +49,15 @@ int wdc_host_alloc(wdc_context* ctx, int64_t bytes, void** hptr);
 int wdc_host_free(wdc_context* ctx, void* hptr);
 int wdc_upload(wdc_context* ctx, void* dst, const void* host, int64_t bytes);
 int wdc_download(wdc_context* ctx, void* host, const void* src, int64_t bytes); /* waits */
+/* Host-to-device transfer on the context's second stream, so that the next batch's input moves
+ * while the current batch's kernels run (no counterpart in the reference, whose tensor upload,
+ * webgpuContextImpl.ts moveTensor / queue.writeBuffer, is ordered with the compute queue).
+ * `host` should be pinned (wdc_host_alloc) and must stay valid until the transfer has run.
+ * The transfer starts after the work already queued on the compute stream.  *ticket identifies it;
+ * wdc_wait_upload makes the compute stream (not the host) wait for that transfer: call it before
+ * the first launch that reads dst. */
+int wdc_upload_async(wdc_context* ctx, void* dst, const void* host, int64_t bytes, int64_t* ticket);
+int wdc_wait_upload(wdc_context* ctx, int64_t ticket);
 int wdc_copy(wdc_context* ctx, void* dst, const void* src, int64_t bytes);
 int wdc_fill_u32(wdc_context* ctx, void* dst, uint32_t value, int64_t count);
 int wdc_sync(wdc_context* ctx);

@@ -84,3 +84,29 @@ def test_config4_lstm(cuda_context):
     for g, w in zip(got, want):
         assert g.shape == w.shape
         assert max_err_rel_linf(g, w) <= 1e-3  # the stated LSTM tolerance after 128 steps
+
+
+def test_prefetched_inputs_overlap_path_matches(cuda_context):
+    """Inputs moved with prefetch_tensor (copy stream, pinned source) give the same outputs as
+    inputs handed over as CPU tensors, step after step with a different batch each time."""
+    from webdnn_b200.backend import CPUTensor
+    from webdnn_b200.runner import load
+
+    model = zoo.conv_bn_relu(8, 32, 28)
+    r = load(model, backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": cuda_context}})
+    batches = [zoo.make_input((8, 32, 28, 28), seed=s) for s in (3, 4, 5)]
+    pinned = [cuda_context.pinned_array(b.shape, np.float32) for b in batches]
+    for p, b in zip(pinned, batches):
+        p[...] = b
+    hosts = [CPUTensor(list(b.shape), "float32", p) for p, b in zip(pinned, batches)]
+    want = [r.run([CPUTensor.from_array(b)])[0].numpy() for b in batches]
+    got = []
+    nxt = cuda_context.prefetch_tensor(hosts[0])
+    for i in range(3):
+        cur = nxt
+        nxt = cuda_context.prefetch_tensor(hosts[i + 1]) if i + 1 < 3 else None
+        got.append(r.run([cur])[0].numpy())
+        cur.dispose()
+    r.dispose()
+    for g, w in zip(got, want):
+        assert np.array_equal(g, w)

@@ -130,6 +130,7 @@ class CudaTensor(TensorImpl):
             raise ValueError("channels-last layout needs a 4-D tensor")
         self.layout = layout
         self.aux: Dict[str, "CudaTensor"] = {}  # derived device data that lives and dies with this tensor
+        self.upload_ticket: Optional[int] = None  # pending transfer on the copy stream (prefetch_tensor)
         self.disposed = False
 
     @property
@@ -307,6 +308,25 @@ class WebDNNCudaContext:
         dst = CudaTensor(self, tensor.dims, tensor.data_type)
         dst.set_data(tensor.get_data())
         return dst
+
+    def prefetch_tensor(self, tensor: CPUTensor) -> CudaTensor:
+        """Like move_tensor, but the transfer runs on the context's copy stream, so that it overlaps
+        the kernels already queued (the next batch moves while the current one is computed).  The
+        source array should be pinned (pinned_array) and must stay unchanged until the tensor has
+        been used; Runner.run orders its first kernel after the transfer."""
+        dst = CudaTensor(self, tensor.dims, tensor.data_type)
+        arr = np.ascontiguousarray(np.asarray(tensor.data).reshape(-1), dtype=NP_DTYPE[tensor.data_type])
+        ticket = ctypes.c_int64()
+        self._call("wdc_upload_async", c_void_p(dst.ptr), arr.ctypes.data_as(c_void_p), arr.nbytes, byref(ticket))
+        dst.upload_ticket = ticket.value
+        dst._prefetch_source = arr  # keeps the host memory alive until the tensor goes away
+        return dst
+
+    def wait_upload(self, t: CudaTensor) -> None:
+        """Compute stream waits (on the device, not the host) for the tensor's pending transfer."""
+        if t.upload_ticket is not None:
+            self._call("wdc_wait_upload", t.upload_ticket)
+            t.upload_ticket = None
 
     # --- layout helpers
     def canonical(self, t: CudaTensor) -> CudaTensor:

@@ -42,6 +42,12 @@ struct wdc_context {
   int* status_word = nullptr;       // device word set by kernels whose bounded waits expire
   int* status_word_host = nullptr;  // pinned mirror
   void* tc_state = nullptr;         // tensor-map cache of the tcgen05 path
+  // second stream for host-to-device transfers that overlap the kernels of `stream`
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t copy_fence = nullptr;             // recorded on `stream`, waited by `copy_stream`
+  static const int kUploadTickets = 16;
+  cudaEvent_t upload_done[kUploadTickets] = {};  // recorded on `copy_stream` after each transfer
+  int64_t upload_seq = 0;
   // optional per-launch timing of the contraction kernels
   struct ProfRec {
     cudaEvent_t start, stop;

@@ -92,6 +92,13 @@ extern "C" int wdc_destroy(wdc_context* ctx) {
   for (auto& s : ctx->arena.slabs) cudaFree(s.base);
   cudaFree(ctx->status_word);
   cudaFreeHost(ctx->status_word_host);
+  if (ctx->copy_stream) {
+    cudaStreamSynchronize(ctx->copy_stream);
+    cudaStreamDestroy(ctx->copy_stream);
+    cudaEventDestroy(ctx->copy_fence);
+    for (auto& ev : ctx->upload_done)
+      if (ev) cudaEventDestroy(ev);
+  }
   cudaStreamDestroy(ctx->stream);
   delete ctx;
   return WDC_OK;
@@ -228,6 +235,42 @@ extern "C" int wdc_upload(wdc_context* ctx, void* dst, const void* host, int64_t
   wdc_tc_evict(ctx, dst);
   WDC_CUDA(ctx, cudaMemcpyAsync(dst, host, (size_t)bytes, cudaMemcpyHostToDevice, ctx->stream));
   ctx->h2d_bytes += bytes;
+  return WDC_OK;
+}
+
+extern "C" int wdc_upload_async(wdc_context* ctx, void* dst, const void* host, int64_t bytes, int64_t* ticket) {
+  if (!ctx || !ticket || bytes < 0 || (bytes > 0 && (!dst || !host)))
+    return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_upload_async: bad argument");
+  DeviceGuard g(ctx->device);
+  if (!ctx->copy_stream) {
+    WDC_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+    WDC_CUDA(ctx, cudaEventCreateWithFlags(&ctx->copy_fence, cudaEventDisableTiming));
+    for (auto& ev : ctx->upload_done) WDC_CUDA(ctx, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+  }
+  wdc_tc_evict(ctx, dst);
+  // dst comes from the arena, whose reuse is ordered on `stream`: the transfer may start only after
+  // everything already queued there (a previous tenant of this memory may still be read)
+  WDC_CUDA(ctx, cudaEventRecord(ctx->copy_fence, ctx->stream));
+  WDC_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->copy_fence, 0));
+  if (bytes > 0)
+    WDC_CUDA(ctx, cudaMemcpyAsync(dst, host, (size_t)bytes, cudaMemcpyHostToDevice, ctx->copy_stream));
+  const int64_t t = ctx->upload_seq++;
+  WDC_CUDA(ctx, cudaEventRecord(ctx->upload_done[t % wdc_context::kUploadTickets], ctx->copy_stream));
+  ctx->h2d_bytes += bytes;
+  *ticket = t;
+  return WDC_OK;
+}
+
+extern "C" int wdc_wait_upload(wdc_context* ctx, int64_t ticket) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_wait_upload: null context");
+  if (ticket < 0 || ticket >= ctx->upload_seq)
+    return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_wait_upload: unknown ticket %lld", (long long)ticket);
+  // an event slot that has been reused marks a later transfer of the same in-order stream, which
+  // implies this one
+  DeviceGuard g(ctx->device);
+  int64_t slot = ticket;
+  if (ctx->upload_seq - ticket > wdc_context::kUploadTickets) slot = ctx->upload_seq - 1;
+  WDC_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->upload_done[slot % wdc_context::kUploadTickets], 0));
   return WDC_OK;
 }
 

@@ -71,6 +71,8 @@ SIGNATURES = {
     "wdc_host_alloc": (c_int, [c_void_p, c_int64, POINTER(c_void_p)]),
     "wdc_host_free": (c_int, [c_void_p, c_void_p]),
     "wdc_upload": (c_int, [c_void_p, c_void_p, c_void_p, c_int64]),
+    "wdc_upload_async": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, POINTER(c_int64)]),
+    "wdc_wait_upload": (c_int, [c_void_p, c_int64]),
     "wdc_download": (c_int, [c_void_p, c_void_p, c_void_p, c_int64]),
     "wdc_copy": (c_int, [c_void_p, c_void_p, c_void_p, c_int64]),
     "wdc_fill_u32": (c_int, [c_void_p, c_void_p, c_uint32, c_int64]),

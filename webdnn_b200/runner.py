@@ -136,6 +136,9 @@ class Runner:
             tensors_for_backends[t.backend][vi.name] = t
             if t.backend != "cpu":
                 borrowed.add(vi.name)  # caller-owned device tensor: never disposed here
+                wait = getattr(self.backend_contexts.get(t.backend), "wait_upload", None)
+                if wait is not None:
+                    wait(t)  # a prefetched input: order the first kernel after its transfer
 
         release_timing = find_tensor_release_timing(self.model, set(self.initializer_tensors))
         self.node_backends = []

@@ -114,3 +114,34 @@ def test_weight_split_cache_follows_buffer_lifetime(cuda_context):
         (want,) = ref_runner.run_model(model, [a, b])
         (got,) = run_cuda(model, [a, b], cuda_context)
         assert max_err_rel_linf(got, want) <= TOL
+
+
+def test_weight_split_cache_sees_in_place_writes(cuda_context):
+    """A weight buffer rewritten on the device (here: negated in place by wdc_unary, and then one
+    half of it overwritten through wdc_strided_copy at an offset) must not be served from the cached
+    split of its old contents."""
+    from webdnn_b200.backend import CPUTensor
+    from webdnn_b200.lib import GemmDesc
+    from webdnn_b200.lib import UNARY_OPS
+    ctx = cuda_context
+    rng = np.random.default_rng(5)
+    m, n, k = 64, 64, 128
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal((n, k)).astype(np.float32)
+    da, db = ctx.move_tensor(CPUTensor.from_array(a)), ctx.move_tensor(CPUTensor.from_array(b))
+    dy = ctx.empty_tensor([m, n])
+    d = GemmDesc(batch=1, m=m, n=n, k=k, sab=0, sa0=k, sa1=1, sbb=0, sb0=1, sb1=k, sc0=0, sc1=0, alpha=1.0, beta=0.0,
+                 relu=0)
+    ctx.gemm(d, da, db, None, dy)
+    assert max_err_rel_linf(dy.get_data().reshape(m, n), a @ b.T) <= TOL
+    ctx.unary(UNARY_OPS["Neg"], db, db)                      # in place
+    ctx.gemm(d, da, db, None, dy)
+    assert max_err_rel_linf(dy.get_data().reshape(m, n), -(a @ b.T)) <= TOL
+    half = ctx.move_tensor(CPUTensor.from_array(np.zeros((n // 2, k), np.float32)))
+    ctx.strided_copy(half, db, [n // 2, k], [k, 1], 0, [k, 1], (n // 2) * k)   # second half of b := 0
+    ctx.gemm(d, da, db, None, dy)
+    want = -(a @ b.T)
+    want[:, n // 2:] = 0
+    assert max_err_rel_linf(dy.get_data().reshape(m, n), want) <= TOL
+    for t in (da, db, dy, half):
+        t.dispose()

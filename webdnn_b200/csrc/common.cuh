@@ -124,3 +124,8 @@ int wdc_tc_gemm(wdc_context* ctx, const wdc_gemm_desc* d, const float* A, const 
 void wdc_tc_destroy(wdc_context* ctx);
 // Drops the cached hi/lo split of a weight matrix when its buffer is freed or overwritten.
 void wdc_tc_evict(wdc_context* ctx, const void* ptr);
+// Every entry point that writes device memory reports the start of its output here: operand splits
+// cached by the tensor-core path for a buffer that contains that address are dropped.
+inline void wdc_note_write(wdc_context* ctx, const void* ptr) {
+  if (ctx && ptr && ctx->tc_state) wdc_tc_evict(ctx, ptr);
+}

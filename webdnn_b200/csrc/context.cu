@@ -324,6 +324,7 @@ __global__ void fill_u32_kernel(uint32_t* dst, uint32_t v, int64_t n) {
 extern "C" int wdc_fill_u32(wdc_context* ctx, void* dst, uint32_t value, int64_t count) {
   if (!ctx || count < 0 || (count > 0 && !dst))
     return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_fill_u32: bad argument");
+  wdc_note_write(ctx, dst);
   if (count == 0) return WDC_OK;
   DeviceGuard g(ctx->device);
   fill_u32_kernel<<<grid_for(ctx, count, 256), 256, 0, ctx->stream>>>((uint32_t*)dst, value, count);
@@ -379,6 +380,7 @@ extern "C" int wdc_peer_copy(wdc_context* dst_ctx, void* dst, wdc_context* src_c
                              int64_t bytes) {
   if (!dst_ctx || !src_ctx || bytes < 0 || (bytes > 0 && (!dst || !src)))
     return wdc_fail(dst_ctx, WDC_ERR_INVALID, "wdc_peer_copy: bad argument");
+  wdc_note_write(dst_ctx, dst);
   if (bytes == 0) return WDC_OK;
   // Order the copy after everything already enqueued on the source stream, run it on the
   // destination stream.

@@ -44,7 +44,6 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
-#include <set>
 
 #include "common.cuh"
 
@@ -1007,6 +1006,7 @@ struct WeightEntry {
   float* hi = nullptr;
   float* lo = nullptr;
   int64_t rows = 0, k = 0;
+  int64_t src_bytes = 0;  // size of the caller's weight buffer the split was made from
   int tile_n = 0;
   CUtensorMap map_hi, map_lo;
 };
@@ -1017,7 +1017,6 @@ struct TcState {
   bool unavailable = false;
   bool attr_set = false;
   std::map<WeightKey, WeightEntry> weights;
-  std::set<const void*> scales;  // buffers used as a key's scale: a write to one evicts those entries
 };
 
 TcState* tc_state(wdc_context* ctx) {
@@ -1072,6 +1071,7 @@ int get_weight(wdc_context* ctx, const float* w, const float* scale, float alpha
   WeightEntry e;
   e.rows = rows;
   e.k = k;
+  e.src_bytes = (c4_kh ? rows * c4_kh * c4_kw * c4_cin : rows * k) * 4;
   e.tile_n = pick_tile_n(rows);
   int s = wdc_alloc(ctx, rows * k * 4, (void**)&e.hi);
   if (s != WDC_OK) return s;
@@ -1096,7 +1096,6 @@ int get_weight(wdc_context* ctx, const float* w, const float* scale, float alpha
                     (long long)rows, (long long)k);
   }
   auto ins = st->weights.emplace(key, e);
-  if (scale) st->scales.insert(scale);
   *out = &ins.first->second;
   return WDC_OK;
 }
@@ -1216,23 +1215,21 @@ bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 void wdc_tc_evict(wdc_context* ctx, const void* ptr) {
   if (!ctx->tc_state) return;
   TcState* st = (TcState*)ctx->tc_state;
-  // entries built from this buffer, as weights or as the per-channel scale
-  for (auto it = st->weights.lower_bound(WeightKey{ptr, nullptr, 0}); it != st->weights.end() && it->first.w == ptr;) {
-    WeightEntry e = it->second;
-    it = st->weights.erase(it);
-    wdc_free(ctx, e.hi);
-    wdc_free(ctx, e.lo);
-  }
-  if (st->scales.count(ptr)) {
-    for (auto it = st->weights.begin(); it != st->weights.end();) {
-      if (it->first.scale == ptr) {
-        WeightEntry e = it->second;
-        it = st->weights.erase(it);
-        wdc_free(ctx, e.hi);
-        wdc_free(ctx, e.lo);
-      } else ++it;
+  if (st->weights.empty()) return;
+  // entries made from a buffer that contains ptr, as weights or as the per-channel scale
+  const char* q = (const char*)ptr;
+  for (auto it = st->weights.begin(); it != st->weights.end();) {
+    const char* w = (const char*)it->first.w;
+    const char* sc = (const char*)it->first.scale;
+    const bool hit = (q >= w && q < w + it->second.src_bytes) || (sc && q >= sc && q < sc + it->second.rows * 4);
+    if (hit) {
+      WeightEntry e = it->second;
+      it = st->weights.erase(it);
+      wdc_free(ctx, e.hi);
+      wdc_free(ctx, e.lo);
+    } else {
+      ++it;
     }
-    st->scales.erase(ptr);
   }
 }
 

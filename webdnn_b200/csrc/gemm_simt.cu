@@ -188,6 +188,7 @@ int wdc_simt_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, co
 extern "C" int wdc_gemm(wdc_context* ctx, const wdc_gemm_desc* d, const float* A, const float* B,
                         const float* C, float* Y) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_gemm: null context");
+  wdc_note_write(ctx, Y);
   WDC_REQUIRE(ctx, d != nullptr, "wdc_gemm: null descriptor");
   WDC_REQUIRE(ctx, d->batch >= 0 && d->m >= 0 && d->n >= 0 && d->k >= 0, "wdc_gemm: negative shape");
   if (d->batch * d->m * d->n == 0) return WDC_OK;
@@ -202,6 +203,7 @@ extern "C" int wdc_gemm(wdc_context* ctx, const wdc_gemm_desc* d, const float* A
 extern "C" int wdc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, const float* w,
                           const float* scale, const float* shift, const float* residual, float* y) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_conv2d: null context");
+  wdc_note_write(ctx, y);
   WDC_REQUIRE(ctx, d != nullptr, "wdc_conv2d: null descriptor");
   WDC_REQUIRE(ctx, d->batch >= 0 && d->ch_in > 0 && d->ch_out > 0 && d->in_h > 0 && d->in_w > 0 &&
                        d->k_h > 0 && d->k_w > 0 && d->stride_h > 0 && d->stride_w > 0 && d->dil_h > 0 &&
@@ -235,6 +237,7 @@ __global__ void pack_conv_weight_kernel(const float* __restrict__ src, float* __
 extern "C" int wdc_pack_conv_weight(wdc_context* ctx, const float* w_onnx, float* w_packed, int64_t ch_out,
                                     int64_t cig, int64_t k_h, int64_t k_w) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_pack_conv_weight: null context");
+  wdc_note_write(ctx, w_packed);
   WDC_REQUIRE(ctx, ch_out > 0 && cig > 0 && k_h > 0 && k_w > 0 && w_onnx && w_packed,
               "wdc_pack_conv_weight: bad argument");
   DeviceGuard g(ctx->device);

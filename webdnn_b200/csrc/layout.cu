@@ -92,6 +92,7 @@ extern "C" int wdc_strided_copy(wdc_context* ctx, const void* src, void* dst, in
                                 const int64_t* dims, const int64_t* sstr, int64_t src_off,
                                 const int64_t* dstr, int64_t dst_off) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_strided_copy: null context");
+  wdc_note_write(ctx, dst ? (const uint32_t*)dst + dst_off : nullptr);
   WDC_REQUIRE(ctx, ndim >= 0 && ndim <= 6, "wdc_strided_copy: rank %d not in 0..6", ndim);
   WDC_REQUIRE(ctx, ndim == 0 || (dims && sstr && dstr), "wdc_strided_copy: null shape");
   WDC_REQUIRE(ctx, src_off >= 0 && dst_off >= 0, "wdc_strided_copy: negative offset");
@@ -174,6 +175,7 @@ __global__ void __launch_bounds__(256) gather_kernel(const uint32_t* __restrict_
 extern "C" int wdc_gather(wdc_context* ctx, const void* data, const int32_t* idx, void* out,
                           int64_t outer, int64_t axis_len, int64_t inner, int64_t n_idx) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_gather: null context");
+  wdc_note_write(ctx, out);
   WDC_REQUIRE(ctx, outer >= 0 && axis_len > 0 && inner >= 0 && n_idx >= 0, "wdc_gather: bad shape");
   int64_t n = outer * n_idx * inner;
   if (n == 0) return WDC_OK;

@@ -42,6 +42,9 @@ extern "C" int wdc_lstm(wdc_context* ctx, const float* X, const float* W, const 
                         const float* h0, const float* c0, float* Y, float* Yh, float* Yc, int64_t T,
                         int64_t Bt, int64_t I, int64_t H) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_lstm: null context");
+  wdc_note_write(ctx, Yc);
+  wdc_note_write(ctx, Yh);
+  wdc_note_write(ctx, Y);
   WDC_REQUIRE(ctx, T >= 0 && Bt > 0 && I > 0 && H > 0, "wdc_lstm: bad shape");
   WDC_REQUIRE(ctx, X && W && R && Yh && Yc && (T == 0 || Y), "wdc_lstm: null buffer");
   DeviceGuard g(ctx->device);
@@ -113,6 +116,9 @@ extern "C" int wdc_lstm_static(wdc_context* ctx, const float* X, const float* W,
                                const float* bias, const float* h0, const float* c0, float* Y, float* Yh,
                                float* Yc, int64_t T, int64_t Bt, int64_t I, int64_t H) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_lstm_static: null context");
+  wdc_note_write(ctx, Yc);
+  wdc_note_write(ctx, Yh);
+  wdc_note_write(ctx, Y);
   WDC_REQUIRE(ctx, T >= 0 && Bt > 0 && I > 0 && H > 0, "wdc_lstm_static: bad shape");
   WDC_REQUIRE(ctx, X && W && R && Yh && Yc && (T == 0 || Y), "wdc_lstm_static: null buffer");
   if (Bt * 4 * H > kLstmStaticFloats)

@@ -128,6 +128,7 @@ static int launch_unary(wdc_context* ctx, const float* src, float* dst, int64_t 
 extern "C" int wdc_unary(wdc_context* ctx, int op, int dtype, const void* src, void* dst, int64_t n,
                          float p0, float p1) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_unary: null context");
+  wdc_note_write(ctx, dst);
   WDC_REQUIRE(ctx, n >= 0 && (n == 0 || (src && dst)), "wdc_unary: bad buffer or count");
   if (n == 0) return WDC_OK;
   DeviceGuard g(ctx->device);
@@ -301,6 +302,7 @@ static int launch_binary_f32(wdc_context* ctx, const float* a, const float* b, f
 extern "C" int wdc_binary(wdc_context* ctx, int op, int dtype, const void* a, const void* b, void* out,
                           int ndim, const int64_t* dims, const int64_t* sa, const int64_t* sb) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_binary: null context");
+  wdc_note_write(ctx, out);
   WDC_REQUIRE(ctx, ndim >= 0 && ndim <= 6, "wdc_binary: rank %d not in 0..6", ndim);
   WDC_REQUIRE(ctx, op >= WDC_B_ADD && op <= WDC_B_MIN, "wdc_binary: unknown op %d", op);
   WDC_REQUIRE(ctx, dtype == 0 || dtype == 1, "wdc_binary: dtype %d not supported", dtype);
@@ -388,6 +390,7 @@ __global__ void cast_i32_f32_kernel(const int32_t* __restrict__ s, float* __rest
 extern "C" int wdc_cast(wdc_context* ctx, int src_dtype, int dst_dtype, const void* src, void* dst,
                         int64_t n) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_cast: null context");
+  wdc_note_write(ctx, dst);
   WDC_REQUIRE(ctx, n >= 0 && (n == 0 || (src && dst)), "wdc_cast: bad buffer or count");
   if (n == 0) return WDC_OK;
   DeviceGuard g(ctx->device);
@@ -456,6 +459,7 @@ extern "C" int wdc_channel_affine(wdc_context* ctx, const float* x, const float*
                                   const float* shift, float* y, int64_t outer, int64_t channels,
                                   int64_t inner, int relu) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_channel_affine: null context");
+  wdc_note_write(ctx, y);
   WDC_REQUIRE(ctx, outer >= 0 && channels > 0 && inner > 0, "wdc_channel_affine: bad shape");
   int64_t n = outer * channels * inner;
   if (n == 0) return WDC_OK;

@@ -117,6 +117,7 @@ __global__ void __launch_bounds__(256) maxpool_cl_small_kernel(const float4* __r
 static int pool_common(wdc_context* ctx, const wdc_pool_desc* d, const float* x, float* y, bool is_max,
                        const char* who) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "%s: null context", who);
+  wdc_note_write(ctx, y);
   WDC_REQUIRE(ctx, d != nullptr, "%s: null descriptor", who);
   WDC_REQUIRE(ctx, d->batch >= 0 && d->ch >= 0 && d->in_h > 0 && d->in_w > 0 && d->out_h >= 0 &&
                        d->out_w >= 0 && d->k_h > 0 && d->k_w > 0 && d->stride_h > 0 && d->stride_w > 0 &&
@@ -197,6 +198,7 @@ __global__ void __launch_bounds__(256) gap_warp_kernel(const float* __restrict__
 extern "C" int wdc_global_avgpool(wdc_context* ctx, const float* x, float* y, int64_t batch, int64_t ch,
                                   int64_t area, int64_t xs_n, int64_t xs_c, int64_t xs_p) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_global_avgpool: null context");
+  wdc_note_write(ctx, y);
   WDC_REQUIRE(ctx, batch >= 0 && ch >= 0 && area > 0, "wdc_global_avgpool: bad shape");
   if (batch * ch == 0) return WDC_OK;
   WDC_REQUIRE(ctx, x && y, "wdc_global_avgpool: null buffer");

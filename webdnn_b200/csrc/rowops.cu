@@ -103,6 +103,7 @@ __global__ void __launch_bounds__(512) softmax_block_kernel(const float* __restr
 
 extern "C" int wdc_softmax(wdc_context* ctx, const float* x, float* y, int64_t outer, int64_t len) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_softmax: null context");
+  wdc_note_write(ctx, y);
   WDC_REQUIRE(ctx, outer >= 0 && len >= 0, "wdc_softmax: negative shape");
   if (outer == 0 || len == 0) return WDC_OK;
   WDC_REQUIRE(ctx, x && y, "wdc_softmax: null buffer");
@@ -205,6 +206,7 @@ __global__ void __launch_bounds__(256) reduce_cols_kernel(int kind, int final, c
 extern "C" int wdc_reduce_axis(wdc_context* ctx, int kind, int final, const float* x, float* y,
                                int64_t outer, int64_t red, int64_t inner, int64_t total) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_reduce_axis: null context");
+  wdc_note_write(ctx, y);
   WDC_REQUIRE(ctx, kind >= R_SUM && kind <= R_SUMSQUARE, "wdc_reduce_axis: unknown kind %d", kind);
   WDC_REQUIRE(ctx, outer >= 0 && red > 0 && inner > 0, "wdc_reduce_axis: bad shape");
   if (outer == 0) return WDC_OK;
@@ -270,6 +272,7 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const float* __rest
 extern "C" int wdc_layernorm(wdc_context* ctx, const float* x, const float* gamma, const float* beta,
                              float* y, int64_t outer, int64_t len, float eps) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_layernorm: null context");
+  wdc_note_write(ctx, y);
   WDC_REQUIRE(ctx, outer >= 0 && len > 0, "wdc_layernorm: bad shape");
   if (len > 1024)
     return wdc_fail(ctx, WDC_ERR_UNSUPPORTED, "wdc_layernorm: rows longer than 1024 (%lld) not supported",
@@ -323,6 +326,7 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ x
 extern "C" int wdc_argmax(wdc_context* ctx, const float* x, int32_t* y, int64_t outer, int64_t len,
                           int select_last) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_argmax: null context");
+  wdc_note_write(ctx, y);
   WDC_REQUIRE(ctx, outer >= 0 && len > 0, "wdc_argmax: bad shape");
   if (outer == 0) return WDC_OK;
   WDC_REQUIRE(ctx, x && y, "wdc_argmax: null buffer");

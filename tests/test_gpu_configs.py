@@ -110,3 +110,20 @@ def test_prefetched_inputs_overlap_path_matches(cuda_context):
     r.dispose()
     for g, w in zip(got, want):
         assert np.array_equal(g, w)
+
+
+@pytest.mark.parametrize("batch", [1, 2])
+def test_config5_detr_style(cuda_context, batch):
+    """Config 5 topology (ResNet trunk -> 1x1 projection -> post-norm encoder/decoder -> class and box
+    heads) at a size the CPU oracle finishes in seconds: 128x128 input (16 tokens), d = 64, 4 heads,
+    2 + 2 layers, 10 queries.  Every node has to run on the cuda backend."""
+    model = zoo.detr(batch=batch, size=128, d=64, heads=4, enc_layers=2, dec_layers=2, ffn=256, queries=10,
+                     classes=12, width=32, blocks=(1, 1, 1, 1))
+    x = zoo.make_input((batch, 3, 128, 128))
+    want = ref_runner.run_model(model, [x])
+    got, r = run_cuda(model, [x], cuda_context, return_runner=True)
+    _all_on_cuda(r)
+    r.dispose()
+    assert [g.shape for g in got] == [(batch, 10, 12), (batch, 10, 4)]
+    for g, w in zip(got, want):
+        assert max_err_rel_linf(g, w) <= TOL

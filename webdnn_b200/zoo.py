@@ -133,6 +133,104 @@ def resnet50(batch: int = 1, size: int = 224, width: int = 64, blocks=(3, 4, 6, 
     return b.model([("input", [batch, 3, size, size])], [(h, [batch, classes])], name="resnet50")
 
 
+class _Transformer:
+    """Node-by-node pieces of a post-norm encoder/decoder (DETR style), written only with operator
+    forms the reference's cpu backend runs: MatMul of rank <= 3, last-axis Softmax, LayerNorm as the
+    ReduceMean / Sub / Mul / Add / Sqrt / Div chain (opset 13)."""
+
+    def __init__(self, b: _Builder, batch: int, d: int, heads: int, ffn: int):
+        self.b, self.batch, self.d, self.heads, self.ffn = b, batch, d, heads, ffn
+        self.dh = d // heads
+        self.scale = b.init(b.name("attn_scale"), np.array(1.0 / np.sqrt(self.dh), np.float32))
+        self.eps = b.init(b.name("ln_eps"), np.array(1e-5, np.float32))
+
+    def shape(self, dims) -> str:
+        return self.b.init(self.b.name("shape"), np.array(dims, np.int64))
+
+    def linear(self, x: str, cin: int, cout: int) -> str:
+        b = self.b
+        w = b.init(b.name("w"), b.he((cin, cout), cin))
+        bias = b.init(b.name("b"), b.bias(cout))
+        return b.node("Add", [b.node("MatMul", [x, w])[0], bias])[0]
+
+    def layer_norm(self, x: str) -> str:
+        b = self.b
+        g = b.init(b.name("ln_g"), b.rng.uniform(0.5, 1.5, self.d).astype(np.float32))
+        be = b.init(b.name("ln_b"), (b.rng.standard_normal(self.d) * 0.1).astype(np.float32))
+        mean = b.node("ReduceMean", [x], axes=[-1], keepdims=1)[0]
+        xc = b.node("Sub", [x, mean])[0]
+        var = b.node("ReduceMean", [b.node("Mul", [xc, xc])[0]], axes=[-1], keepdims=1)[0]
+        std = b.node("Sqrt", [b.node("Add", [var, self.eps])[0]])[0]
+        y = b.node("Div", [xc, std])[0]
+        return b.node("Add", [b.node("Mul", [y, g])[0], be])[0]
+
+    def split_heads(self, x: str, tokens: int) -> str:
+        b = self.b
+        h = b.node("Reshape", [x, self.shape([self.batch, tokens, self.heads, self.dh])])[0]
+        h = b.node("Transpose", [h], perm=[0, 2, 1, 3])[0]
+        return b.node("Reshape", [h, self.shape([self.batch * self.heads, tokens, self.dh])])[0]
+
+    def attention(self, q_in: str, k_in: str, v_in: str, tq: int, tk: int) -> str:
+        b = self.b
+        q = self.split_heads(self.linear(q_in, self.d, self.d), tq)
+        k = self.split_heads(self.linear(k_in, self.d, self.d), tk)
+        v = self.split_heads(self.linear(v_in, self.d, self.d), tk)
+        kt = b.node("Transpose", [k], perm=[0, 2, 1])[0]
+        scores = b.node("Mul", [b.node("MatMul", [q, kt])[0], self.scale])[0]
+        p = b.node("Softmax", [scores], axis=-1)[0]
+        ctx = b.node("MatMul", [p, v])[0]
+        ctx = b.node("Reshape", [ctx, self.shape([self.batch, self.heads, tq, self.dh])])[0]
+        ctx = b.node("Transpose", [ctx], perm=[0, 2, 1, 3])[0]
+        ctx = b.node("Reshape", [ctx, self.shape([self.batch, tq, self.d])])[0]
+        return self.linear(ctx, self.d, self.d)
+
+    def feed_forward(self, x: str) -> str:
+        h = self.b.node("Relu", [self.linear(x, self.d, self.ffn)])[0]
+        return self.linear(h, self.ffn, self.d)
+
+    def add_norm(self, x: str, y: str) -> str:
+        return self.layer_norm(self.b.node("Add", [x, y])[0])
+
+
+def detr(batch: int = 1, size: int = 800, d: int = 256, heads: int = 8, enc_layers: int = 6, dec_layers: int = 6,
+         ffn: int = 2048, queries: int = 100, classes: int = 92, width: int = 64, blocks=(3, 4, 6, 3)) -> Model:
+    """DETR-style detector: ResNet trunk, 1x1 projection to d channels, learned position embeddings,
+    post-norm transformer encoder / decoder with `queries` object queries, class head and 3-layer box
+    head.  Input [batch, 3, size, size]; outputs logits [batch, queries, classes] and boxes
+    [batch, queries, 4].  Tokens are kept batch-first so that every MatMul has rank <= 3."""
+    b = _Builder(0)
+    h, c = resnet_trunk(b, "input", width, blocks)
+    side = size
+    for _ in range(5):
+        side = (side + 1) // 2
+    tokens = side * side
+    h = b.conv(h, c, d, 1, bias=True)
+    t = _Transformer(b, batch, d, heads, ffn)
+    h = b.node("Reshape", [h, t.shape([batch, d, tokens])])[0]
+    src = b.node("Transpose", [h], perm=[0, 2, 1])[0]                       # [batch, tokens, d]
+    pos = b.init("pos_embed", b.rng.standard_normal((1, tokens, d)).astype(np.float32))
+    for _ in range(enc_layers):
+        qk = b.node("Add", [src, pos])[0]
+        src = t.add_norm(src, t.attention(qk, qk, src, tokens, tokens))
+        src = t.add_norm(src, t.feed_forward(src))
+    memory = src
+    mem_k = b.node("Add", [memory, pos])[0]
+    qpos = b.init("query_embed", b.rng.standard_normal((1, queries, d)).astype(np.float32))
+    tgt = b.init("tgt0", np.zeros((batch, queries, d), np.float32))
+    for _ in range(dec_layers):
+        q = b.node("Add", [tgt, qpos])[0]
+        tgt = t.add_norm(tgt, t.attention(q, q, tgt, queries, queries))
+        q = b.node("Add", [tgt, qpos])[0]
+        tgt = t.add_norm(tgt, t.attention(q, mem_k, memory, queries, tokens))
+        tgt = t.add_norm(tgt, t.feed_forward(tgt))
+    logits = t.linear(tgt, d, classes)
+    box = b.node("Relu", [t.linear(tgt, d, d)])[0]
+    box = b.node("Relu", [t.linear(box, d, d)])[0]
+    box = b.node("Sigmoid", [t.linear(box, d, 4)])[0]
+    return b.model([("input", [batch, 3, size, size])],
+                   [(logits, [batch, queries, classes]), (box, [batch, queries, 4])], name="detr")
+
+
 def lstm(seq: int = 128, batch: int = 64, input_size: int = 256, hidden: int = 512) -> Model:
     """Single forward LSTM node; inputs [X, W, R, B] only (zero initial state by omission)."""
     b = _Builder(0)

@@ -145,3 +145,34 @@ def test_weight_split_cache_sees_in_place_writes(cuda_context):
     assert max_err_rel_linf(dy.get_data().reshape(m, n), want) <= TOL
     for t in (da, db, dy, half):
         t.dispose()
+
+
+@pytest.mark.parametrize("shape_a,shape_b", [
+    ((64, 256), (256, 512)),          # 2-D, B stored [k, n]
+    ((8, 625, 256), (256, 256)),      # rank-3 A times a shared 2-D B: one tall matrix
+    ((3, 40, 2048), (2048, 256)),     # K = 2048, M = 120 (partly filled tile)
+])
+def test_matmul_row_major_b_on_tensor_cores(cuda_context, shape_a, shape_b):
+    rng = np.random.default_rng(6)
+    a = rng.standard_normal(shape_a).astype(np.float32)
+    b = (rng.standard_normal(shape_b) * np.sqrt(2.0 / shape_b[0])).astype(np.float32)
+    model = single_op_model("MatMul", {}, [a, b])
+    (want,) = ref_runner.run_model(model, [a, b])
+    before = cuda_context.stats()["tensor_core_launches"]
+    (got,) = run_cuda(model, [a, b], cuda_context)
+    assert cuda_context.stats()["tensor_core_launches"] > before
+    assert got.shape == want.shape
+    assert max_err_rel_linf(got, want) <= TOL
+
+
+def test_gemm_trans_b_0_on_tensor_cores(cuda_context):
+    rng = np.random.default_rng(7)
+    a = rng.standard_normal((96, 128)).astype(np.float32)
+    b = (rng.standard_normal((128, 72)) * 0.1).astype(np.float32)
+    c = rng.uniform(-0.1, 0.1, 72).astype(np.float32)
+    model = single_op_model("Gemm", {"alpha": 1.25, "beta": 0.5}, [a, b, c])
+    (want,) = ref_runner.run_model(model, [a, b, c])
+    before = cuda_context.stats()["tensor_core_launches"]
+    (got,) = run_cuda(model, [a, b, c], cuda_context)
+    assert cuda_context.stats()["tensor_core_launches"] > before
+    assert max_err_rel_linf(got, want) <= TOL

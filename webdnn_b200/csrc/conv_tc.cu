@@ -950,6 +950,36 @@ __global__ void split_tf32_kernel(const float* __restrict__ w, float* __restrict
   }
 }
 
+// Same split for a weight matrix stored [k][rows] (rows contiguous, MatMul's B): 32x32 tiles through
+// shared memory so that both the reads (along rows) and the writes (along k) are coalesced.
+__global__ void __launch_bounds__(256) split_tf32_transpose_kernel(const float* __restrict__ w, float* __restrict__ hi,
+                                                                   float* __restrict__ lo, int64_t rows, int64_t k,
+                                                                   const float* __restrict__ scale, float alpha) {
+  __shared__ float tile[32][33];
+  const int64_t tiles_r = (rows + 31) / 32, tiles_k = (k + 31) / 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  for (int64_t t = blockIdx.x; t < tiles_r * tiles_k; t += gridDim.x) {
+    const int64_t r0 = (t / tiles_k) * 32, k0 = (t % tiles_k) * 32;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int64_t kk = k0 + ty + i * 8, r = r0 + tx;
+      if (kk < k && r < rows) tile[ty + i * 8][tx] = w[kk * rows + r];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int64_t r = r0 + ty + i * 8, kk = k0 + tx;
+      if (r < rows && kk < k) {
+        const float v = tile[tx][ty + i * 8] * (scale ? alpha * scale[r] : alpha);
+        const float h = to_tf32(v);
+        hi[r * k + kk] = h;
+        lo[r * k + kk] = to_tf32(v - h);
+      }
+    }
+    __syncthreads();
+  }
+}
+
 // Stem mode operand preparation: 4 channels per pixel, 8 taps per filter row.
 __global__ void pad_channels4_kernel(const float* __restrict__ x, float* __restrict__ x4, int64_t pixels, int cin) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -995,10 +1025,12 @@ struct WeightKey {
   const void* w;
   const void* scale;
   uint32_t alpha_bits;
+  int k_major;  // 1: source stored [rows][k]; 0: stored [k][rows]
   bool operator<(const WeightKey& o) const {
     if (w != o.w) return w < o.w;
     if (scale != o.scale) return scale < o.scale;
-    return alpha_bits < o.alpha_bits;
+    if (alpha_bits != o.alpha_bits) return alpha_bits < o.alpha_bits;
+    return k_major < o.k_major;
   }
 };
 
@@ -1054,9 +1086,9 @@ int encode_rows_map(TcState* st, CUtensorMap* map, const float* base, int64_t ro
 
 // Looks up (or builds) the hi/lo split and the tensor maps of a [rows, k] K-major weight matrix.
 int get_weight(wdc_context* ctx, const float* w, const float* scale, float alpha, int64_t rows, int64_t k,
-               WeightEntry** out, int c4_kh = 0, int c4_kw = 0, int c4_cin = 0) {
+               WeightEntry** out, int c4_kh = 0, int c4_kw = 0, int c4_cin = 0, bool k_major = true) {
   TcState* st = tc_state(ctx);
-  WeightKey key = {w, scale, 0};
+  WeightKey key = {w, scale, 0, k_major ? 1 : 0};
   memcpy(&key.alpha_bits, &alpha, 4);
   auto it = st->weights.find(key);
   if (it != st->weights.end() && it->second.rows == rows && it->second.k == k) {
@@ -1083,6 +1115,9 @@ int get_weight(wdc_context* ctx, const float* w, const float* scale, float alpha
   if (c4_kh)
     split_tf32_c4_kernel<<<grid_for(ctx, rows * k, 256, 8), 256, 0, ctx->stream>>>(w, e.hi, e.lo, rows, c4_kh, c4_kw,
                                                                                     c4_cin, scale, alpha);
+  else if (!k_major)
+    split_tf32_transpose_kernel<<<grid_for(ctx, ((rows + 31) / 32) * ((k + 31) / 32) * 256, 256, 16), 256, 0,
+                                  ctx->stream>>>(w, e.hi, e.lo, rows, k, scale, alpha);
   else
     split_tf32_kernel<<<grid_for(ctx, rows * k, 256, 8), 256, 0, ctx->stream>>>(w, e.hi, e.lo, rows * k, k, scale, alpha);
   s = wdc_check_launch(ctx, "split_tf32_kernel");
@@ -1164,9 +1199,9 @@ bool encode_a_map(TcState* st, const TcProblem& p, const float* x, CUtensorMap* 
 }
 
 int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, float* y, int c4_kw = 0,
-              int c4_cin = 0) {
+              int c4_cin = 0, bool w_k_major = true) {
   WeightEntry* we = nullptr;
-  int s = get_weight(ctx, w, p.scale, p.alpha, p.N, p.K, &we, p.c4 ? p.K / 32 : 0, c4_kw, c4_cin);
+  int s = get_weight(ctx, w, p.scale, p.alpha, p.N, p.K, &we, p.c4 ? p.K / 32 : 0, c4_kw, c4_cin, w_k_major);
   if (s != WDC_OK) return s;
   p.scale = nullptr;  // folded into the split weights
   p.alpha = 1.f;
@@ -1280,9 +1315,18 @@ int wdc_tc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, cons
 
 int wdc_tc_gemm(wdc_context* ctx, const wdc_gemm_desc* d, const float* A, const float* B, const float* C,
                 float* Y) {
-  // A [m, k] with k contiguous, B given as [n, k] with k contiguous (Gemm transB=1, LSTM weights)
-  if (d->batch != 1 || d->sa1 != 1 || d->sb0 != 1 || d->sb1 != d->k || d->sa0 != d->k) return WDC_ERR_UNSUPPORTED;
-  if (d->k % 4 != 0 || d->sa0 % 4 != 0 || d->k < 32 || d->m < 32) return WDC_ERR_UNSUPPORTED;
+  // A [m, k] with k contiguous; B either [n, k] with k contiguous (Gemm transB=1, LSTM weights) or [k, n] with n
+  // contiguous (MatMul, Gemm transB=0: transposed while it is split).  A batch whose B is shared (stride 0) and
+  // whose A and Y are stacked without gaps is one tall matrix.
+  int64_t m = d->m;
+  if (d->batch != 1) {
+    if (d->sbb != 0 || d->sab != d->m * d->sa0 || C) return WDC_ERR_UNSUPPORTED;
+    m = d->batch * d->m;
+  }
+  const bool b_k_major = d->sb0 == 1 && d->sb1 == d->k;
+  const bool b_n_major = d->sb1 == 1 && d->sb0 == d->n;
+  if (d->sa1 != 1 || d->sa0 != d->k || !(b_k_major || b_n_major)) return WDC_ERR_UNSUPPORTED;
+  if (d->k % 4 != 0 || d->k < 32 || m < 32) return WDC_ERR_UNSUPPORTED;
   if (!aligned16(A) || !aligned16(B) || !aligned16(Y)) return WDC_ERR_UNSUPPORTED;
   const float* shift = nullptr;
   const float* residual = nullptr;
@@ -1297,7 +1341,7 @@ int wdc_tc_gemm(wdc_context* ctx, const wdc_gemm_desc* d, const float* A, const 
   if (d->k > (1 << 30) || d->n > (1 << 24)) return WDC_ERR_UNSUPPORTED;
   if (!tc_ready(ctx)) return WDC_ERR_UNSUPPORTED;
   TcProblem p = {};
-  p.M = d->m;
+  p.M = m;
   p.N = (int)d->n;
   p.K = (int)d->k;
   p.ch_in = (int)d->k; p.in_h = 1; p.in_w = 1; p.out_h = 1; p.out_w = 1; p.k_h = 1; p.k_w = 1;
@@ -1305,5 +1349,5 @@ int wdc_tc_gemm(wdc_context* ctx, const wdc_gemm_desc* d, const float* A, const 
   p.cblocks = (int)((d->k + BLOCK_K - 1) / BLOCK_K);
   p.shift = shift; p.residual = residual; p.res_stride = res_stride;
   p.alpha = d->alpha; p.shift_mul = d->beta; p.res_mul = d->beta; p.relu = d->relu;
-  return launch_tc(ctx, p, A, B, Y);
+  return launch_tc(ctx, p, A, B, Y, 0, 0, b_k_major);
 }

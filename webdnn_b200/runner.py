@@ -194,6 +194,9 @@ class Runner:
                     if t is not None:
                         t.dispose()
             if measure_performance:
+                sync = getattr(context, "sync", None)
+                if sync is not None:
+                    sync()  # device backends only enqueue: wait, so that elapsed is this node's time
                 self.node_performances.append(dict(
                     opType=op_type, name=node.name, backend=operator.backend,
                     inputDims=[t.dims for t in operator_inputs], outputDims=[t.dims for t in outputs],

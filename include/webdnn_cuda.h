@@ -201,7 +201,10 @@ int wdc_gather(wdc_context* ctx, const void* data, const int32_t* idx, void* out
 /* ---- LSTM -----------------------------------------------------------------------------------
  * ONNX LSTM, forward direction, default activations, no peepholes (not in the reference; ONNX
  * operator spec).  X [T, Bt, I], W [4H, I], R [4H, H], bias [8H] or NULL, h0/c0 [Bt, H] or NULL;
- * Y [T, 1, Bt, H], Yh/Yc [Bt, H].  Gate order i, o, f, c. */
+ * Y [T, 1, Bt, H], Yh/Yc [Bt, H].  Gate order i, o, f, c.  One tensor-core GEMM projects the
+ * inputs of all steps; the recurrence runs as one persistent cooperative kernel with R resident in
+ * shared memory across the SMs when Bt <= 64 and H % 32 == 0 (and the slices fit), else as one
+ * GEMM + one gate kernel per step. */
 int wdc_lstm(wdc_context* ctx, const float* X, const float* W, const float* R, const float* bias,
              const float* h0, const float* c0, float* Y, float* Yh, float* Yc, int64_t T,
              int64_t Bt, int64_t I, int64_t H);

@@ -127,3 +127,25 @@ def test_config5_detr_style(cuda_context, batch):
     assert [g.shape for g in got] == [(batch, 10, 12), (batch, 10, 4)]
     for g, w in zip(got, want):
         assert max_err_rel_linf(g, w) <= TOL
+
+
+@pytest.mark.parametrize("seq,batch,inp,hidden", [
+    (5, 3, 16, 32),      # persistent kernel, 4 units per CTA, batch not a multiple of 4
+    (7, 64, 32, 512),    # persistent kernel at the configuration's batch and hidden size
+    (4, 8, 32, 1024),    # persistent kernel, 8 units per CTA
+    (6, 2, 8, 24),       # hidden size not a multiple of 16: per-step path
+    (3, 70, 16, 32),     # batch above 64: per-step path
+])
+def test_lstm_shapes(cuda_context, seq, batch, inp, hidden):
+    model = zoo.lstm(seq, batch, inp, hidden)
+    x = zoo.make_input((seq, batch, inp))
+    want = ref_runner.run_model(model, [x])
+    before = cuda_context.stats()["launches"]
+    got = run_cuda(model, [x], cuda_context)
+    launches = cuda_context.stats()["launches"] - before
+    persistent = batch <= 64 and hidden % 32 == 0
+    # one projection GEMM (+ its weight split) and one recurrence kernel, against two launches per step
+    assert (launches <= 6) == persistent, launches
+    for g, w in zip(got, want):
+        assert g.shape == w.shape
+        assert max_err_rel_linf(g, w) <= 1e-4

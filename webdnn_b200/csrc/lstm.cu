@@ -1,7 +1,8 @@
 // ONNX LSTM (forward, default activations, gate order i,o,f,c).
 // Step 1: one GEMM projects all T steps of the input: P[T*Bt, 4H] = X * W^T.
-// Step 2: per time step, G = h_{t-1} * R^T + P_t (GEMM with P_t as the C operand), then a fused
-// gate kernel applies bias, sigmoid/tanh, updates c and h and writes Y_t.
+// Step 2: the recurrence, as one persistent cooperative kernel (lstm_persistent.cu) when the shape
+// fits it; otherwise per time step G = h_{t-1} * R^T + P_t (GEMM with P_t as the C operand) and a
+// fused gate kernel that applies bias, sigmoid/tanh, updates c and h and writes Y_t.
 // Scratch (P, G, and the running h/c state) comes from the context arena.
 #include <math.h>
 
@@ -9,6 +10,8 @@
 
 int wdc_simt_gemm(wdc_context* ctx, const wdc_gemm_desc* d, const float* A, const float* B, const float* C,
                   float* Y);
+int wdc_lstm_persistent(wdc_context* ctx, const float* P, const float* R, const float* bias, const float* h0,
+                        const float* c0, float* Y, float* Yh, float* Yc, int64_t T, int64_t Bt, int64_t H);
 
 __device__ __forceinline__ float sigmoid_ref(float x) { return (tanhf(x * 0.5f) + 1.f) * 0.5f; }
 
@@ -51,6 +54,23 @@ extern "C" int wdc_lstm(wdc_context* ctx, const float* X, const float* W, const 
   float *P = nullptr, *G = nullptr;
   int s = wdc_alloc(ctx, (T > 0 ? T : 1) * Bt * 4 * H * 4, (void**)&P);
   if (s != WDC_OK) return s;
+  if (T > 0) {
+    wdc_gemm_desc d = {};
+    d.batch = 1; d.m = T * Bt; d.n = 4 * H; d.k = I;
+    d.sa0 = I; d.sa1 = 1; d.sb0 = 1; d.sb1 = I;  // B = W^T
+    d.alpha = 1.f; d.beta = 0.f;
+    s = wdc_gemm(ctx, &d, X, W, nullptr, P);
+    if (s != WDC_OK) {
+      wdc_free(ctx, P);
+      return s;
+    }
+    // the whole recurrence as one persistent kernel when the shape fits it
+    s = wdc_lstm_persistent(ctx, P, R, bias, h0, c0, Y, Yh, Yc, T, Bt, H);
+    if (s != WDC_ERR_UNSUPPORTED) {
+      wdc_free(ctx, P);
+      return s;
+    }
+  }
   s = wdc_alloc(ctx, Bt * 4 * H * 4, (void**)&G);
   if (s != WDC_OK) {
     wdc_free(ctx, P);
@@ -62,13 +82,6 @@ extern "C" int wdc_lstm(wdc_context* ctx, const float* X, const float* W, const 
   if (s == WDC_OK) {
     if (c0) s = wdc_copy(ctx, Yc, c0, Bt * H * 4);
     else s = wdc_fill_u32(ctx, Yc, 0u, Bt * H);
-  }
-  if (s == WDC_OK && T > 0) {
-    wdc_gemm_desc d = {};
-    d.batch = 1; d.m = T * Bt; d.n = 4 * H; d.k = I;
-    d.sa0 = I; d.sa1 = 1; d.sb0 = 1; d.sb1 = I;  // B = W^T
-    d.alpha = 1.f; d.beta = 0.f;
-    s = wdc_gemm(ctx, &d, X, W, nullptr, P);
   }
   for (int64_t t = 0; t < T && s == WDC_OK; t++) {
     wdc_gemm_desc d = {};

@@ -82,7 +82,10 @@ struct TcProblem {
   int cblocks;        // K blocks per filter tap = ceil(ch_in / 32)
   int tile_n;         // 32, 64 or 128
   int tma_epi;        // 1: residual tiles and output tiles move by TMA (map_res, map_y)
-  int c4;             // 1: input has 4 channels per pixel, one K block per filter row, chunk j = tap kx
+  int c4;             // 1: input has 4 channels per pixel, one K block per filter row, chunk j = tap kx;
+                      // 2: the same with the row physically padded on the left and stride_w 2, so that taps
+                      //    (2j, 2j+1) are one 32-byte pixel pair: 4 loads of 128 x 32 bytes per K block
+  int in_w_pad;       // c4 == 2: pixels per padded input row (even)
   int tiles_m, tiles_n;   // their product fits 31 bits (checked on the host)
   // epilogue
   const float* scale;     // per channel or null
@@ -374,8 +377,9 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     const int64_t items = my_tiles * p.kblocks;
     const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)TMEM_A_COL0;
     // normal mode: 128-byte rows, 16-byte chunks XOR-swizzled by the row; 4-channel mode: 8 planes
-    // (one per filter tap of the row) of 128 rows x 16 bytes
-    const uint32_t row_off = (uint32_t)row * (p.c4 ? 16u : 128u);
+    // (one per filter tap of the row) of 128 rows x 16 bytes, or 4 planes (one per tap pair) of 128
+    // rows x 32 bytes with the 32B swizzle (chunk ^= bit 2 of the row)
+    const uint32_t row_off = (uint32_t)row * (p.c4 == 1 ? 16u : p.c4 == 2 ? 32u : 128u);
     const uint32_t sw = (uint32_t)(row & 7);
     int stage = 0, as = 0;
     uint32_t phase = 0, aphase = 0;
@@ -385,7 +389,10 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       const unsigned char* tile = ss->a_raw[as] + row_off;
 #pragma unroll
       for (int j = 0; j < 8; j++)
-        v[j] = *reinterpret_cast<const float4*>(tile + (p.c4 ? (uint32_t)j * (TILE_M * 16u) : (((uint32_t)j ^ sw) << 4)));
+        v[j] = *reinterpret_cast<const float4*>(
+            tile + (p.c4 == 1   ? (uint32_t)j * (TILE_M * 16u)
+                    : p.c4 == 2 ? (uint32_t)(j >> 1) * (TILE_M * 32u) + ((((uint32_t)j & 1u) ^ ((uint32_t)(row >> 2) & 1u)) << 4)
+                                : (((uint32_t)j ^ sw) << 4)));
       if (!mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 12)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t a_hi = lane_base + (uint32_t)(stage * 64);
@@ -429,7 +436,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         const int64_t n = m0 / hw;
         const uint32_t rem = (uint32_t)(m0 - n * hw);
         const int oy = (int)(rem / (uint32_t)p.out_w), ox = (int)rem - oy * p.out_w;
-        const int cw = ox * p.stride_w - p.pad_l, ch = oy * p.stride_h - p.pad_t;
+        const int cw = p.c4 == 2 ? ox : ox * p.stride_w - p.pad_l, ch = oy * p.stride_h - p.pad_t;
         // first K block of this CTA's rotation
         const int tap = rot / p.cblocks;
         int c0 = (rot - tap * p.cblocks) * BLOCK_K;
@@ -438,12 +445,15 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         for (int kb = 0; kb < p.kblocks; kb++) {
           if (!mbar_wait(&ss->a_empty_bar[stage], phase ^ 1, ss, p.status, 22)) { ok = false; break; }
           if (p.c4) {
-            // K block = filter row ky; one load of 128 pixels x 4 channels per tap of the row
-            if (lane == 0) mbar_arrive_expect_tx(&ss->a_full_bar[stage], (uint32_t)(p.k_w * TILE_M * 16));
+            // K block = filter row ky; one load of 128 pixels x 4 channels per tap of the row, or of 128
+            // pixel pairs x 8 channels per tap pair
+            const int nload = p.c4 == 2 ? (p.k_w + 1) >> 1 : p.k_w;
+            const int plane = p.c4 == 2 ? TILE_M * 32 : TILE_M * 16;
+            if (lane == 0) mbar_arrive_expect_tx(&ss->a_full_bar[stage], (uint32_t)(nload * plane));
             __syncwarp(0xffu);
-            if (lane < p.k_w)
-              tma_load_im2col(ss->a_raw[stage] + lane * (TILE_M * 16), &map_a, &ss->a_full_bar[stage], 0, cw, ch,
-                              (int)n, lane * p.dil_w, ky * p.dil_h);
+            if (lane < nload)
+              tma_load_im2col(ss->a_raw[stage] + lane * plane, &map_a, &ss->a_full_bar[stage], 0, cw, ch, (int)n,
+                              p.c4 == 2 ? lane : lane * p.dil_w, ky * p.dil_h);
             if (++ky == p.k_h) ky = 0;
           } else {
             mbar_arrive_expect_tx(&ss->a_full_bar[stage], (uint32_t)A_TILE_BYTES);
@@ -994,6 +1004,27 @@ __global__ void pad_channels4_kernel(const float* __restrict__ x, float* __restr
     reinterpret_cast<float4*>(x4)[i] = v;
   }
 }
+// Same with every image row shifted right by pad_l pixels into a zero-filled row of wp pixels: pixel pair
+// (2j, 2j+1) of the padded row is then the pair of taps (2j, 2j+1) of output column j for stride 2.
+__global__ void pad_channels4_rows_kernel(const float* __restrict__ x, float* __restrict__ x4, int64_t rows, int w,
+                                          int wp, int pad_l, int cin) {
+  int64_t total = rows * wp;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < total; i += step) {
+    const int64_t r = i / wp;
+    const int px = (int)(i - r * wp) - pad_l;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (px >= 0 && px < w) {
+      const float* s = x + (r * w + px) * cin;
+      v.x = s[0];
+      if (cin > 1) v.y = s[1];
+      if (cin > 2) v.z = s[2];
+      if (cin > 3) v.w = s[3];
+    }
+    reinterpret_cast<float4*>(x4)[i] = v;
+  }
+}
 // w [n][k_h][k_w][cin] -> hi/lo of [n][k_h][8][4] (zero where kx >= k_w or c >= cin)
 __global__ void split_tf32_c4_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo,
                                      int64_t rows, int k_h, int k_w, int cin, const float* __restrict__ scale,
@@ -1178,6 +1209,23 @@ bool encode_a_map(TcState* st, const TcProblem& p, const float* x, CUtensorMap* 
   if (p.c4 && p.k_w > 8) return false;
   const int64_t hw = (int64_t)p.out_h * p.out_w;
   const int64_t images = (p.M + hw - 1) / hw;
+  if (p.c4 == 2) {
+    // pixel pairs of the physically padded rows: 8 channels per position, in_w_pad / 2 positions per row,
+    // horizontal stride 1 and no horizontal padding; vertical geometry as given
+    const int wpos = p.in_w_pad / 2;
+    const int lower2[2] = {0, -p.pad_t};
+    const int upper2[2] = {(p.out_w - 1) - (wpos - 1), -p.pad_t + (p.out_h - 1) * p.stride_h - (p.in_h - 1)};
+    for (int i = 0; i < 2; i++)
+      if (lower2[i] < -128 || upper2[i] < -128 || upper2[i] > 127) return false;
+    if (p.stride_h < 1 || p.stride_h > 8 || (p.k_h - 1) * p.dil_h > 255 || images >= (1ll << 31)) return false;
+    cuuint64_t dims2[4] = {8, (cuuint64_t)wpos, (cuuint64_t)p.in_h, (cuuint64_t)images};
+    cuuint64_t strides2[3] = {32, (cuuint64_t)32 * wpos, (cuuint64_t)32 * wpos * p.in_h};
+    cuuint32_t estr2[4] = {1, 1, (cuuint32_t)p.stride_h, 1};
+    CUresult r2 = st->encode_im2col(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void*)x, dims2, strides2, lower2, upper2,
+                                    8, TILE_M, estr2, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r2 == CUDA_SUCCESS;
+  }
   const int lower[2] = {-p.pad_l, -p.pad_t};
   const int upper[2] = {-p.pad_l + (p.out_w - 1) * p.stride_w - (p.in_w - 1),
                         -p.pad_t + (p.out_h - 1) * p.stride_h - (p.in_h - 1)};
@@ -1234,7 +1282,9 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
   }
   CUtensorMap map_a;
   const size_t smem = sizeof(SharedStorage) + 1024;
-  if (encode_a_map(st, p, x, &map_a))
+  const bool a_by_tma = encode_a_map(st, p, x, &map_a);
+  if (!a_by_tma && p.c4 == 2) return WDC_ERR_UNSUPPORTED;  // the paired layout exists only for the TMA path
+  if (a_by_tma)
     tc_igemm_kernel<true><<<grid, NUM_THREADS, smem, ctx->stream>>>(p, x, we->map_hi, we->map_lo, map_a, map_y, map_res, y);
   else
     tc_igemm_kernel<false><<<grid, NUM_THREADS, smem, ctx->stream>>>(p, x, we->map_hi, we->map_lo, we->map_hi, map_y,
@@ -1297,13 +1347,21 @@ int wdc_tc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, cons
   // Few input channels (the network's first convolution): pad the pixels to 4 channels so that one
   // 16-byte chunk is one pixel, and lay the filter out as 8 taps x 4 channels per filter row.
   float* x4 = nullptr;
-  const int64_t pixels = d->batch * d->in_h * d->in_w;
+  // stride-2 stems: pad the rows physically so that two taps are one 32-byte pixel pair
+  const bool pairs = d->stride_w == 2 && d->dil_w == 1 && tc_state(ctx)->encode_im2col != nullptr && !(getenv("WDC_TC_NO_PAIRS"));
+  const int wp = pairs ? (int)(2 * d->out_w + 6) : (int)d->in_w;
+  const int64_t pixels = d->batch * d->in_h * wp;
   int s = wdc_alloc(ctx, pixels * 16, (void**)&x4);
   if (s != WDC_OK) return s;
-  pad_channels4_kernel<<<grid_for(ctx, pixels, 256, 8), 256, 0, ctx->stream>>>(x, x4, pixels, (int)d->ch_in);
+  if (pairs)
+    pad_channels4_rows_kernel<<<grid_for(ctx, pixels, 256, 8), 256, 0, ctx->stream>>>(
+        x, x4, d->batch * d->in_h, (int)d->in_w, wp, (int)d->pad_l, (int)d->ch_in);
+  else
+    pad_channels4_kernel<<<grid_for(ctx, pixels, 256, 8), 256, 0, ctx->stream>>>(x, x4, pixels, (int)d->ch_in);
   s = wdc_check_launch(ctx, "pad_channels4_kernel");
   if (s == WDC_OK) {
-    p.c4 = 1;
+    p.c4 = pairs ? 2 : 1;
+    p.in_w_pad = wp;
     p.ch_in = 4;
     p.K = (int)d->k_h * 32;
     p.cblocks = 1;

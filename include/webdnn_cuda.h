@@ -198,6 +198,11 @@ int wdc_strided_copy(wdc_context* ctx, const void* src, void* dst, int ndim, con
 int wdc_gather(wdc_context* ctx, const void* data, const int32_t* idx, void* out, int64_t outer,
                int64_t axis_len, int64_t inner, int64_t n_idx);
 
+/* 8-bit weight codec of the WDN2 tensor container (core/tensorDecoder/decodeTensorEightbit.ts:36-61): `codes`
+ * holds one byte per element (the inflated zlib stream, uploaded as bytes); out[i] = level[codes[i] & 127] * scale,
+ * negated when bit 7 is set, bit-identical to the reference's table lookup.  Both buffers 16-byte aligned. */
+int wdc_decode_eightbit(wdc_context* ctx, const void* codes, float* out, int64_t n, float scale);
+
 /* ---- LSTM -----------------------------------------------------------------------------------
  * ONNX LSTM, forward direction, default activations, no peepholes (not in the reference; ONNX
  * operator spec).  X [T, Bt, I], W [4H, I], R [4H, H], bias [8H] or NULL, h0/c0 [Bt, H] or NULL;

@@ -149,3 +149,35 @@ def test_lstm_shapes(cuda_context, seq, batch, inp, hidden):
     for g, w in zip(got, want):
         assert g.shape == w.shape
         assert max_err_rel_linf(g, w) <= 1e-4
+
+
+def test_external_eightbit_weights_decoded_on_device(cuda_context, tmp_path):
+    """A model whose weights live in a WDN2 container with the 8-bit codec: the large tensors reach
+    the GPU as codes and are expanded there; the result equals the oracle run on the host-decoded
+    weights (same values bit for bit, so the usual tolerance applies)."""
+    import os
+    from webdnn_b200 import onnx_io, tensor_export, tensor_loader
+    from webdnn_b200.backend import CPUTensor
+    from webdnn_b200.runner import load
+    model = zoo.mlp(64)
+    tensors = {t.name: np.asarray(t.array).reshape(t.dims) for t in model.graph.initializer}
+    paths = tensor_export.serialize_tensors(str(tmp_path / "weight-{}.bin"), tensors, split_size=1 << 20,
+                                            compression_algorithm=1)
+    decoded = {k: v.numpy() for k, v in tensor_loader.TensorLoader(paths).load_all().items()}
+    host_model = zoo.mlp(64)
+    for t in host_model.graph.initializer:
+        t.array = decoded[t.name].reshape(t.dims)
+    del model.graph.initializer[:]
+    model.metadata_props["WebDNN2.WeightPaths"] = ":".join(os.path.basename(p) for p in paths)
+    onnx_io.save_model(model, str(tmp_path / "model.onnx"))
+    x = zoo.make_input((64, 784), "uniform")
+    (want,) = ref_runner.run_model(host_model, [x])
+    before = cuda_context.stats()["h2d_bytes"]
+    r = load(str(tmp_path), backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": cuda_context}})
+    got = r.run([CPUTensor.from_array(x)])[0].numpy()
+    moved = cuda_context.stats()["h2d_bytes"] - before
+    _all_on_cuda(r)
+    r.dispose()
+    assert max_err_rel_linf(got, want) <= TOL
+    n_weights = sum(v.size for v in tensors.values())
+    assert moved < 2 * n_weights + x.nbytes   # codes (1 byte each), not 4-byte floats, crossed the bus

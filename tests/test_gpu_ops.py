@@ -189,3 +189,17 @@ def test_gemm_larger_and_odd_shapes(cuda_context):
         (want,) = ref_runner.run_model(model, [a, b, c])
         (got,) = run_cuda(model, [a, b, c], cuda_context)
         assert max_err_rel_linf(got, want) <= TOL, (m, n, k)
+
+
+def test_eightbit_decode_on_device_is_bit_exact(cuda_context):
+    """wdc_decode_eightbit against the host decoder (itself pinned to the reference's table and
+    encoder by tests/test_tensor_loader.py) for every code value, odd lengths and several scales."""
+    from webdnn_b200 import tensor_loader
+    rng = np.random.default_rng(9)
+    for n, scale in [(256, 1.0), (1, 0.37), (15, 1e-20), (16, 3.25), (100003, 0.0123), (1 << 20, 7.5)]:
+        codes = rng.integers(0, 256, n, dtype=np.uint8) if n != 256 else np.arange(256, dtype=np.uint8)
+        want = tensor_loader.scaled_table(scale)[codes]
+        t = cuda_context.decode_eightbit(codes, scale, [n])
+        got = t.get_data()
+        t.dispose()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))

@@ -98,6 +98,28 @@ class CPUTensor(TensorImpl):
         pass
 
 
+class EightbitCPUTensor(CPUTensor):
+    """A float32 initializer still held as the 8-bit codes of a WDN2 container.  On the host it decodes
+    itself at first access; a cuda context moves it by uploading the codes and decoding on the
+    device (``WebDNNCudaContext.move_tensor``)."""
+
+    def __init__(self, dims: Sequence[int], codes: np.ndarray, scale: float):
+        TensorImpl.__init__(self, dims, "float32", "cpu")
+        self.codes = np.ascontiguousarray(codes, dtype=np.uint8)
+        if self.codes.size != self.length:
+            raise ValueError("EightbitCPUTensor: code count does not match dims")
+        self.scale = float(scale)
+        self._decoded: Optional[np.ndarray] = None
+        self.use_external_buffer = False
+
+    @property
+    def data(self) -> np.ndarray:
+        if self._decoded is None:
+            from .tensor_loader import scaled_table
+            self._decoded = scaled_table(self.scale)[self.codes]
+        return self._decoded
+
+
 class CudaSharedBuffer:
     """Refcounted device allocation shared by aliases of one tensor."""
 
@@ -305,8 +327,27 @@ class WebDNNCudaContext:
         return CudaTensor(self, dims, data_type, layout=layout)
 
     def move_tensor(self, tensor, option=None) -> CudaTensor:
+        if isinstance(tensor, EightbitCPUTensor):
+            return self.decode_eightbit(tensor.codes, tensor.scale, tensor.dims)
         dst = CudaTensor(self, tensor.dims, tensor.data_type)
         dst.set_data(tensor.get_data())
+        return dst
+
+    def decode_eightbit(self, codes: np.ndarray, scale: float, dims: Sequence[int]) -> CudaTensor:
+        """float32 tensor from the 8-bit codes of a WDN2 container: the codes (1 byte per element)
+        are uploaded and expanded on the device."""
+        codes = np.ascontiguousarray(codes, dtype=np.uint8)
+        dst = CudaTensor(self, dims, "float32")
+        if dst.length != codes.size:
+            raise ValueError("decode_eightbit: code count does not match dims")
+        if codes.size:
+            staging = self._alloc(codes.size)
+            try:
+                self._upload(staging, codes)
+                self._call("wdc_decode_eightbit", c_void_p(staging), c_void_p(dst.ptr), codes.size,
+                           ctypes.c_float(scale))
+            finally:
+                self._free(staging)  # stream-ordered: reused only by work queued after the decode
         return dst
 
     def prefetch_tensor(self, tensor: CPUTensor) -> CudaTensor:

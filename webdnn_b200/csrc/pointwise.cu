@@ -473,3 +473,69 @@ extern "C" int wdc_channel_affine(wdc_context* ctx, const float* x, const float*
                                                                            channels, inner, relu, vec_ok);
   return wdc_check_launch(ctx, "channel_affine_kernel");
 }
+
+// ---- 8-bit weight codec (WDN2 tensor container) ------------------------------------------------
+// code b -> level[b & 127] * scale, negated when bit 7 is set.  The 128 levels are the format's
+// constants (core/tensorDecoder/decodeTensorEightbit.ts:5-34).  The reference builds a 256-entry
+// float32 table per tensor from level * scale evaluated in double (:52-55); so does each block here,
+// which makes the output bit-identical.  16 codes (one 16-byte load) per thread per step.
+__constant__ double kEightbitLevels[128] = {
+    0.0, 2.750000021e-6, 7.249999726e-6, 1.875000089e-5, 3.624999954e-5, 5.874999624e-5, 8.624999464e-5,
+    1.437500032e-4, 2.312500001e-4, 3.187500115e-4, 4.062500084e-4, 5.187499919e-4, 6.562499912e-4,
+    7.937499322e-4, 9.312499315e-4, 1.218750025e-3, 1.65624998e-3, 2.093750052e-3, 2.531250007e-3,
+    2.968749963e-3, 3.406249918e-3, 3.843750106e-3, 4.281249829e-3, 4.843750037e-3, 5.531250034e-3,
+    6.218749564e-3, 6.90624956e-3, 7.593749557e-3, 8.281249553e-3, 8.968749084e-3, 9.656248614e-3,
+    1.109374966e-2, 1.328125037e-2, 1.546875015e-2, 1.765624993e-2, 1.98437497e-2, 2.203124948e-2,
+    2.421874925e-2, 2.640625089e-2, 2.859375067e-2, 3.078125045e-2, 3.296874836e-2, 3.515625e-2,
+    3.734375164e-2, 3.953124955e-2, 4.171875119e-2, 4.390624911e-2, 4.671875015e-2, 5.01562506e-2,
+    5.359374732e-2, 5.703124776e-2, 6.046874821e-2, 6.390624493e-2, 6.734374911e-2, 7.078124583e-2,
+    7.421874255e-2, 7.765624672e-2, 8.109374344e-2, 8.453124017e-2, 8.796874434e-2, 9.140624106e-2,
+    9.484373778e-2, 9.828124195e-2, 1.0546875e-1, 1.16406247e-1, 1.27343744e-1, 1.38281256e-1, 1.49218753e-1,
+    1.6015625e-1, 1.71093747e-1, 1.82031244e-1, 1.92968756e-1, 2.03906253e-1, 2.1484375e-1, 2.25781247e-1,
+    2.36718744e-1, 2.47656256e-1, 2.585937381e-1, 2.6953125e-1, 2.804687619e-1, 2.91406244e-1, 3.02343756e-1,
+    3.132812381e-1, 3.2421875e-1, 3.351562619e-1, 3.46093744e-1, 3.57031256e-1, 3.679687381e-1, 3.7890625e-1,
+    3.898437619e-1, 4.00781244e-1, 4.11718756e-1, 4.226562381e-1, 4.3359375e-1, 4.445312619e-1, 4.58593756e-1,
+    4.757812321e-1, 4.929687381e-1, 5.101562142e-1, 5.2734375e-1, 5.445312262e-1, 5.617187023e-1,
+    5.789062381e-1, 5.960937142e-1, 6.1328125e-1, 6.304687262e-1, 6.476562023e-1, 6.648437381e-1,
+    6.820312142e-1, 6.992186904e-1, 7.164062262e-1, 7.335937023e-1, 7.507811785e-1, 7.679687142e-1,
+    7.851561904e-1, 8.023436666e-1, 8.195312023e-1, 8.367186785e-1, 8.539061546e-1, 8.710936904e-1,
+    8.882811666e-1, 9.054686427e-1, 9.226561785e-1, 9.398436546e-1, 9.570311308e-1, 9.742186666e-1,
+    9.914061427e-1, 1.0};
+
+__global__ void __launch_bounds__(256) decode_eightbit_kernel(const uint8_t* __restrict__ codes,
+                                                              float* __restrict__ out, int64_t n, float scale) {
+  __shared__ float table[256];
+  {
+    const int i = threadIdx.x;
+    const double v = kEightbitLevels[i & 127] * (double)scale * (i < 128 ? 1.0 : -1.0);
+    table[i] = (float)v;
+  }
+  __syncthreads();
+  const int64_t groups = n / 16;
+  int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; g < groups; g += step) {
+    const uint4 c = __ldg(reinterpret_cast<const uint4*>(codes) + g);
+    const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+    float4* dst = reinterpret_cast<float4*>(out) + g * 4;
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+      dst[j] = make_float4(table[w[j] & 255u], table[(w[j] >> 8) & 255u], table[(w[j] >> 16) & 255u],
+                           table[w[j] >> 24]);
+  }
+  // tail of fewer than 16 codes
+  for (int64_t i = groups * 16 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += step)
+    out[i] = table[codes[i]];
+}
+
+extern "C" int wdc_decode_eightbit(wdc_context* ctx, const void* codes, float* out, int64_t n, float scale) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_decode_eightbit: null context");
+  wdc_note_write(ctx, out);
+  WDC_REQUIRE(ctx, n >= 0 && (n == 0 || (codes && out)), "wdc_decode_eightbit: bad buffer or count");
+  WDC_REQUIRE(ctx, (((uintptr_t)codes | (uintptr_t)out) & 15) == 0, "wdc_decode_eightbit: buffers must be 16-byte aligned");
+  if (n == 0) return WDC_OK;
+  DeviceGuard g(ctx->device);
+  decode_eightbit_kernel<<<grid_for(ctx, (n + 15) / 16, 256, 8), 256, 0, ctx->stream>>>((const uint8_t*)codes, out, n,
+                                                                                      scale);
+  return wdc_check_launch(ctx, "decode_eightbit_kernel");
+}

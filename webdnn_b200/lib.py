@@ -71,6 +71,7 @@ SIGNATURES = {
     "wdc_host_alloc": (c_int, [c_void_p, c_int64, POINTER(c_void_p)]),
     "wdc_host_free": (c_int, [c_void_p, c_void_p]),
     "wdc_upload": (c_int, [c_void_p, c_void_p, c_void_p, c_int64]),
+    "wdc_decode_eightbit": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_float]),
     "wdc_upload_async": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, POINTER(c_int64)]),
     "wdc_wait_upload": (c_int, [c_void_p, c_int64]),
     "wdc_download": (c_int, [c_void_p, c_void_p, c_void_p, c_int64]),

@@ -25,10 +25,11 @@ from typing import Dict, List, Optional, Sequence, Union
 
 import numpy as np
 
-from . import onnx_io
-from .backend import CPUTensor, WebDNNCPUContext, WebDNNCudaContext
+from . import onnx_io, tensor_loader
+from .backend import CPUTensor, EightbitCPUTensor, WebDNNCPUContext, WebDNNCudaContext
 from .model_transform import find_tensor_release_timing, model_transform
 from .onnx_io import FLOAT, INT32, INT64, Model, clip_long
+from .tensor_loader import TensorLoader
 from .operator_table import instantiate_operator, register_operators, registered_op_types
 
 logger = logging.getLogger("WebDNN.runner")
@@ -66,6 +67,8 @@ class Runner:
         self.node_performances: List[dict] = []
 
     # ---- runnerImpl.ts:88-134
+    DEVICE_DECODE_MIN_ELEMENTS = 4096  # 8-bit initializers at least this large are decoded on the device
+
     def load_model(self, source: Union[str, bytes, Model], onnx_basename: str = "model.onnx") -> None:
         if isinstance(source, Model):
             model = onnx_io.decode_model(onnx_io.encode_model(source))  # private copy
@@ -74,12 +77,35 @@ class Runner:
         else:
             path = os.path.join(source, onnx_basename) if os.path.isdir(source) else source
             model = onnx_io.load_model(path)
+        # external initializers (runnerImpl.ts:235-270): "WebDNN2.WeightPaths" names the parts of one
+        # WDN2 container beside the model.  Small or uncompressed tensors join the graph's own
+        # initializers before the load-time rewrite (which folds BatchNormalization parameters);
+        # large 8-bit ones stay as codes and are expanded on the device when first moved there.
+        lazy = []
+        weight_paths = model.metadata_props.get("WebDNN2.WeightPaths")
+        if weight_paths and isinstance(source, str):
+            directory = source if os.path.isdir(source) else os.path.dirname(source)
+            loader = TensorLoader([os.path.join(directory, bn) for bn in weight_paths.split(":")],
+                                  self.backend_contexts["cpu"])
+            own = {t.name: i for i, t in enumerate(model.graph.initializer)}
+            for rec in loader.records():
+                if rec.compression == 1 and "cuda" in self.backend_order and rec.numel >= self.DEVICE_DECODE_MIN_ELEMENTS:
+                    lazy.append(rec)
+                    continue
+                t = onnx_io.make_tensor(rec.name, tensor_loader.decode(rec).reshape(rec.dims))
+                if rec.name in own:
+                    model.graph.initializer[own[rec.name]] = t
+                else:
+                    model.graph.initializer.append(t)
         model_transform(model, self.backend_order)
         if not model.opset_import:
             raise ValueError("opsetImport is empty")
         self.opset = int(model.opset_import[0][1])
         self.model = model
         self.initializer_tensors = self._extract_initializer_tensor()
+        for rec in lazy:
+            codes, scale = tensor_loader.eightbit_codes(rec)
+            self.initializer_tensors[rec.name] = EightbitCPUTensor(rec.dims, codes, scale)
         for md_key, md_value in model.metadata_props.items():
             if md_key == "WebDNN2.TensorMoveOptions":
                 self.tensor_move_options = json.loads(md_value)

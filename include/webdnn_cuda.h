@@ -198,6 +198,24 @@ int wdc_strided_copy(wdc_context* ctx, const void* src, void* dst, int ndim, con
 int wdc_gather(wdc_context* ctx, const void* data, const int32_t* idx, void* out, int64_t outer,
                int64_t axis_len, int64_t inner, int64_t n_idx);
 
+/* ConvTranspose, 2-D, NCHW (operators/cpu/operators/standard/convtranspose.ts:30-263, shape rule
+ * base/convtranspose.ts:34-104): x [batch, ch_in, in_h, in_w], w [ch_in, ch_out_per_group, k_h, k_w],
+ * bias [group * ch_out_per_group] or NULL, y [batch, group * ch_out_per_group, out_h, out_w].  Rounding
+ * points as in the reference: channel contraction per tap in double -> float32, taps summed in
+ * double -> float32, bias added in float32. */
+typedef struct wdc_convt_desc {
+  int64_t batch, ch_in, in_h, in_w;
+  int64_t ch_out_per_group, group, k_h, k_w, out_h, out_w;
+  int64_t stride_h, stride_w, pad_t, pad_l, dil_h, dil_w;
+} wdc_convt_desc;
+int wdc_conv_transpose2d(wdc_context* ctx, const wdc_convt_desc* d, const float* x, const float* w,
+                         const float* bias, float* y);
+/* InstanceNormalization over NCHW rows (operators/cpu/operators/standard/instancenormalization.ts:24-53):
+ * per (batch, channel): y = x * (scale[c] * invstd) + (bias[c] - mean * scale[c] * invstd), statistics and
+ * arithmetic in double.  eps is passed as the reference evaluates it (see CudaInstanceNormalization). */
+int wdc_instance_norm(wdc_context* ctx, const float* x, const float* scale, const float* bias, float* y,
+                      int64_t batch, int64_t ch, int64_t area, double eps);
+
 /* 8-bit weight codec of the WDN2 tensor container (core/tensorDecoder/decodeTensorEightbit.ts:36-61): `codes`
  * holds one byte per element (the inflated zlib stream, uploaded as bytes); out[i] = level[codes[i] & 127] * scale,
  * negated when bit 7 is set, bit-identical to the reference's table lookup.  Both buffers 16-byte aligned. */

@@ -375,3 +375,98 @@ def slice_(x, starts, ends, axes=None, steps=None) -> np.ndarray:
     if any(d == 0 for d in dims):
         return np.empty(dims, x.dtype)
     return strided_copy(x, dims, sstr, soff)
+
+
+def conv_transpose2d(x, w, bias=None, strides=(1, 1), pads=(0, 0, 0, 0), dilations=(1, 1), group=1,
+                     output_padding=(0, 0)) -> np.ndarray:
+    """convtranspose.ts:30-263 with its rounding points: the channel contraction of every (input
+    pixel, output channel, tap) in double, stored as float32 (matmul :218-240); the taps that land on
+    an output pixel summed in double in (k0, k1) order, stored as float32 (col2im :139-196); bias
+    added in float32 (:242-262).  Shape rule: base/convtranspose.ts:53-72."""
+    x, w = _f32(x), _f32(w)
+    batch, ch_in, in_h, in_w = x.shape
+    cig, cog, kh, kw = ch_in // group, w.shape[1], w.shape[2], w.shape[3]
+    out_h = strides[0] * (in_h - 1) + output_padding[0] + (kh - 1) * dilations[0] + 1 - pads[0] - pads[2]
+    out_w = strides[1] * (in_w - 1) + output_padding[1] + (kw - 1) * dilations[1] + 1 - pads[1] - pads[3]
+    y = np.zeros((batch, group * cog, out_h, out_w), np.float64)
+    for g in range(group):
+        xg = x[:, g * cig:(g + 1) * cig].astype(np.float64)
+        wg = w[g * cig:(g + 1) * cig].astype(np.float64)
+        # NB: einsum's double sum over ci may associate differently from the JS loop; the result is
+        # rounded to float32 right after, so a difference needs a near-tie in the double sum
+        part = np.einsum("bchw,cokl->bohwkl", xg, wg).astype(np.float32).astype(np.float64)
+        for k0 in range(kh):
+            for k1 in range(kw):
+                for i0 in range(in_h):
+                    o0 = i0 * strides[0] - pads[0] + k0 * dilations[0]
+                    if o0 < 0 or o0 >= out_h:
+                        continue
+                    for i1 in range(in_w):
+                        o1 = i1 * strides[1] - pads[1] + k1 * dilations[1]
+                        if o1 < 0 or o1 >= out_w:
+                            continue
+                        y[:, g * cog:(g + 1) * cog, o0, o1] += part[:, :, i0, i1, k0, k1]
+    out = y.astype(np.float32)
+    if bias is not None:
+        out = (out + _f32(bias)[None, :, None, None]).astype(np.float32)
+    return out
+
+
+def instance_norm(x, scale, bias, eps) -> np.ndarray:
+    """instancenormalization.ts:24-53: left-to-right double sums per (batch, channel) row."""
+    x = _f32(x)
+    n, c = x.shape[:2]
+    rows = x.reshape(n, c, -1).astype(np.float64)
+    length = rows.shape[2]
+    total = np.cumsum(rows, axis=2)[:, :, -1]
+    sq = np.cumsum(rows * rows, axis=2)[:, :, -1]
+    mean = total / length
+    variance = sq / length - mean * mean
+    invstd = 1.0 / np.sqrt(variance + eps)
+    chscale = _f32(scale).astype(np.float64)[None, :] * invstd
+    chbias = -mean * chscale + _f32(bias).astype(np.float64)[None, :]
+    return (rows * chscale[:, :, None] + chbias[:, :, None]).astype(np.float32).reshape(x.shape)
+
+
+def pad(x, pads, mode="constant", value=0) -> np.ndarray:
+    """pad11.ts: every mode maps an output index d to an input index per axis: constant i = d - pad
+    (outside -> value, :139-149), edge clamps (:900-907), reflect folds with period 2n-2 (:408-420)."""
+    x = np.asarray(x)
+    nd = x.ndim
+    if nd > 6:
+        raise ValueError(f"Pad: input.ndim = {nd} > 6 is not yet supported")
+    pads = [int(p) for p in pads]
+    out_shape = [x.shape[i] + pads[i] + pads[i + nd] for i in range(nd)]
+    maps, valid = [], []
+    for i in range(nd):
+        n = x.shape[i]
+        src = np.arange(out_shape[i], dtype=np.int64) - pads[i]
+        ok = (src >= 0) & (src < n)
+        if mode == "edge":
+            src = np.clip(src, 0, n - 1)
+        elif mode == "reflect":
+            period = n * 2 - 2
+            with np.errstate(divide="ignore", invalid="ignore"):
+                folded = np.where(src < 0, np.fmod(-src, period) if period else 0, np.fmod(src, period) if period else 0)
+            folded = np.where(folded >= n, n * 2 - folded - 2, folded)
+            src = np.where(ok, src, folded)
+        elif mode != "constant":
+            raise ValueError(f"Pad: unknown mode {mode}")
+        maps.append(src)
+        valid.append(ok)
+    if mode == "constant":
+        out = np.full(out_shape, value, dtype=x.dtype)
+        if all(v.any() for v in valid) or nd == 0:
+            dst = tuple(np.nonzero(v)[0] for v in valid)
+            out[np.ix_(*dst)] = x[np.ix_(*[m[v] for m, v in zip(maps, valid)])] if nd else x
+        return out
+    return x[np.ix_(*maps)] if nd else x.copy()
+
+
+def tile(x, repeats) -> np.ndarray:
+    """tile.ts:19-70: out[d] = in[d mod dims] (at most 4-D in the reference)."""
+    x = np.asarray(x)
+    if x.ndim > 4:
+        raise ValueError(f"Tile: input.ndim = {x.ndim} > 4 is not yet supported")
+    idx = [np.arange(x.shape[i] * int(repeats[i])) % max(x.shape[i], 1) for i in range(x.ndim)]
+    return x[np.ix_(*idx)] if x.ndim else x.copy()

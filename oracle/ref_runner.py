@@ -202,6 +202,25 @@ def run_node(node, ins: List[np.ndarray], opset: int) -> List[np.ndarray]:
     if t == "LayerNormalization":
         return [ops.layernorm_chain(ins[0], ins[1] if len(ins) > 1 else None, ins[2] if len(ins) > 2 else None,
                                     float(np.float32(a.get("epsilon", 1e-5))))]
+    if t == "ConvTranspose":
+        if a.get("auto_pad", "NOTSET") != "NOTSET":
+            raise ValueError("ConvTranspose: auto_pad !== NOTSET is not yet supported.")
+        if a.get("output_shape"):
+            raise ValueError("ConvTranspose: explicit output_shape is not yet supported.")
+        return [ops.conv_transpose2d(ins[0], ins[1], ins[2] if len(ins) > 2 else None, a.get("strides") or (1, 1),
+                                     a.get("pads") or (0, 0, 0, 0), a.get("dilations") or (1, 1), a.get("group", 1),
+                                     a.get("output_padding") or (0, 0))]
+    if t == "InstanceNormalization":
+        # instancenormalization.ts:18 reads epsilon with getAttrInt: a float attribute has integer field 0
+        eps = 1e-5 if "epsilon" not in a else (float(a["epsilon"]) if isinstance(a["epsilon"], int) else 0.0)
+        return [ops.instance_norm(ins[0], ins[1], ins[2], eps)]
+    if t == "Pad":
+        if opset < 11:
+            raise NotImplementedError(f"Operator implementation for {t}, opset={opset} does not exist.")
+        value = ins[2].reshape(-1)[0] if len(ins) > 2 else 0
+        return [ops.pad(ins[0], [int(v) for v in ins[1].reshape(-1)], a.get("mode", "constant"), value)]
+    if t == "Tile":
+        return [ops.tile(ins[0], [int(v) for v in ins[1].reshape(-1)])]
     raise NotImplementedError(f"Operator implementation for {t}, opset={opset} does not exist.")
 
 

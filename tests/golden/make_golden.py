@@ -169,6 +169,66 @@ add("lstm", "LSTM", dict(hidden_size=H, direction="forward"), [X, W, R, Bv],
 x = f32(4, 9, 11)
 add("argmax", "ArgMax", dict(axis=1, keepdims=0), [x], [t64(x).argmax(1).numpy().astype(np.int32)])
 
+
+# ---- operators of the cpu backend outside the benchmark configurations (make_models.py:583, 645-676, 731)
+def convt_case(name, cin, cout, k, stride, pad, outpad, groups, dil, bias, shape):
+    x = f32(*shape)
+    w = f32(cin, cout // groups, k, k, scale=(2.0 / (cin * k * k)) ** 0.5)
+    b = f32(cout) if bias else None
+    y = F.conv_transpose2d(t64(x), t64(w), t64(b) if bias else None, stride, pad, outpad, groups, dil)
+    attrs = dict(kernel_shape=[k, k], strides=[stride, stride], pads=[pad] * 4, dilations=[dil, dil], group=groups,
+                 output_padding=[outpad, outpad])
+    add(name, "ConvTranspose", attrs, [x, w] + ([b] if bias else []), [y.numpy().astype(np.float32)])
+
+
+convt_case("convtranspose1", 16, 32, 3, 1, 0, 0, 1, 1, False, (1, 16, 7, 7))
+convt_case("convtranspose2", 16, 32, 3, 2, 0, 0, 1, 1, True, (2, 16, 7, 9))
+convt_case("convtranspose3", 16, 32, 3, 2, 0, 0, 2, 1, False, (2, 16, 7, 9))
+convt_case("convtranspose4", 16, 32, 3, 2, 1, 1, 1, 1, False, (2, 16, 7, 9))
+convt_case("convtranspose5", 16, 32, 3, 2, 1, 1, 1, 2, False, (2, 16, 7, 9))
+
+
+def pad_case(name, torch_pads, shape, mode="constant", constant=0.0):
+    """torch_pads is F.pad's order (last axis first); ONNX wants all begins then all ends."""
+    x = f32(*shape)
+    nd = len(shape)
+    begins, ends = [0] * nd, [0] * nd
+    for j in range(len(torch_pads) // 2):
+        begins[nd - 1 - j], ends[nd - 1 - j] = torch_pads[2 * j], torch_pads[2 * j + 1]
+    tmode = {"constant": "constant", "reflect": "reflect", "edge": "replicate"}[mode]
+    xt = torch.tensor(x)
+    if mode == "constant":
+        y = F.pad(xt, torch_pads, value=constant)
+    else:
+        y = F.pad(xt, torch_pads, mode=tmode)
+    ins = [x, np.array(begins + ends, np.int64)]
+    if mode == "constant" and constant != 0.0:
+        ins.append(np.array(constant, np.float32))
+    add(name, "Pad", dict(mode=mode, _opset=11), ins, [y.numpy()])
+
+
+pad_case("pad1", (1, 2), (2,))
+pad_case("pad2", (1, 2, 3, 4), (2, 3))
+pad_case("pad3", (1, 2, 3, 4, 5, 6), (2, 3, 4))
+pad_case("pad4", (1, 2, 3, 4, 5, 6, 7, 8), (2, 3, 4, 5))
+pad_case("pad5", (1, 2, 1, 0, 2, 1, 0, 1, 1, 1), (2, 3, 4, 5, 6))
+pad_case("pad6", (1, 0, 0, 1, 1, 1, 2, 0, 0, 2, 1, 1), (2, 3, 4, 5, 6, 7))
+pad_case("padc2", (1, 2, 3, 4), (2, 3), constant=-1.0)
+pad_case("padc4", (1, 2, 3, 4, 5, 6, 7, 8), (2, 3, 4, 5), constant=-1.0)
+pad_case("padr3", (2, 1), (2, 3, 4), mode="reflect")
+pad_case("padr4", (4, 3, 2, 1), (2, 3, 4, 5), mode="reflect")
+pad_case("padr5", (6, 5, 4, 3, 2, 1), (3, 4, 5, 6, 7), mode="reflect")
+pad_case("pade3", (2, 1), (2, 3, 4), mode="edge")
+pad_case("pade4", (4, 3, 2, 1), (2, 3, 4, 5), mode="edge")
+pad_case("pade5", (6, 5, 4, 3, 2, 1), (3, 4, 5, 6, 7), mode="edge")
+xt_ = f32(3, 4, 5, 6, positive=True)
+add("tile", "Tile", dict(_opset=6), [xt_, np.array([2, 3, 1, 2], np.int64)], [np.tile(xt_, (2, 3, 1, 2))])
+xi = f32(3, 4, 5, 6, positive=True)
+gi, bi = f32(4, positive=True), f32(4, positive=True)
+# epsilon left at its default: the reference reads a given epsilon as 0 (instancenormalization.ts:18)
+add("instancenorm1", "InstanceNormalization", {}, [xi, gi, bi],
+    [F.instance_norm(t64(xi), weight=t64(gi), bias=t64(bi), eps=1e-5).numpy().astype(np.float32)])
+
 flat = {}
 meta = {}
 for name, c in cases.items():

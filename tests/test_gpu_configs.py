@@ -181,3 +181,33 @@ def test_external_eightbit_weights_decoded_on_device(cuda_context, tmp_path):
     assert max_err_rel_linf(got, want) <= TOL
     n_weights = sum(v.size for v in tensors.values())
     assert moved < 2 * n_weights + x.nbytes   # codes (1 byte each), not 4-byte floats, crossed the bus
+
+
+@pytest.mark.parametrize("compression", [0, 1])
+def test_offline_bundle_runs_on_cuda(cuda_context, tmp_path, compression):
+    """A bundle written by optimize_model (fused graph + WDN2 weights) gives the load-time-rewrite
+    result: identical for raw weights; with the 8-bit codec, the oracle on the decoded weights."""
+    from webdnn_b200 import onnx_io, optimize_model, tensor_loader
+    from webdnn_b200.backend import CPUTensor
+    from webdnn_b200.runner import load
+    model = zoo.conv_bn_relu(4, 64, 28)
+    info = optimize_model.optimize(model, str(tmp_path), compression)
+    x = zoo.make_input((4, 64, 28, 28))
+    r = load(str(tmp_path), backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": cuda_context}},
+             onnx_basename="model-cuda.onnx")
+    got = r.run([CPUTensor.from_array(x)])[0].numpy()
+    _all_on_cuda(r)
+    assert [t for _, t, _ in r.node_backends] == ["CudaConvFused"]
+    r.dispose()
+    if compression == 0:
+        (want,) = ref_runner.run_model(zoo.conv_bn_relu(4, 64, 28), [x])
+        assert max_err_rel_linf(got, want) <= TOL
+    else:
+        # the oracle has no fused node: rebuild conv -> affine -> relu from the decoded constants
+        from oracle import ops
+        dec = {k: v.numpy() for k, v in tensor_loader.TensorLoader(info["weights"]).load_all().items()}
+        node = onnx_io.load_model(info["model"]).graph.node[0]
+        w, scale, shift = (dec[n] for n in node.input[1:4])
+        conv = ops.conv2d(x, w, None, (1, 1), (1, 1, 1, 1)).astype(np.float64)
+        want = np.maximum(conv * scale[None, :, None, None] + shift[None, :, None, None], 0).astype(np.float32)
+        assert max_err_rel_linf(got, want) <= TOL

@@ -38,9 +38,11 @@ def test_relu_js_edge_semantics(cuda_context):
 @pytest.mark.parametrize("name", sorted(torch_cases()))
 def test_case_matches_oracle_and_golden(cuda_context, name):
     case = torch_cases()[name]
-    model = single_op_model(case["op"], case["attrs"], case["inputs"], n_out=len(case["outputs"]))
-    want = ref_runner.run_model(model, case["inputs"])
-    got, r = run_cuda(model, case["inputs"], cuda_context, return_runner=True)
+    # from the first int64 operand (pads, repeats) on, operands are constants of the graph, like an exporter writes them
+    n_run = next((i for i, a in enumerate(case["inputs"]) if a.dtype == np.int64), len(case["inputs"]))
+    model = single_op_model(case["op"], case["attrs"], case["inputs"], n_out=len(case["outputs"]), n_graph_inputs=n_run)
+    want = ref_runner.run_model(model, case["inputs"][:n_run])
+    got, r = run_cuda(model, case["inputs"][:n_run], cuda_context, return_runner=True)
     _check_all_on_cuda(r)
     r.dispose()
     for g, w, gold in zip(got, want, case["outputs"]):
@@ -48,7 +50,7 @@ def test_case_matches_oracle_and_golden(cuda_context, name):
         if w.dtype == np.int32:
             assert np.array_equal(g, w)
             continue
-        if case["op"] in EXACT_UNARY or case["op"] in ("MaxPool", "ReduceMax", "ReduceMin"):
+        if case["op"] in EXACT_UNARY or case["op"] in ("MaxPool", "ReduceMax", "ReduceMin", "Pad", "Tile"):
             assert np.array_equal(g.view(np.uint32), w.view(np.uint32)), name
         assert max_err_rel_linf(g, w) <= TOL, name
         assert max_err_rel_linf(g, gold) <= TOL, name
@@ -203,3 +205,22 @@ def test_eightbit_decode_on_device_is_bit_exact(cuda_context):
         got = t.get_data()
         t.dispose()
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_pad_examples_written_in_the_reference_source(cuda_context):
+    ka = known_answers()["pad_examples"]
+    x = np.asarray(ka["input"], np.float32)
+    for c in ka["cases"]:
+        pads = np.asarray(c["pads"], np.int64)
+        model = single_op_model("Pad", {"mode": c["mode"], "_opset": 11}, [x, pads], n_graph_inputs=1)
+        (y,) = run_cuda(model, [x], cuda_context)
+        assert y.tolist() == c["expected"], c
+
+
+def test_pad_negative_pads_crop_and_int32(cuda_context):
+    x = np.arange(2 * 3 * 4, dtype=np.int32).reshape(2, 3, 4)
+    pads = np.asarray([0, -1, 2, 1, 0, -1], np.int64)
+    model = single_op_model("Pad", {"_opset": 11}, [x, pads, np.asarray(-7, np.int32)], n_graph_inputs=1)
+    model.graph.input[0].elem_type = 6
+    (y,) = run_cuda(model, [x], cuda_context)
+    assert np.array_equal(y, ops.pad(x, pads.tolist(), "constant", -7))

@@ -59,8 +59,8 @@ def test_int32_typed_array_semantics():
 @pytest.mark.parametrize("name", sorted(torch_cases()))
 def test_oracle_matches_float64_pytorch(name):
     case = torch_cases()[name]
-    n_in = len(case["inputs"])
-    model = single_op_model(case["op"], case["attrs"], case["inputs"], n_out=len(case["outputs"]))
+    n_in = next((i for i, a in enumerate(case["inputs"]) if a.dtype == np.int64), len(case["inputs"]))   # from the first int64 operand on: graph constants
+    model = single_op_model(case["op"], case["attrs"], case["inputs"], n_out=len(case["outputs"]), n_graph_inputs=n_in)
     outs = ref_runner.run_model(model, case["inputs"][:n_in])
     for got, want in zip(outs, case["outputs"]):
         assert list(got.shape) == list(want.shape)
@@ -85,3 +85,22 @@ def test_softmax_rounding_points():
     e = np.exp(x.astype(np.float64) - 7.25)
     want = (e.astype(np.float32).astype(np.float64) / e.sum()).astype(np.float32)
     assert np.array_equal(ops.softmax(x), want)
+
+
+def test_pad_examples_written_in_the_reference_source():
+    """The edge / reflect examples in the comment block of the reference's Pad implementation."""
+    ka = known_answers()["pad_examples"]
+    x = np.asarray(ka["input"], np.float32)
+    for c in ka["cases"]:
+        assert ops.pad(x, c["pads"], c["mode"]).tolist() == c["expected"], c
+
+
+def test_instance_norm_epsilon_is_read_like_the_reference():
+    """instancenormalization.ts:18 reads epsilon with getAttrInt: absent -> 1e-5; given as a float
+    attribute -> its integer field, 0.  The oracle keeps that."""
+    rng = np.random.default_rng(0)
+    x, s, b = rng.random((2, 3, 4, 5)).astype(np.float32), rng.random(3).astype(np.float32), rng.random(3).astype(np.float32)
+    (default,) = ref_runner.run_model(single_op_model("InstanceNormalization", {}, [x, s, b]), [x, s, b])
+    (given,) = ref_runner.run_model(single_op_model("InstanceNormalization", {"epsilon": 0.5}, [x, s, b]), [x, s, b])
+    assert np.array_equal(default, ops.instance_norm(x, s, b, 1e-5))
+    assert np.array_equal(given, ops.instance_norm(x, s, b, 0.0))

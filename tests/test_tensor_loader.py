@@ -119,3 +119,31 @@ def test_runner_reads_external_weights(tmp_path, compression):
                 assert np.array_equal(got, want)
             else:
                 assert np.max(np.abs(got - want)) <= 0.04 * np.max(np.abs(want)) + 1e-12
+
+
+def test_offline_optimizer_bundle(tmp_path):
+    """optimize_model writes the rewritten graph without constants, the weight files and the
+    reference's metadata keys; loading the bundle gives back exactly the constants of a load-time
+    rewrite of the original model, and rewrites nothing a second time."""
+    from webdnn_b200 import optimize_model
+    from webdnn_b200.backend import WebDNNCPUContext
+    from webdnn_b200.runner import Runner
+    src = tmp_path / "src.onnx"
+    onnx_io.save_model(zoo.conv_bn_relu(2, 8, 6), str(src))
+    optimize_model.main([str(src), str(tmp_path / "out")])
+    bundle = onnx_io.load_model(str(tmp_path / "out" / "model-cuda.onnx"))
+    assert [n.op_type for n in bundle.graph.node] == ["CudaConvFused"]
+    assert not bundle.graph.initializer
+    paths = bundle.metadata_props["WebDNN2.WeightPaths"].split(":")
+    sizes = [int(v) for v in bundle.metadata_props["WebDNN2.WeightSizes"].split(":")]
+    assert sizes == [os.path.getsize(tmp_path / "out" / p) for p in paths]
+    assert json.loads(bundle.metadata_props["WebDNN2.TensorMoveOptions"]) == {}
+    direct = Runner(["cuda", "cpu"], {"cpu": WebDNNCPUContext()})
+    direct.load_model(zoo.conv_bn_relu(2, 8, 6))
+    loaded = Runner(["cuda", "cpu"], {"cpu": WebDNNCPUContext()})
+    loaded.load_model(str(tmp_path / "out"), "model-cuda.onnx")
+    assert [n.op_type for n in loaded.model.graph.node] == ["CudaConvFused"]
+    assert [vi.name for vi in loaded.inputs_without_initializer] == ["input"]
+    assert set(loaded.initializer_tensors) == set(direct.initializer_tensors)
+    for name, t in direct.initializer_tensors.items():
+        assert np.array_equal(loaded.initializer_tensors[name].numpy(), t.numpy())

@@ -51,6 +51,11 @@ class ConvDesc(Structure):
         "stride_h", "stride_w", "pad_t", "pad_l", "dil_h", "dil_w", "group")] + [("relu", c_int)]
 
 
+class ConvTransposeDesc(Structure):
+    _fields_ = [(n, c_int64) for n in ("batch", "ch_in", "in_h", "in_w", "ch_out_per_group", "group", "k_h", "k_w",
+                                       "out_h", "out_w", "stride_h", "stride_w", "pad_t", "pad_l", "dil_h", "dil_w")]
+
+
 class PoolDesc(Structure):
     _fields_ = [(n, c_int64) for n in (
         "batch", "ch", "in_h", "in_w", "out_h", "out_w", "k_h", "k_w", "stride_h", "stride_w",
@@ -71,6 +76,9 @@ SIGNATURES = {
     "wdc_host_alloc": (c_int, [c_void_p, c_int64, POINTER(c_void_p)]),
     "wdc_host_free": (c_int, [c_void_p, c_void_p]),
     "wdc_upload": (c_int, [c_void_p, c_void_p, c_void_p, c_int64]),
+    "wdc_conv_transpose2d": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "wdc_instance_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                  ctypes.c_double]),
     "wdc_decode_eightbit": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_float]),
     "wdc_upload_async": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, POINTER(c_int64)]),
     "wdc_wait_upload": (c_int, [c_void_p, c_int64]),

@@ -13,17 +13,18 @@ the fused types the load-time graph rewrite emits) follow the ONNX operator spec
 """
 from __future__ import annotations
 
-from ctypes import c_void_p
+import ctypes
+from ctypes import byref, c_void_p
 from typing import List
 
 import numpy as np
 
-from ..backend import CudaTensor, WebDNNCudaContext
-from ..lib import BINARY_OPS, REDUCE_KINDS, UNARY_OPS, ConvDesc, GemmDesc, PoolDesc
+from ..backend import NP_DTYPE, CPUTensor, CudaTensor, WebDNNCudaContext
+from ..lib import BINARY_OPS, REDUCE_KINDS, UNARY_OPS, ConvDesc, ConvTransposeDesc, GemmDesc, PoolDesc
 from ..operator_table import OperatorEntry
 from . import base
 from .base import (OperatorImpl, array_prod, broadcast_multi, broadcast_uni, get_attr_float, get_attr_int,
-                   get_attr_ints, squeeze_shape, unsqueeze_shape)
+                   get_attr_ints, get_attr_string, squeeze_shape, unsqueeze_shape)
 
 
 def _p(t):
@@ -699,6 +700,190 @@ class CudaGather(OperatorImpl):
         return [y]
 
 
+class CudaConvTranspose(OperatorImpl):
+    """convtranspose.ts:30-263 with the shape rule of base/convtranspose.ts:34-104 (2-D only,
+    auto_pad NOTSET, no explicit output_shape, like the reference)."""
+
+    def __init__(self):
+        super().__init__("cuda")
+
+    def initialize(self, attribute):
+        self.auto_pad = get_attr_string(attribute, "auto_pad", "NOTSET")
+        self.dilations = get_attr_ints(attribute, "dilations", [])
+        self.group = get_attr_int(attribute, "group", 1)
+        self.kernel_shape = get_attr_ints(attribute, "kernel_shape", [])
+        self.output_padding = get_attr_ints(attribute, "output_padding", [])
+        self.output_shape = get_attr_ints(attribute, "output_shape", [])
+        self.pads = get_attr_ints(attribute, "pads", [])
+        self.strides = get_attr_ints(attribute, "strides", [])
+
+    def run(self, context, inputs, n_outputs):
+        context.asserts_cuda_tensor_array(inputs)
+        if inputs[0].ndim != 4:
+            raise ValueError("ConvTranspose other than 2D is not yet supported")
+        if self.auto_pad != "NOTSET":
+            raise ValueError("ConvTranspose: auto_pad !== NOTSET is not yet supported.")
+        if self.output_shape:
+            raise ValueError("ConvTranspose: explicit output_shape is not yet supported.")
+        x = context.canonical(inputs[0])
+        w = context.canonical(inputs[1])
+        bias = inputs[2] if len(inputs) > 2 else None
+        dil = self.dilations or [1, 1]
+        ks = self.kernel_shape or [w.dims[2], w.dims[3]]
+        pads = self.pads or [0, 0, 0, 0]
+        st = self.strides or [1, 1]
+        op = self.output_padding or [0, 0]
+        batch, ch_in, in_h, in_w = x.dims
+        out_h = st[0] * (in_h - 1) + op[0] + (ks[0] - 1) * dil[0] + 1 - pads[0] - pads[2]
+        out_w = st[1] * (in_w - 1) + op[1] + (ks[1] - 1) * dil[1] + 1 - pads[1] - pads[3]
+        cog = w.dims[1]
+        d = ConvTransposeDesc(batch=batch, ch_in=ch_in, in_h=in_h, in_w=in_w, ch_out_per_group=cog, group=self.group,
+                              k_h=ks[0], k_w=ks[1], out_h=out_h, out_w=out_w, stride_h=st[0], stride_w=st[1],
+                              pad_t=pads[0], pad_l=pads[1], dil_h=dil[0], dil_w=dil[1])
+        y = context.empty_tensor([batch, cog * self.group, out_h, out_w], "float32")
+        context._call("wdc_conv_transpose2d", byref(d), _p(x), _p(w), _p(bias) if bias is not None else None, _p(y))
+        for t, o in ((x, inputs[0]), (w, inputs[1])):
+            if t is not o:
+                t.dispose()
+        return [y]
+
+
+class CudaInstanceNormalization(OperatorImpl):
+    """instancenormalization.ts:9-53.  The reference reads ``epsilon`` with getAttrInt (:18): absent it
+    is 1e-5, but an attribute stored as a float (the ONNX way) has an integer field of 0, so a given
+    epsilon acts as 0.  That is kept: the same graph gives the reference's numbers."""
+
+    def __init__(self):
+        super().__init__("cuda")
+
+    def initialize(self, attribute):
+        self.epsilon = float(get_attr_int(attribute, "epsilon", 1e-5))
+
+    def run(self, context, inputs, n_outputs):
+        context.asserts_cuda_tensor_array(inputs)
+        x = context.canonical(inputs[0])
+        scale, bias = inputs[1], inputs[2]
+        y = context.empty_tensor(x.dims, "float32")
+        area = array_prod(x.dims[2:])
+        if x.length:
+            context._call("wdc_instance_norm", _p(x), _p(scale), _p(bias), _p(y), x.dims[0], x.dims[1], area,
+                          ctypes.c_double(self.epsilon))
+        if x is not inputs[0]:
+            x.dispose()
+        return [y]
+
+
+def _gather_axis(context, t, axis: int, index: np.ndarray):
+    """t with axis `axis` re-indexed by `index` (int32 positions along that axis)."""
+    idx = context.move_tensor(CPUTensor.from_array(np.ascontiguousarray(index, dtype=np.int32)))
+    out_dims = list(t.dims)
+    out_dims[axis] = int(index.size)
+    y = context.empty_tensor(out_dims, t.data_type)
+    context._call("wdc_gather", _p(t), _p(idx), _p(y), array_prod(t.dims[:axis]), t.dims[axis],
+                  array_prod(t.dims[axis + 1:]), int(index.size))
+    idx.dispose()
+    return y
+
+
+class CudaPad11(OperatorImpl):
+    """pad11.ts (cpu) / base/pad11.ts:14-50: constant, reflect and edge padding of up to 6-D tensors;
+    pads (and the optional constant) are cpu tensors.  Every mode maps an output index to an input
+    index axis by axis, so reflect/edge are one gather per padded axis and constant is a fill plus
+    one strided copy of the part of the input that stays visible (negative pads crop)."""
+
+    def __init__(self):
+        super().__init__("cuda")
+
+    def initialize(self, attribute):
+        self.mode = get_attr_string(attribute, "mode", "constant")
+
+    def get_tensor_backend_requirement(self, n_inputs, n_outputs):
+        return [self.backend, "cpu"] if n_inputs == 2 else [self.backend, "cpu", "cpu"]
+
+    def run(self, context, inputs, n_outputs):
+        x = context.canonical(inputs[0])
+        if x.ndim > 6:
+            raise ValueError(f"Pad: input.ndim = {x.ndim} > 6 is not yet supported")
+        pads = [int(v) for v in inputs[1].get_data()]
+        nd = x.ndim
+        out_dims = [x.dims[i] + pads[i] + pads[i + nd] for i in range(nd)]
+        if self.mode == "constant":
+            value = inputs[2].get_data()[0] if len(inputs) > 2 else 0
+            y = context.empty_tensor(out_dims, x.data_type)
+            bits = int(np.asarray(value, dtype=NP_DTYPE[x.data_type]).view(np.uint32))
+            if y.length:
+                context._call("wdc_fill_u32", _p(y), bits, y.length)
+            lo = [max(0, -pads[i]) for i in range(nd)]                           # first visible input index
+            hi = [min(x.dims[i], out_dims[i] - pads[i]) for i in range(nd)]     # one past the last
+            region = [h - l for l, h in zip(lo, hi)]
+            if nd == 0:
+                context.unary(UNARY_OPS["Identity"], x, y)
+            elif all(r > 0 for r in region):
+                soff = sum(l * s for l, s in zip(lo, x.strides))
+                doff = sum((l + pads[i]) * s for i, (l, s) in enumerate(zip(lo, y.strides)))
+                context.strided_copy(x, y, region, list(x.strides), soff, list(y.strides), doff)
+        elif self.mode in ("reflect", "edge"):
+            cur = x
+            for i in range(nd):
+                if pads[i] == 0 and pads[i + nd] == 0:
+                    continue
+                n = cur.dims[i]
+                src = np.arange(out_dims[i], dtype=np.int64) - pads[i]
+                if self.mode == "edge":
+                    src = np.clip(src, 0, n - 1)
+                else:
+                    period = n * 2 - 2
+                    neg = src < 0
+                    m = np.where(neg, (-src) % period if period else 0, src % period if period else 0)
+                    m = np.where((neg | (src >= n)), m, src)
+                    src = np.where(m >= n, n * 2 - m - 2, m)
+                nxt = _gather_axis(context, cur, i, src)
+                if cur is not x:
+                    cur.dispose()
+                cur = nxt
+            y = cur if cur is not x else context.empty_tensor(out_dims, x.data_type)
+            if cur is x:
+                context.unary(UNARY_OPS["Identity"], x, y)
+        else:
+            raise ValueError(f"Pad: unknown mode {self.mode}")
+        if x is not inputs[0]:
+            x.dispose()
+        return [y]
+
+
+class CudaTile6(OperatorImpl):
+    """tile.ts:11-70: out[d] = in[d mod dims], up to 4-D like the reference; repeats is a cpu tensor.
+    One gather per repeated axis."""
+
+    def __init__(self):
+        super().__init__("cuda")
+
+    def get_tensor_backend_requirement(self, n_inputs, n_outputs):
+        return [self.backend, "cpu"]
+
+    def run(self, context, inputs, n_outputs):
+        x = context.canonical(inputs[0])
+        if x.ndim > 4:
+            raise ValueError(f"Tile: input.ndim = {x.ndim} > 4 is not yet supported")
+        repeats = [int(v) for v in inputs[1].get_data()]
+        cur = x
+        for i in range(x.ndim):
+            if repeats[i] == 1:
+                continue
+            n = x.dims[i]
+            nxt = _gather_axis(context, cur, i, np.arange(n * repeats[i], dtype=np.int64) % max(n, 1))
+            if cur is not x:
+                cur.dispose()
+            cur = nxt
+        if cur is x:
+            y = context.empty_tensor(x.dims, x.data_type)
+            context.unary(UNARY_OPS["Identity"], x, y)
+            cur = y
+        if x is not inputs[0]:
+            x.dispose()
+        return [cur]
+
+
 class CudaLSTM(OperatorImpl):
     """ONNX LSTM, forward direction, inputs [X, W, R, (B), (sequence_lens), (initial_h),
     (initial_c)] given without empty-name placeholders: the runner cannot bind ""
@@ -778,6 +963,10 @@ def get_op_entries() -> List[OperatorEntry]:
         E("Split", 13, None, "cuda", lambda: CudaSplit(True)),
         E("Slice", 10, None, "cuda", CudaSlice),
         E("Gather", 1, None, "cuda", CudaGather),
+        E("ConvTranspose", 1, None, "cuda", CudaConvTranspose),
+        E("InstanceNormalization", 1, None, "cuda", CudaInstanceNormalization),
+        E("Pad", 11, None, "cuda", CudaPad11),
+        E("Tile", 6, None, "cuda", CudaTile6),
         E("LSTM", 7, None, "cuda", CudaLSTM),
     ]
     for name in REDUCE_KINDS:

@@ -363,6 +363,19 @@ class WebDNNCudaContext:
         dst._prefetch_source = arr  # keeps the host memory alive until the tensor goes away
         return dst
 
+    def peer_copy_from(self, dst: CudaTensor, dst_offset: int, src_context: "WebDNNCudaContext", src: CudaTensor,
+                       n_elements: int) -> None:
+        """dst[dst_offset : dst_offset + n] <- src[0 : n] across devices (NVLink peer copy, ordered after
+        the work queued on the source's stream and before later work on this context's stream)."""
+        if dst.data_type != src.data_type:
+            raise TypeError("peer_copy_from: dtype mismatch")
+        if dst_offset < 0 or n_elements < 0 or dst_offset + n_elements > dst.length or n_elements > src.length:
+            raise ValueError("peer_copy_from: range out of bounds")
+        st = self._L.lib.wdc_peer_copy(self.handle, c_void_p(dst.ptr + 4 * dst_offset), src_context.handle,
+                                       c_void_p(src.ptr), 4 * n_elements)
+        if st != 0:
+            self._L.check(self.handle, st)
+
     def wait_upload(self, t: CudaTensor) -> None:
         """Compute stream waits (on the device, not the host) for the tensor's pending transfer."""
         if t.upload_ticket is not None:

@@ -82,8 +82,13 @@ class ReplicaGroup:
             self.contexts.append(ctx)
             self.runners.append(load(source, backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": ctx}}))
 
-    def run(self, inputs: Sequence[np.ndarray]) -> List[np.ndarray]:
+    def run(self, inputs: Sequence[np.ndarray], gather: str = "host") -> List[np.ndarray]:
+        """``gather="host"``: every replica copies its output slice to the host.  ``gather="peer"``: the
+        slices are first collected on the first device by peer copies over NVLink (batch axis 0 only:
+        a replica's slice is then one contiguous range) and leave in one device-to-host transfer."""
         from .backend import CPUTensor
+        if gather not in ("host", "peer"):
+            raise ValueError("gather must be 'host' or 'peer'")
         n = len(self.runners)
         pending = []
         for i, runner in enumerate(self.runners):  # enqueue everything first: nothing here waits for a GPU
@@ -91,6 +96,29 @@ class ReplicaGroup:
             dev_in = [runner.backend_contexts["cuda"].move_tensor(CPUTensor.from_array(a)) for a in shard]
             outs = runner.run(dev_in, outputs_on_device=True)
             pending.append((dev_in, outs))
+        axes = self.output_axes or [self.batch_axis] * len(pending[0][1])
+        if gather == "peer":
+            if any(a != 0 for a in axes):
+                raise ValueError("gather='peer' needs outputs sharded along axis 0")
+            ctx0 = self.contexts[0]
+            results = []
+            for j in range(len(pending[0][1])):
+                parts = [ctx.canonical(outs[j]) for ctx, (_, outs) in zip(self.contexts, pending)]
+                dims = [sum(p.dims[0] for p in parts)] + list(parts[0].dims[1:])
+                whole = ctx0.empty_tensor(dims, parts[0].data_type)
+                off = 0
+                for ctx, p in zip(self.contexts, parts):
+                    ctx0.peer_copy_from(whole, off, ctx, p, p.length)
+                    off += p.length
+                results.append(whole.get_data().reshape(dims))
+                whole.dispose()
+                for p, (_, outs) in zip(parts, pending):
+                    if p is not outs[j]:
+                        p.dispose()
+            for dev_in, outs in pending:
+                for t in list(outs) + list(dev_in):
+                    t.dispose()
+            return results
         per_output: List[List[np.ndarray]] = []
         for dev_in, outs in pending:               # now drain, replica by replica
             arrays = []
@@ -100,7 +128,6 @@ class ReplicaGroup:
             for t in dev_in:
                 t.dispose()
             per_output.append(arrays)
-        axes = self.output_axes or [self.batch_axis] * len(per_output[0])
         return [np.concatenate([rep[j] for rep in per_output], axis=axes[j]) for j in range(len(per_output[0]))]
 
     def close(self) -> None:

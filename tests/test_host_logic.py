@@ -167,3 +167,39 @@ def test_load_without_gpu_reports_no_backend():
         pytest.skip("a GPU is present")
     with pytest.raises(RuntimeError, match="No backend available"):
         load(zoo.mlp(2), backend_order=["cuda"])
+
+
+def test_transformer_fusions_layernorm_chain_and_matmul_bias():
+    m = zoo.detr(batch=1, size=64, d=32, heads=4, enc_layers=1, dec_layers=1, ffn=64, queries=5, classes=7, width=8,
+                 blocks=(1, 1, 1, 1))
+    before = [n.op_type for n in m.graph.node]
+    n_ln = before.count("Sqrt")                      # one Sqrt per decomposed LayerNormalization
+    model_transform(m, ["cuda", "cpu"])
+    types = [n.op_type for n in m.graph.node]
+    assert types.count("CudaLayerNorm") == n_ln == 5
+    assert not {"ReduceMean", "Sub", "Sqrt", "Div"} & set(types)
+    # every linear layer (MatMul by a constant + bias) is one node; the FFN's first one carries its Relu
+    assert types.count("CudaMatMulBias") == 4 * 3 + 2 * 2 + 1 + 3
+    relus = [n for n in m.graph.node if n.op_type == "CudaMatMulBias" and {a.name: a.i for a in n.attribute}["relu"]]
+    assert len(relus) == 2 + 2                        # two feed-forward blocks, two hidden layers of the box head
+    assert types.count("MatMul") == 3 * 2            # scores and context of the three attention blocks stay
+    ln = next(n for n in m.graph.node if n.op_type == "CudaLayerNorm")
+    attrs = {a.name: a for a in ln.attribute}
+    assert attrs["axis"].i == -1 and abs(attrs["epsilon"].f - 1e-5) < 1e-12 and len(ln.input) == 3
+    known = {vi.name for vi in m.graph.input} | {t.name for t in m.graph.initializer}
+    for n in m.graph.node:
+        assert all(i in known for i in n.input), (n.op_type, n.name)
+        known.update(n.output)
+
+
+def test_layernorm_chain_with_an_outside_consumer_is_left_alone():
+    from webdnn_b200.zoo import _Builder, _Transformer
+    b = _Builder(0)
+    t = _Transformer(b, 1, 8, 2, 16)
+    y = t.layer_norm("x")
+    # the centred value (output of Sub) is also a graph output: the chain must stay
+    sub_out = next(n.output[0] for n in b.nodes if n.op_type == "Sub")
+    m = b.model([("x", [1, 3, 8])], [(y, [1, 3, 8]), (sub_out, [1, 3, 8])])
+    model_transform(m, ["cuda", "cpu"])
+    types = [n.op_type for n in m.graph.node]
+    assert "CudaLayerNorm" not in types and types.count("ReduceMean") == 2

@@ -9,6 +9,10 @@ unchanged:
   Bias and the BatchNormalization parameters are folded (in float64, once) into a per-channel
   scale/shift pair stored as new initializers; weights are left untouched.
 * ``Gemm`` + ``Relu`` -> ``CudaGemmRelu``.
+* ``MatMul`` by a constant 2-D matrix + ``Add`` of a constant vector [+ ``Relu``] -> ``CudaMatMulBias``
+  (the bias and the Relu move into the contraction's epilogue).
+* the decomposed LayerNormalization chain over the last axis (``ReduceMean``, ``Sub``, ``Mul``/``Pow``,
+  ``ReduceMean``, ``Add`` epsilon, ``Sqrt``, ``Div``, ``Mul`` gamma, ``Add`` beta) -> ``CudaLayerNorm``.
 
 The private op types are registered like a custom operator (``example/custom_operator/twice.ts``),
 the same way the offline WebGL passes rename ``op_type`` to ``ConvReshapeWebGL`` / ``MatMulNT141``.
@@ -62,6 +66,84 @@ def find_tensor_release_timing(model: Model, initializer_names) -> Dict[str, Lis
     for name, node_name in last.items():
         timing.setdefault(node_name, []).append(name)
     return timing
+
+
+def _last_axis_mean(n: Node) -> bool:
+    axes = [a for a in n.attribute if a.name == "axes"]
+    keep = [a for a in n.attribute if a.name == "keepdims"]
+    return (n.op_type == "ReduceMean" and len(n.input) == 1 and len(axes) == 1 and list(axes[0].ints) == [-1]
+            and (not keep or keep[0].i == 1))
+
+
+def _match_layernorm(mean_node: Node, inits, consumers, graph_outputs, removed):
+    """Matches the opset-13 export of LayerNormalization over the last axis that starts at
+    ``mean_node`` and ends with the affine part; returns (chain in graph order, fused node) or None.
+    Every intermediate value must have no consumer outside the chain and must not be a graph output."""
+    if not _last_axis_mean(mean_node):
+        return None
+
+    def users(t):
+        seen, out = set(), []
+        for c in consumers.get(t, []):   # a node that takes t twice is listed twice
+            if id(c) not in removed and id(c) not in seen:
+                seen.add(id(c))
+                out.append(c)
+        return out
+
+    def internal(t, allowed):
+        return t not in graph_outputs and all(any(c is a for a in allowed) for c in users(t))
+
+    x = mean_node.input[0]
+    mean = mean_node.output[0]
+    sub = users(mean)
+    if len(sub) != 1 or sub[0].op_type != "Sub" or list(sub[0].input) != [x, mean] or not internal(mean, sub):
+        return None
+    sub = sub[0]
+    xc = sub.output[0]
+    xc_users = users(xc)
+    sq = [c for c in xc_users if (c.op_type == "Mul" and list(c.input) == [xc, xc]) or
+          (c.op_type == "Pow" and c.input[0] == xc and c.input[1] in inits and inits[c.input[1]].array.size == 1
+           and float(inits[c.input[1]].array.reshape(-1)[0]) == 2.0)]
+    div = [c for c in xc_users if c.op_type == "Div" and c.input[0] == xc]
+    if len(sq) != 1 or len(div) != 1 or not internal(xc, [sq[0], div[0]]):
+        return None
+    sq, div = sq[0], div[0]
+    var = users(sq.output[0])
+    if len(var) != 1 or not _last_axis_mean(var[0]) or not internal(sq.output[0], var):
+        return None
+    var = var[0]
+    add = users(var.output[0])
+    if len(add) != 1 or add[0].op_type != "Add" or not internal(var.output[0], add):
+        return None
+    add = add[0]
+    eps_name = add.input[1] if add.input[0] == var.output[0] else add.input[0]
+    if eps_name not in inits or inits[eps_name].array.size != 1:
+        return None
+    sqrt = users(add.output[0])
+    if len(sqrt) != 1 or sqrt[0].op_type != "Sqrt" or not internal(add.output[0], sqrt):
+        return None
+    sqrt = sqrt[0]
+    if list(div.input) != [xc, sqrt.output[0]] or not internal(sqrt.output[0], [div]):
+        return None
+    mul = users(div.output[0])
+    if len(mul) != 1 or mul[0].op_type != "Mul" or not internal(div.output[0], mul):
+        return None
+    mul = mul[0]
+    gamma = mul.input[1] if mul.input[0] == div.output[0] else mul.input[0]
+    addb = users(mul.output[0])
+    if gamma not in inits or len(addb) != 1 or addb[0].op_type != "Add" or not internal(mul.output[0], addb):
+        return None
+    addb = addb[0]
+    beta = addb.input[1] if addb.input[0] == mul.output[0] else addb.input[0]
+    if beta not in inits:
+        return None
+    gd, bd = list(inits[gamma].dims), list(inits[beta].dims)
+    if len(gd) != 1 or gd != bd:
+        return None
+    eps = float(np.float32(inits[eps_name].array.reshape(-1)[0]))
+    fused = Node("CudaLayerNorm", [x, gamma, beta], [addb.output[0]], mean_node.name or mean,
+                 [make_attr("axis", -1), make_attr("epsilon", eps)])
+    return [mean_node, sub, sq, var, add, sqrt, div, mul, addb], fused
 
 
 def _fuse_cuda(model: Model) -> None:
@@ -140,6 +222,37 @@ def _fuse_cuda(model: Model) -> None:
             for c in chain:
                 removed.add(id(c))
             replace_at[id(chain[-1])] = fused
+        elif n.op_type == "MatMul" and len(n.input) == 2 and n.input[1] in inits and len(inits[n.input[1]].dims) == 2:
+            nxt = sole_consumer(n.output[0])
+            if nxt is None or nxt.op_type != "Add" or len(nxt.input) != 2:
+                continue
+            other = nxt.input[0] if nxt.input[1] == n.output[0] else nxt.input[1]
+            n_out = inits[n.input[1]].dims[1]
+            if other not in inits or other == n.output[0]:
+                continue
+            bdims = [d for d in inits[other].dims if d != 1]
+            if bdims != [n_out] or inits[other].dims[-1] != n_out:
+                continue
+            chain = [n, nxt]
+            out = nxt.output[0]
+            relu = False
+            nx2 = sole_consumer(out)
+            if nx2 is not None and nx2.op_type == "Relu":
+                relu = True
+                chain.append(nx2)
+                out = nx2.output[0]
+            fused = Node("CudaMatMulBias", [n.input[0], n.input[1], other], [out], n.name or n.output[0],
+                         [make_attr("relu", int(relu))])
+            for c in chain:
+                removed.add(id(c))
+            replace_at[id(chain[-1])] = fused
+        elif n.op_type == "ReduceMean":
+            fused_ln = _match_layernorm(n, inits, consumers, graph_outputs, removed)
+            if fused_ln is not None:
+                chain, fused = fused_ln
+                for c in chain:
+                    removed.add(id(c))
+                replace_at[id(chain[-1])] = fused
         elif n.op_type == "Gemm":
             nxt = sole_consumer(n.output[0])
             if nxt is not None and nxt.op_type == "Relu":

@@ -220,6 +220,36 @@ class CudaMatMul(base.MatMul):
         return [y]
 
 
+class CudaMatMulBias(OperatorImpl):
+    """``MatMul(A, W) + b`` [+ Relu] in one launch: A [..., k] (leading dims stacked into rows), W a
+    constant [k, n], b a constant vector of n (load-time rewrite of MatMul + Add, matmul.ts:11-111 and
+    binary7.ts broadcasting for the reference semantics)."""
+
+    def __init__(self):
+        super().__init__("cuda")
+        self.relu = False
+
+    def initialize(self, attribute):
+        self.relu = get_attr_int(attribute, "relu", 0) != 0
+
+    def run(self, context, inputs, n_outputs):
+        context.asserts_cuda_tensor_array(inputs)
+        a = context.canonical(inputs[0])
+        w, b = inputs[1], inputs[2]
+        k, n = w.dims
+        if a.ndim < 1 or a.dims[-1] != k:
+            raise ValueError("CudaMatMulBias: inner dimensions do not match")
+        m = a.length // k
+        d = GemmDesc(batch=1, m=m, n=n, k=k, sab=0, sa0=k, sa1=1, sbb=0, sb0=n, sb1=1, sc0=0, sc1=1,
+                     alpha=1.0, beta=1.0, relu=int(self.relu))
+        y = context.empty_tensor(list(a.dims[:-1]) + [n], "float32")
+        if y.length:
+            context.gemm(d, a, w, b, y)
+        if a is not inputs[0]:
+            a.dispose()
+        return [y]
+
+
 def _packed_weight(context: WebDNNCudaContext, w: CudaTensor) -> CudaTensor:
     """[Cout, Cin/g, kh, kw] -> [Cout, kh, kw, Cin/g], cached on the (persistent) weight tensor."""
     pk = w.aux.get("krsc")
@@ -942,6 +972,7 @@ def get_op_entries() -> List[OperatorEntry]:
         E("Cast", 6, None, "cuda", CudaCast),
         E("Gemm", 1, None, "cuda", CudaGemm),
         E("CudaGemmRelu", 1, None, "cuda", lambda: CudaGemm(relu=True)),
+        E("CudaMatMulBias", 1, None, "cuda", CudaMatMulBias),
         E("MatMul", 1, None, "cuda", CudaMatMul),
         E("Conv", 1, None, "cuda", CudaConv),
         E("CudaConvFused", 1, None, "cuda", lambda: CudaConv(fused=True)),

@@ -31,6 +31,9 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 METRIC = "resnet50_fp32_inference_images_per_sec"
+# dram__bytes_read.sum + dram__bytes_write.sum of the 54 tc_igemm launches of one batch-256 step, divided by 54
+# (profiles/resnet50_b256_contraction_dram_traffic.md); the algorithmic bytes of the same launches are 28.06 GB.
+CONTRACTION_DRAM_BYTES_PER_LAUNCH_B256 = 25.180e9 / 54
 
 
 class ClockSampler:
@@ -259,7 +262,10 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             "gpu_launches": int(launches),
             "clocks": clocks,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
-                         "frac": achieved / tf32_peak if tf32_peak else None, "traffic": None,
+                         "frac": achieved / tf32_peak if tf32_peak else None,
+                         "traffic": CONTRACTION_DRAM_BYTES_PER_LAUNCH_B256 if B == 256 else None,
+                         "traffic_unit": "bytes of DRAM read + written per launch, average over the step's 54 "
+                                         "contraction launches (one ncu capture at batch 256, see profiles/)",
                          "kernel": "Conv/Gemm contraction launches (wdc_conv2d, wdc_gemm)",
                          "launches": int(k_launches), "kernel_ms_per_step": k_ms / args.steps,
                          "algorithmic_flops_per_step": flops_per_step,

@@ -56,6 +56,19 @@ int wdc_download(wdc_context* ctx, void* host, const void* src, int64_t bytes); 
  * The transfer starts after the work already queued on the compute stream.  *ticket identifies it;
  * wdc_wait_upload makes the compute stream (not the host) wait for that transfer: call it before
  * the first launch that reads dst. */
+/* Replay of a whole run without per-launch host work (the reference has no counterpart: its runner
+ * re-issues every operator on every run, runnerImpl.ts:315-596).  Between wdc_capture_begin and
+ * wdc_capture_end every launch on the context's stream is recorded instead of executed, and every
+ * wdc_alloc / wdc_free is served by a private arena that the resulting graph keeps, so the recorded
+ * launches find their buffers at the same addresses on every wdc_graph_launch.  Rules for the calls made
+ * while capturing: no host<->device transfer, no wdc_sync, per-launch profiling off; buffers that were
+ * allocated while capturing (the run's outputs) must be freed before wdc_graph_destroy; run the same
+ * sequence once normally first, so that one-time work (weight packing and splitting) is not recorded. */
+typedef struct wdc_graph wdc_graph;
+int wdc_capture_begin(wdc_context* ctx);
+int wdc_capture_end(wdc_context* ctx, wdc_graph** graph);
+int wdc_graph_launch(wdc_context* ctx, wdc_graph* graph);
+int wdc_graph_destroy(wdc_context* ctx, wdc_graph* graph);
 int wdc_upload_async(wdc_context* ctx, void* dst, const void* host, int64_t bytes, int64_t* ticket);
 int wdc_wait_upload(wdc_context* ctx, int64_t ticket);
 int wdc_copy(wdc_context* ctx, void* dst, const void* src, int64_t bytes);

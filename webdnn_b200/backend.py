@@ -363,6 +363,22 @@ class WebDNNCudaContext:
         dst._prefetch_source = arr  # keeps the host memory alive until the tensor goes away
         return dst
 
+    # --- capture of a run into a CUDA graph
+    def capture_begin(self) -> None:
+        self._call("wdc_capture_begin")
+
+    def capture_end(self) -> int:
+        g = c_void_p()
+        self._call("wdc_capture_end", byref(g))
+        return g.value
+
+    def graph_launch(self, graph: int) -> None:
+        self._call("wdc_graph_launch", c_void_p(graph))
+
+    def graph_destroy(self, graph: int) -> None:
+        if self.handle is not None:
+            self._call("wdc_graph_destroy", c_void_p(graph))
+
     def peer_copy_from(self, dst: CudaTensor, dst_offset: int, src_context: "WebDNNCudaContext", src: CudaTensor,
                        n_elements: int) -> None:
         """dst[dst_offset : dst_offset + n] <- src[0 : n] across devices (NVLink peer copy, ordered after

@@ -42,6 +42,10 @@ struct wdc_context {
   int* status_word = nullptr;       // device word set by kernels whose bounded waits expire
   int* status_word_host = nullptr;  // pinned mirror
   void* tc_state = nullptr;         // tensor-map cache of the tcgen05 path
+  // While a run is being captured into a CUDA graph, allocations come from (and return to) a private
+  // arena that the finished graph keeps: replays reuse exactly the addresses the capture saw.
+  wdc_arena* capture_arena = nullptr;
+  std::vector<wdc_arena*> graph_arenas;   // arenas owned by finished graphs (and by failed captures)
   // second stream for host-to-device transfers that overlap the kernels of `stream`
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t copy_fence = nullptr;             // recorded on `stream`, waited by `copy_stream`

@@ -90,6 +90,11 @@ extern "C" int wdc_destroy(wdc_context* ctx) {
   cudaStreamSynchronize(ctx->stream);
   wdc_tc_destroy(ctx);
   for (auto& s : ctx->arena.slabs) cudaFree(s.base);
+  if (ctx->capture_arena) ctx->graph_arenas.push_back(ctx->capture_arena);
+  for (wdc_arena* a : ctx->graph_arenas) {
+    for (auto& s : a->slabs) cudaFree(s.base);
+    delete a;
+  }
   cudaFree(ctx->status_word);
   cudaFreeHost(ctx->status_word_host);
   if (ctx->copy_stream) {
@@ -122,7 +127,7 @@ extern "C" int wdc_alloc(wdc_context* ctx, int64_t bytes, void** dptr) {
   *dptr = nullptr;
   if (bytes < 0) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_alloc: negative size %lld", (long long)bytes);
   std::lock_guard<std::mutex> lk(ctx->mu);
-  wdc_arena& a = ctx->arena;
+  wdc_arena& a = ctx->capture_arena ? *ctx->capture_arena : ctx->arena;
   int64_t need = ((bytes > 0 ? bytes : 1) + kAlign - 1) / kAlign * kAlign;
   if (a.limit > 0 && a.in_use + need > a.limit)
     return wdc_fail(ctx, WDC_ERR_OOM, "wdc_alloc: %lld bytes would exceed the arena budget of %lld (in use %lld)",
@@ -177,10 +182,17 @@ extern "C" int wdc_free(wdc_context* ctx, void* dptr) {
   if (!dptr) return WDC_OK;
   wdc_tc_evict(ctx, dptr);
   std::lock_guard<std::mutex> lk(ctx->mu);
-  wdc_arena& a = ctx->arena;
-  auto lit = a.live.find(dptr);
-  if (lit == a.live.end())
+  wdc_arena* owner = &ctx->arena;
+  if (ctx->arena.live.find(dptr) == ctx->arena.live.end()) {
+    owner = nullptr;
+    if (ctx->capture_arena && ctx->capture_arena->live.count(dptr)) owner = ctx->capture_arena;
+    for (wdc_arena* g : ctx->graph_arenas)
+      if (!owner && g->live.count(dptr)) owner = g;
+  }
+  if (!owner)
     return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_free: %p is not a live allocation of this context", dptr);
+  wdc_arena& a = *owner;
+  auto lit = a.live.find(dptr);
   int slab = lit->second.first;
   int64_t off = lit->second.second;
   a.live.erase(lit);
@@ -271,6 +283,84 @@ extern "C" int wdc_wait_upload(wdc_context* ctx, int64_t ticket) {
   int64_t slot = ticket;
   if (ctx->upload_seq - ticket > wdc_context::kUploadTickets) slot = ctx->upload_seq - 1;
   WDC_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, ctx->upload_done[slot % wdc_context::kUploadTickets], 0));
+  return WDC_OK;
+}
+
+// ---- capture of one run into a CUDA graph ------------------------------------------------------
+struct wdc_graph {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  wdc_arena* arena = nullptr;  // owns every buffer the captured launches touch that was allocated while capturing
+};
+
+extern "C" int wdc_capture_begin(wdc_context* ctx) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_capture_begin: null context");
+  if (ctx->capture_arena) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_capture_begin: a capture is already open");
+  if (ctx->profile) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_capture_begin: switch per-launch profiling off first");
+  DeviceGuard g(ctx->device);
+  // relaxed mode: growing the private arena calls cudaMalloc, which the stricter modes refuse in this thread
+  WDC_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed));
+  ctx->capture_arena = new wdc_arena();
+  return WDC_OK;
+}
+
+static void arena_release(wdc_arena* a) {
+  for (auto& s : a->slabs) cudaFree(s.base);
+  delete a;
+}
+
+extern "C" int wdc_capture_end(wdc_context* ctx, wdc_graph** out) {
+  if (!ctx || !out) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_capture_end: null argument");
+  *out = nullptr;
+  if (!ctx->capture_arena) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_capture_end: no capture is open");
+  DeviceGuard g(ctx->device);
+  wdc_arena* arena = ctx->capture_arena;
+  ctx->capture_arena = nullptr;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+  cudaGraphExec_t exec = nullptr;
+  if (e == cudaSuccess) e = cudaGraphInstantiate(&exec, graph, 0);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    if (graph) cudaGraphDestroy(graph);
+    // buffers handed out during the failed capture stay valid until their owners free them
+    ctx->graph_arenas.push_back(arena);
+    return wdc_fail(ctx, WDC_ERR_CUDA, "wdc_capture_end: %s", cudaGetErrorString(e));
+  }
+  wdc_graph* gr = new wdc_graph();
+  gr->graph = graph;
+  gr->exec = exec;
+  gr->arena = arena;
+  ctx->graph_arenas.push_back(arena);
+  *out = gr;
+  return WDC_OK;
+}
+
+extern "C" int wdc_graph_launch(wdc_context* ctx, wdc_graph* graph) {
+  if (!ctx || !graph || !graph->exec) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_graph_launch: bad argument");
+  if (ctx->capture_arena) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_graph_launch: a capture is open");
+  DeviceGuard g(ctx->device);
+  WDC_CUDA(ctx, cudaGraphLaunch(graph->exec, ctx->stream));
+  ctx->n_launch++;
+  return WDC_OK;
+}
+
+extern "C" int wdc_graph_destroy(wdc_context* ctx, wdc_graph* graph) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_graph_destroy: null context");
+  if (!graph) return WDC_OK;
+  DeviceGuard g(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  if (graph->exec) cudaGraphExecDestroy(graph->exec);
+  if (graph->graph) cudaGraphDestroy(graph->graph);
+  if (graph->arena) {
+    if (!graph->arena->live.empty())
+      wdc_fail(ctx, WDC_ERR_INVALID, "wdc_graph_destroy: %zu buffers of the captured run are still allocated; they are "
+               "released with the graph", graph->arena->live.size());
+    for (size_t i = 0; i < ctx->graph_arenas.size(); i++)
+      if (ctx->graph_arenas[i] == graph->arena) ctx->graph_arenas.erase(ctx->graph_arenas.begin() + i--);
+    arena_release(graph->arena);
+  }
+  delete graph;
   return WDC_OK;
 }
 

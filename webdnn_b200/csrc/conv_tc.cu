@@ -1126,6 +1126,10 @@ int get_weight(wdc_context* ctx, const float* w, const float* scale, float alpha
     *out = &it->second;
     return WDC_OK;
   }
+  if (ctx->capture_arena)
+    return wdc_fail(ctx, WDC_ERR_INVALID,
+                    "a weight operand was seen for the first time while capturing: run the sequence once before "
+                    "wdc_capture_begin, so that the one-time split is not part of the recorded run");
   if (it != st->weights.end()) {
     wdc_free(ctx, it->second.hi);
     wdc_free(ctx, it->second.lo);

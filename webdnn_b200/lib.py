@@ -80,6 +80,10 @@ SIGNATURES = {
     "wdc_instance_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                   ctypes.c_double]),
     "wdc_decode_eightbit": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_float]),
+    "wdc_capture_begin": (c_int, [c_void_p]),
+    "wdc_capture_end": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "wdc_graph_launch": (c_int, [c_void_p, c_void_p]),
+    "wdc_graph_destroy": (c_int, [c_void_p, c_void_p]),
     "wdc_upload_async": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, POINTER(c_int64)]),
     "wdc_wait_upload": (c_int, [c_void_p, c_int64]),
     "wdc_download": (c_int, [c_void_p, c_void_p, c_void_p, c_int64]),

@@ -132,6 +132,36 @@ class Runner:
                 raise ValueError(f"Unsupported initializer dataType {t.data_type}")
         return tensors
 
+    def capture(self, inputs: Sequence[CPUTensor]) -> CapturedRun:
+        """Records ``run(inputs)`` on the cuda backend as a CUDA graph.  The run is executed once
+        normally first (constants are moved, packed and split then), and the recorded run must stay on
+        the device: a node placed on the cpu backend, or an operator that uploads host data while it
+        runs (Pad / Tile index tables), ends the capture with an error."""
+        ctx = self.backend_contexts.get("cuda")
+        if ctx is None:
+            raise RuntimeError("capture needs the cuda backend")
+        dev_in = [ctx.move_tensor(t) for t in inputs]
+        for o in self.run(dev_in, outputs_on_device=True):
+            o.dispose()
+        if self.nodes_on("cpu"):
+            for t in dev_in:
+                t.dispose()
+            raise RuntimeError(f"capture: nodes on the cpu backend: {self.nodes_on('cpu')}")
+        ctx.sync()
+        ctx.capture_begin()
+        try:
+            outs = self.run(dev_in, outputs_on_device=True)
+        except Exception:
+            try:
+                ctx.capture_end()
+            except Exception:
+                pass
+            for t in dev_in:
+                t.dispose()
+            raise
+        graph = ctx.capture_end()
+        return CapturedRun(ctx, graph, dev_in, outs)
+
     def get_input_names(self) -> List[str]:
         return [vi.name for vi in self.inputs_without_initializer]
 
@@ -265,6 +295,41 @@ class Runner:
             for t in kv.values():
                 t.dispose()
             kv.clear()
+
+
+class CapturedRun:
+    """One ``Runner.run`` recorded as a CUDA graph (``Runner.capture``): every later ``run`` copies the
+    inputs into the recorded input buffers, replays all launches with one call and reads the outputs
+    back.  Valid for inputs of the shapes and dtypes given at capture time; the recorded buffers belong
+    to this object until ``dispose``."""
+
+    def __init__(self, context: WebDNNCudaContext, graph: int, inputs: List, outputs: List):
+        self.context, self.graph, self.inputs, self.outputs = context, graph, inputs, outputs
+
+    def launch(self) -> None:
+        """Replay on the inputs currently in the recorded input buffers; results stay on the device."""
+        self.context.graph_launch(self.graph)
+
+    def run(self, inputs: Sequence[CPUTensor]) -> List[CPUTensor]:
+        if len(inputs) != len(self.inputs):
+            raise ValueError("length of inputs mismatch")
+        for dst, src in zip(self.inputs, inputs):
+            if list(src.dims) != list(dst.dims) or src.data_type != dst.data_type:
+                raise ValueError("CapturedRun.run: input shape or dtype differs from the captured one")
+            dst.set_data(src.get_data())
+        self.launch()
+        return [self.context.cpu_context.empty_tensor(o.dims, o.data_type, o.get_data()) for o in self.outputs]
+
+    def dispose(self) -> None:
+        if self.graph is None:
+            return
+        self.context.sync()
+        for t in self.outputs:
+            t.dispose()
+        self.context.graph_destroy(self.graph)
+        self.graph = None
+        for t in self.inputs:
+            t.dispose()
 
 
 def load(source: Union[str, bytes, Model], backend_order: Optional[Sequence[str]] = None,

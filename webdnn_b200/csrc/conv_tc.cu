@@ -3,9 +3,12 @@
 //   Y[m, n] = epilogue( sum_k A[m, k] * W[n, k] )       m = output pixel, n = output channel,
 //                                                       k = (ky, kx, ci) over an NHWC input.
 //
-// fp32-class accuracy comes from the 3xTF32 split: every fp32 operand x is written as hi + lo with
-// hi = tf32(x), lo = tf32(x - hi); the product is accumulated as A_lo*W_hi + A_hi*W_lo + A_hi*W_hi
-// in fp32 TMEM accumulators (the lo*lo term, ~2^-22 relative, is dropped).
+// fp32-class accuracy comes from the 3xTF32 split: every fp32 operand x is written as hi + lo and the
+// product is accumulated as A_lo*W_hi + A_hi*W_lo + A_hi*W_hi in fp32 TMEM accumulators (the lo*lo
+// term, ~2^-22 relative, is dropped).  Weights are split once (hi = tf32(w), lo = tf32(w - hi), after
+// the per-channel scale has been multiplied in) and cached.  For activations the tensor core's own
+// operand truncation is the split: the raw fp32 value is the high operand (the MMA ignores its low
+// 13 mantissa bits) and lo = x - (x & 0xffffe000), exact in fp32.
 //
 // The tensor core's fp32 accumulator truncates when it aligns addends, which biases long sums
 // toward zero (measured ~0.15 ulp of the running sum per MMA).  To keep fp32-class accuracy through
@@ -15,27 +18,31 @@
 //
 // Shared memory bandwidth (128 B/clk) is the scarce resource of a 3xTF32 kernel: with both operands
 // in shared memory a 128x128x8 MMA reads 8 KB per 64 clocks, which alone saturates it.  So the A
-// operand (activations, gathered and split by ordinary threads anyway) lives in TENSOR MEMORY: the
-// producer threads write A_hi / A_lo with tcgen05.st and the MMA takes A from TMEM, W from shared
-// memory.  Shared memory then carries only the weight tiles (TMA in, MMA out).
+// operand lives in TENSOR MEMORY (tcgen05.st by the splitter threads; the MMA takes A from TMEM, W
+// from shared memory) and shared memory carries the weight tiles, the raw A tiles on their way to the
+// splitters, and the epilogue's staging buffers.
 //
 // One persistent CTA per SM, warp specialised, 16 warps (4 per SM sub-partition, so that every
-// thread can have 128 registers):
-//   warps 0-3   A producers: thread (w, l) owns row 32w+l of the 128-row tile (= TMEM lane).  Per K
-//               block it gathers the row's 32 values from global memory (8 x 128-bit loads, zero fill
-//               for padding, loads running 2 K blocks ahead and crossing tile boundaries), splits them
-//               into hi/lo and writes 32+32 TMEM columns of the stage with tcgen05.st.
-//   warp  4     W producer: one lane issues two TMA tile loads per stage (pre-split W_hi, W_lo,
-//               128B-swizzled).
+// thread can have 128 registers).  tc_igemm_kernel<true> (A tiles by TMA):
+//   warp  6     A loader: one im2col-mode TMA load per K block brings the raw 128-pixel x 32-channel
+//               tile of the NHWC input (padding and rows past M arrive as zeros) into a 128B-swizzled
+//               stage; first-layer mode (4 channels per pixel) loads one plane per tap or tap pair.
+//   warps 0-3   A splitters: thread (w, l) owns row 32w+l of the tile (= TMEM lane); per K block it
+//               reads its row from the stage (8 conflict-free 16-byte reads) and writes raw / lo into
+//               32 + 32 TMEM columns with tcgen05.st.
+//   warp  4     W loader: one lane issues two TMA tile loads per stage (pre-split W_hi, W_lo).
 //   warp  5     MMA issuer: one lane issues tcgen05.mma.kind::tf32 (M=128, N=tile, K=8, A from TMEM),
 //               12 per 32-wide K block; tcgen05.commit releases the stage / publishes the segment.
 //   warps 8-15  accumulate + epilogue: each warp owns one TMEM lane quadrant and half of the tile's
-//               columns; per segment tcgen05.ld + add into registers; at the end of a tile the
-//               accumulators are transposed through shared memory so that scale/shift (bias, folded
-//               BatchNormalization), residual add, Relu and the NHWC store touch 8 rows x 64
-//               contiguous bytes per warp instruction.
-// TMEM columns: [0,256) two segment accumulators of up to 128 columns, [256,512) four A stages of
-// 32 (hi) + 32 (lo) columns.
+//               columns; accumulators start at the per-channel shift; per segment tcgen05.ld + add into
+//               registers; at the end of a tile the residual tile (brought by TMA into the warp's
+//               staging buffer) is added, Relu applied, the result written over it and stored by TMA.
+// tc_igemm_kernel<false> keeps the earlier producers for geometries an im2col tensor map cannot
+// express: warps 0-3 gather A from global memory themselves (8 x 128-bit loads per row and K block,
+// running 2 K blocks ahead).  Outputs whose row pitch is not a multiple of 16 bytes use the plain
+// epilogue (transpose through shared memory, per-thread loads and stores).
+// TMEM columns: [0,256) two segment accumulators of up to 128 columns, [256,448) three A stages of
+// 32 (raw) + 32 (lo) columns.
 // Every mbarrier wait is bounded in wall time; on expiry the kernel records an error code in the
 // context's status word, raises a CTA-wide abort flag so the other roles stop too, frees its TMEM
 // and returns.

@@ -176,3 +176,29 @@ def test_gemm_trans_b_0_on_tensor_cores(cuda_context):
     (got,) = run_cuda(model, [a, b, c], cuda_context)
     assert cuda_context.stats()["tensor_core_launches"] > before
     assert max_err_rel_linf(got, want) <= TOL
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_conv_random_geometry(cuda_context, seed):
+    """Random kernel sizes (k_h != k_w), strides, dilations and asymmetric pads: the im2col tensor map's
+    corner offsets, traversal strides and tap offsets against the oracle's direct loops."""
+    rng = np.random.default_rng(100 + seed)
+    cin, cout = int(rng.choice([32, 64, 96])), int(rng.choice([8, 36, 64, 132]))
+    kh, kw = int(rng.integers(1, 6)), int(rng.integers(1, 6))
+    sh, sw = int(rng.integers(1, 4)), int(rng.integers(1, 4))
+    dh, dw = int(rng.integers(1, 3)), int(rng.integers(1, 3))
+    pads = [int(v) for v in rng.integers(0, 4, 4)]                      # [top, left, bottom, right]
+    h = int(rng.integers((kh - 1) * dh + 1, (kh - 1) * dh + 14))
+    w_ = int(rng.integers((kw - 1) * dw + 1, (kw - 1) * dw + 14))
+    n = int(rng.integers(1, 4))
+    x = rng.standard_normal((n, cin, h, w_)).astype(np.float32)
+    wt = (rng.standard_normal((cout, cin, kh, kw)) * np.sqrt(2.0 / (cin * kh * kw))).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, cout).astype(np.float32)
+    attrs = dict(kernel_shape=[kh, kw], strides=[sh, sw], pads=pads, dilations=[dh, dw])
+    model = single_op_model("Conv", attrs, [x, wt, b], n_graph_inputs=1)
+    (want,) = ref_runner.run_model(model, [x])
+    before = cuda_context.stats()["tensor_core_launches"]
+    (got,) = run_cuda(model, [x], cuda_context)
+    assert cuda_context.stats()["tensor_core_launches"] > before
+    assert got.shape == want.shape, (attrs, x.shape)
+    assert max_err_rel_linf(got, want) <= TOL, (attrs, x.shape)

@@ -1077,8 +1077,10 @@ struct WeightEntry {
   float* lo = nullptr;
   int64_t rows = 0, k = 0;
   int64_t src_bytes = 0;  // size of the caller's weight buffer the split was made from
-  int tile_n = 0;
-  CUtensorMap map_hi, map_lo;
+  // tensor maps of the split copies for tile heights of 32, 64 and 128 weight rows (index log2(n / 32)),
+  // encoded when a launch first asks for that height
+  CUtensorMap map_hi[3], map_lo[3];
+  bool has_map[3] = {false, false, false};
 };
 
 struct TcState {
@@ -1146,7 +1148,6 @@ int get_weight(wdc_context* ctx, const float* w, const float* scale, float alpha
   e.rows = rows;
   e.k = k;
   e.src_bytes = (c4_kh ? rows * c4_kh * c4_kw * c4_cin : rows * k) * 4;
-  e.tile_n = pick_tile_n(rows);
   int s = wdc_alloc(ctx, rows * k * 4, (void**)&e.hi);
   if (s != WDC_OK) return s;
   s = wdc_alloc(ctx, rows * k * 4, (void**)&e.lo);
@@ -1163,14 +1164,10 @@ int get_weight(wdc_context* ctx, const float* w, const float* scale, float alpha
   else
     split_tf32_kernel<<<grid_for(ctx, rows * k, 256, 8), 256, 0, ctx->stream>>>(w, e.hi, e.lo, rows * k, k, scale, alpha);
   s = wdc_check_launch(ctx, "split_tf32_kernel");
-  int r1 = encode_map(st, &e.map_hi, e.hi, rows, k, e.tile_n);
-  int r2 = encode_map(st, &e.map_lo, e.lo, rows, k, e.tile_n);
-  if (s != WDC_OK || r1 || r2) {
+  if (s != WDC_OK) {
     wdc_free(ctx, e.hi);
     wdc_free(ctx, e.lo);
-    if (s != WDC_OK) return s;
-    return wdc_fail(ctx, WDC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d, %d) for a [%lld, %lld] weight", r1, r2,
-                    (long long)rows, (long long)k);
+    return s;
   }
   auto ins = st->weights.emplace(key, e);
   *out = &ins.first->second;
@@ -1257,6 +1254,25 @@ bool encode_a_map(TcState* st, const TcProblem& p, const float* x, CUtensorMap* 
   return r == CUDA_SUCCESS;
 }
 
+// Tile width for an [M, N] output: the widest tile is the cheapest per column (a 64-column MMA costs about
+// 0.65 of a 128-column one, a 32-column one about 0.45), but a small problem cut into wide tiles leaves most
+// SMs without work, so the estimate waves(tiles / SMs) x cost picks the width.
+int choose_tile_n(const wdc_context* ctx, int64_t m, int64_t n) {
+  const int widest = pick_tile_n(n);
+  const double cost[3] = {0.45, 0.65, 1.0};
+  int best = widest;
+  double best_t = 1e300;
+  for (int t = widest, i = widest == 128 ? 2 : widest == 64 ? 1 : 0; t >= 32; t >>= 1, i--) {
+    const int64_t tiles = ceil_div64(m, TILE_M) * ceil_div64(n, t);
+    const double est = (double)ceil_div64(tiles, ctx->sm_count) * cost[i];
+    if (est < best_t - 1e-9) {
+      best_t = est;
+      best = t;
+    }
+  }
+  return best;
+}
+
 int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, float* y, int c4_kw = 0,
               int c4_cin = 0, bool w_k_major = true) {
   WeightEntry* we = nullptr;
@@ -1264,8 +1280,19 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
   if (s != WDC_OK) return s;
   p.scale = nullptr;  // folded into the split weights
   p.alpha = 1.f;
-  p.tile_n = we->tile_n;
-  if (ceil_div64(p.M, TILE_M) * ceil_div64(p.N, we->tile_n) >= (1ll << 31) - 65536) return WDC_ERR_UNSUPPORTED;
+  p.tile_n = choose_tile_n(ctx, p.M, p.N);
+  const int mi = p.tile_n == 128 ? 2 : p.tile_n == 64 ? 1 : 0;
+  if (!we->has_map[mi]) {
+    const int r1 = encode_map(tc_state(ctx), &we->map_hi[mi], we->hi, we->rows, we->k, p.tile_n);
+    const int r2 = encode_map(tc_state(ctx), &we->map_lo[mi], we->lo, we->rows, we->k, p.tile_n);
+    if (r1 || r2)
+      return wdc_fail(ctx, WDC_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d, %d) for a [%lld, %lld] weight", r1, r2,
+                      (long long)we->rows, (long long)we->k);
+    we->has_map[mi] = true;
+  }
+  const CUtensorMap& w_map_hi = we->map_hi[mi];
+  const CUtensorMap& w_map_lo = we->map_lo[mi];
+  if (ceil_div64(p.M, TILE_M) * ceil_div64(p.N, p.tile_n) >= (1ll << 31) - 65536) return WDC_ERR_UNSUPPORTED;
   p.tiles_m = (int)ceil_div64(p.M, TILE_M);
   p.tiles_n = (int)ceil_div64(p.N, p.tile_n);
   p.kblocks = (p.K + BLOCK_K - 1) / BLOCK_K;
@@ -1282,7 +1309,7 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
   int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   TcState* st = tc_state(ctx);
   // output and residual as [M, N] matrices cut into 32-row x cw-column boxes for the epilogue warps
-  CUtensorMap map_y = we->map_hi, map_res = we->map_hi;
+  CUtensorMap map_y = w_map_hi, map_res = w_map_hi;
   {
     const int ncols = p.tile_n / 2, cw = ncols < 32 ? ncols : 32;
     bool can = (p.N % 4 == 0) && p.M < (1ll << 31) && !(p.dbg & 64) && (((uintptr_t)p.scale | (uintptr_t)p.shift) & 15) == 0 &&
@@ -1296,9 +1323,9 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
   const bool a_by_tma = encode_a_map(st, p, x, &map_a);
   if (!a_by_tma && p.c4 == 2) return WDC_ERR_UNSUPPORTED;  // the paired layout exists only for the TMA path
   if (a_by_tma)
-    tc_igemm_kernel<true><<<grid, NUM_THREADS, smem, ctx->stream>>>(p, x, we->map_hi, we->map_lo, map_a, map_y, map_res, y);
+    tc_igemm_kernel<true><<<grid, NUM_THREADS, smem, ctx->stream>>>(p, x, w_map_hi, w_map_lo, map_a, map_y, map_res, y);
   else
-    tc_igemm_kernel<false><<<grid, NUM_THREADS, smem, ctx->stream>>>(p, x, we->map_hi, we->map_lo, we->map_hi, map_y,
+    tc_igemm_kernel<false><<<grid, NUM_THREADS, smem, ctx->stream>>>(p, x, w_map_hi, w_map_lo, w_map_hi, map_y,
                                                                      map_res, y);
   ctx->n_tc_launch++;
   return wdc_check_launch(ctx, "tc_igemm_kernel");

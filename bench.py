@@ -127,7 +127,7 @@ def cpu_port_images_per_sec(n_images: int):
 def run_reference(args, rank: int) -> None:
     if rank != 0:
         return
-    n = args.cpu_images
+    n = args.ref_images
     vals = []
     for _ in range(args.warmup):
         cpu_port_images_per_sec(1)
@@ -291,7 +291,10 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cpu-images", type=int, default=8, help="images per CPU-baseline sample")
+    ap.add_argument("--cpu-images", type=int, default=64,
+                    help="images in the CPU-baseline sample of the default arm (about 10 s of host work)")
+    ap.add_argument("--ref-images", type=int, default=16,
+                    help="images per step of the reference arm (13 steps of 16 images are about 35 s of host work)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

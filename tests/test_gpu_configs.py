@@ -6,7 +6,7 @@ import pytest
 from oracle import ref_runner
 from webdnn_b200 import zoo
 
-from util import max_err_rel_linf, run_cuda
+from util import max_err_rel_linf, run_cuda, single_op_model
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-4
@@ -241,3 +241,35 @@ def test_captured_run_replays_bit_exact(cuda_context, which):
     # the context keeps working node by node after the graph is gone
     assert np.array_equal(r.run([CPUTensor.from_array(xs[1])])[0].numpy(), want[1])
     r.dispose()
+
+
+def test_config3_full_batch_properties(cuda_context):
+    """ResNet-50 at the benchmark's batch of 256, where the CPU oracle would need a minute: properties
+    that do not depend on the size.  The batch is 4 distinct images repeated 64 times, so (a) every copy
+    of an image must give the logits of its first copy (each image is independent of its neighbours
+    and of its position in the batch; the summation order depends on the tile's position, so this is
+    checked to 1e-5, not bit for bit), and (b) the first four rows must agree with a batch-4 run of the
+    same network, which the oracle checks at small batch in test_config3_resnet50."""
+    base = zoo.make_input((4, 3, 224, 224))
+    big = np.tile(base, (64, 1, 1, 1))
+    model = zoo.resnet50(256, softmax=False)
+    (got,) = run_cuda(model, [big], cuda_context)
+    assert got.shape == (256, 1000) and np.isfinite(got).all()
+    for i in range(4):
+        copies = got[i::4]
+        assert max_err_rel_linf(copies, np.broadcast_to(copies[0], copies.shape)) <= 1e-5
+    (small,) = run_cuda(zoo.resnet50(4, softmax=False), [base], cuda_context)
+    assert max_err_rel_linf(got[:4], small) <= 1e-5
+
+
+def test_config2_full_size_scaling_is_exact(cuda_context):
+    """Convolution is linear: with bias-free weights, doubling the input doubles every product of the
+    3xTF32 split exactly (powers of two do not touch mantissas), so the output doubles bit for bit."""
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((32, 64, 56, 56)).astype(np.float32)
+    w = (rng.standard_normal((64, 64, 3, 3)) * 0.06).astype(np.float32)
+    attrs = dict(kernel_shape=[3, 3], strides=[1, 1], pads=[1, 1, 1, 1])
+    model = single_op_model("Conv", attrs, [x, w], n_graph_inputs=1)
+    (y1,) = run_cuda(model, [x], cuda_context)
+    (y2,) = run_cuda(model, [2.0 * x], cuda_context)
+    assert np.array_equal(y2.view(np.uint32), (2.0 * y1).view(np.uint32))

@@ -202,3 +202,58 @@ def test_conv_random_geometry(cuda_context, seed):
     assert cuda_context.stats()["tensor_core_launches"] > before
     assert got.shape == want.shape, (attrs, x.shape)
     assert max_err_rel_linf(got, want) <= TOL, (attrs, x.shape)
+
+
+@pytest.mark.parametrize("n,cin,cout,size,k,stride,pad,res", [
+    (1, 512, 512, (7, 7), 3, 1, 1, False),      # 49 rows, K = 4608: many ranges
+    (1, 2048, 512, (7, 7), 1, 1, 0, False),     # 1x1, K = 2048
+    (2, 256, 256, (14, 14), 3, 1, 1, True),     # with residual + Relu in the second pass
+    (1, 1024, 36, (5, 5), 1, 1, 0, False),      # narrow output (N = 36), ragged last range (K blocks 32 = 4 x 8)
+    (1, 320, 64, (9, 9), 3, 2, 1, False),       # K blocks = 90: ranges of unequal length
+])
+def test_split_reduction(cuda_context, n, cin, cout, size, k, stride, pad, res):
+    """Small outputs with long reductions run as (tile, K range) work units plus a reduction pass: the
+    result must not depend on that (parity with the oracle, and with the unsplit kernel)."""
+    import os
+    from ctypes import byref
+    from webdnn_b200.backend import CPUTensor
+    from webdnn_b200.lib import ConvDesc
+    ctx = cuda_context
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((n, cin, size[0], size[1])).astype(np.float32)
+    wt = (rng.standard_normal((cout, cin, k, k)) * np.sqrt(2.0 / (cin * k * k))).astype(np.float32)
+    shift = rng.uniform(-0.1, 0.1, cout).astype(np.float32)
+    oh = (size[0] + 2 * pad - k) // stride + 1
+    ow = (size[1] + 2 * pad - k) // stride + 1
+    r = rng.standard_normal((n, cout, oh, ow)).astype(np.float32) if res else None
+    want = ops.conv2d(x, wt, shift, (stride, stride), (pad,) * 4).astype(np.float64)
+    if res:
+        want = np.maximum(want + r, 0)
+    want = want.astype(np.float32)
+    dx = ctx.channels_last(ctx.move_tensor(CPUTensor.from_array(x)))
+    dw = ctx.move_tensor(CPUTensor.from_array(np.ascontiguousarray(wt.transpose(0, 2, 3, 1))))
+    dsh = ctx.move_tensor(CPUTensor.from_array(shift))
+    dr = ctx.channels_last(ctx.move_tensor(CPUTensor.from_array(r))) if res else None
+    d = ConvDesc(batch=n, ch_in=cin, in_h=size[0], in_w=size[1], ch_out=cout, k_h=k, k_w=k, out_h=oh, out_w=ow,
+                 stride_h=stride, stride_w=stride, pad_t=pad, pad_l=pad, dil_h=1, dil_w=1, group=1, relu=int(res))
+    warm = ctx.empty_tensor([n, cout, oh, ow], layout="nhwc")
+    ctx.conv2d(d, dx, dw, None, dsh, dr, warm)     # first use of the weights: their one-time split
+    warm.dispose()
+    outs = []
+    for no_split in (False, True):
+        if no_split:
+            os.environ["WDC_TC_NO_SPLITK"] = "1"
+        try:
+            dy = ctx.empty_tensor([n, cout, oh, ow], layout="nhwc")
+            before = ctx.stats()["launches"]
+            ctx.conv2d(d, dx, dw, None, dsh, dr, dy)
+            launches = ctx.stats()["launches"] - before
+            outs.append((ctx.canonical(dy).get_data().reshape(n, cout, oh, ow), launches))
+            dy.dispose()
+        finally:
+            os.environ.pop("WDC_TC_NO_SPLITK", None)
+    (split, l_split), (single, l_single) = outs
+    assert l_split == l_single + 1, (l_split, l_single)    # the reduction pass really ran
+    assert max_err_rel_linf(split, want) <= TOL
+    assert max_err_rel_linf(single, want) <= TOL
+    assert max_err_rel_linf(split, single) <= 1e-5

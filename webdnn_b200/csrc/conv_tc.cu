@@ -88,6 +88,9 @@ struct TcProblem {
   int kblocks;        // ceil(K / 32)
   int cblocks;        // K blocks per filter tap = ceil(ch_in / 32)
   int tile_n;         // 32, 64 or 128
+  int splits;         // > 1: the reduction is cut into `splits` ranges of kbs K blocks; work unit = (tile, range);
+  int kbs;            //      each unit stores its raw partial sums at row range * m_pad + m of a workspace
+  int64_t m_pad;      //      (tiles_m * 128 rows per range); a second kernel adds the ranges and applies the epilogue
   int tma_epi;        // 1: residual tiles and output tiles move by TMA (map_res, map_y)
   int c4;             // 1: input has 4 channels per pixel, one K block per filter row, chunk j = tap kx;
                       // 2: the same with the row physically padded on the left and stride_w 2, so that taps
@@ -190,6 +193,14 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t pari
   for (int i = 0; i < 4096; i++)
     if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_timed(bar, parity, ss, status, code);
+}
+
+// Work unit u of a launch: tile u / splits, reduction range u % splits (K blocks kb0 .. kb0 + kbn - 1).
+__device__ __forceinline__ void unit_of(const TcProblem& p, int u, int& tile, int& sp, int& kb0, int& kbn) {
+  tile = u / p.splits;
+  sp = u - tile * p.splits;
+  kb0 = sp * p.kbs;
+  kbn = p.kblocks - kb0 < p.kbs ? p.kblocks - kb0 : p.kbs;
 }
 
 __device__ __forceinline__ bool elect_one() {
@@ -309,6 +320,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
   SharedStorage* ss = reinterpret_cast<SharedStorage*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_tiles = p.tiles_m * p.tiles_n;
+  const int total_units = total_tiles * p.splits;   // = total_tiles unless the reduction is split
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
@@ -371,7 +383,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
   const uint32_t tmem_base = ss->tmem_base;
   // Each CTA walks the K blocks from a different starting point so that the CTAs, which all need the
   // same weight tiles, do not ask the same L2 lines at the same moment.
-  const int rot = (int)(((int64_t)blockIdx.x * p.kblocks) / gridDim.x);
+  const int rot = p.splits > 1 ? 0 : (int)(((int64_t)blockIdx.x * p.kblocks) / gridDim.x);
 
   if (kTmaA && warp < NUM_A_WARPS) {
     // ===================================================================== A producers (split only)
@@ -380,8 +392,12 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     // tensor core ignores the low 13 bits of a tf32 operand, i.e. it truncates) and
     // lo = x - truncate(x), exact in fp32, as the low operand.
     const int row = threadIdx.x;
-    const int64_t my_tiles = (total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int64_t items = my_tiles * p.kblocks;
+    int64_t items = 0;   // K blocks of all work units of this CTA
+    for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
+      int tile, sp, kb0, kbn;
+      unit_of(p, u, tile, sp, kb0, kbn);
+      items += kbn;
+    }
     const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)TMEM_A_COL0;
     // normal mode: 128-byte rows, 16-byte chunks XOR-swizzled by the row; 4-channel mode: 8 planes
     // (one per filter tap of the row) of 128 rows x 16 bytes, or 4 planes (one per tap pair) of 128
@@ -437,19 +453,22 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       uint32_t phase = 0;
       const uint32_t hw = (uint32_t)p.out_h * (uint32_t)p.out_w;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        int tile, sp, kb0, kbn;
+        unit_of(p, u, tile, sp, kb0, kbn);
         // base pixel of the tile's first row
         const int64_t m0 = (int64_t)(tile / p.tiles_n) * TILE_M;
         const int64_t n = m0 / hw;
         const uint32_t rem = (uint32_t)(m0 - n * hw);
         const int oy = (int)(rem / (uint32_t)p.out_w), ox = (int)rem - oy * p.out_w;
         const int cw = p.c4 == 2 ? ox : ox * p.stride_w - p.pad_l, ch = oy * p.stride_h - p.pad_t;
-        // first K block of this CTA's rotation
-        const int tap = rot / p.cblocks;
-        int c0 = (rot - tap * p.cblocks) * BLOCK_K;
+        // first K block: this CTA's rotation, or the start of the unit's range (no rotation then)
+        const int kfirst = kb0 + rot;
+        const int tap = kfirst / p.cblocks;
+        int c0 = (kfirst - tap * p.cblocks) * BLOCK_K;
         int ky = tap / p.k_w, kx = tap - ky * p.k_w;
-        if (p.c4) ky = rot;
-        for (int kb = 0; kb < p.kblocks; kb++) {
+        if (p.c4) ky = kfirst;
+        for (int kb = 0; kb < kbn; kb++) {
           if (!mbar_wait(&ss->a_empty_bar[stage], phase ^ 1, ss, p.status, 22)) { ok = false; break; }
           if (p.c4) {
             // K block = filter row ky; one load of 128 pixels x 4 channels per tap of the row, or of 128
@@ -618,13 +637,15 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       uint32_t phase = 0;
       const uint32_t bytes = 2u * (uint32_t)p.tile_n * BLOCK_K * 4u;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        int tile, sp, kb0, kbn;
+        unit_of(p, u, tile, sp, kb0, kbn);
         const int n0 = (int)(tile % p.tiles_n) * p.tile_n;
-        for (int kb = 0; kb < p.kblocks; kb++) {
+        for (int kb = 0; kb < kbn; kb++) {
           if (!mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 21)) { ok = false; break; }
           mbar_arrive_expect_tx(&ss->full_bar[stage], bytes);
-          int kr = kb + rot;
-          if (kr >= p.kblocks) kr -= p.kblocks;
+          int kr = kb0 + kb + rot;
+          if (kr >= kb0 + kbn) kr -= kbn;
           tma_load_2d(ss->w_hi[stage], &map_w_hi, &ss->full_bar[stage], kr * BLOCK_K, n0);
           tma_load_2d(ss->w_lo[stage], &map_w_lo, &ss->full_bar[stage], kr * BLOCK_K, n0);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -639,10 +660,12 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       const uint32_t idesc = make_idesc(p.tile_n);
       int64_t seg = 0;  // segments issued by this CTA so far
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        int tile, sp, kb0, kbn;
+        unit_of(p, u, tile, sp, kb0, kbn);
         uint32_t d_tmem = 0;
         int buf = 0;
-        for (int kb = 0; kb < p.kblocks; kb++) {
+        for (int kb = 0; kb < kbn; kb++) {
           const int in_seg = kb % SEG_KBLOCKS;
           if (in_seg == 0) {
             buf = (int)(seg % NBUF);
@@ -667,7 +690,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
           }
           umma_commit(&ss->empty_bar[stage]);  // stage reusable once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
-          if (in_seg == SEG_KBLOCKS - 1 || kb == p.kblocks - 1) {
+          if (in_seg == SEG_KBLOCKS - 1 || kb == kbn - 1) {
             umma_commit(&ss->seg_full_bar[buf]);  // partial sum of this segment is complete
             seg++;
           }
@@ -681,7 +704,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     const int half = ew >> 2;                     // which half of the tile's columns
     const int ncols = p.tile_n >> 1;              // 16, 32 or 64 columns per warp
     const int col0 = half * ncols;
-    const int nseg = (p.kblocks + SEG_KBLOCKS - 1) / SEG_KBLOCKS;
+    int nseg = (p.kblocks + SEG_KBLOCKS - 1) / SEG_KBLOCKS;
     int64_t seg = 0;
     bool ok = true;
     if (p.tma_epi) {
@@ -705,8 +728,12 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         tma_load_2d(ss->epi_buf[ew][0], &map_res, &ss->res_bar[ew][0], (int)(t0 % p.tiles_n) * p.tile_n + col0,
                     (int)((t0 / p.tiles_n) * TILE_M + q * 32));
       }
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        int tile, sp, kb0, kbn;
+        unit_of(p, u, tile, sp, kb0, kbn);
+        nseg = (kbn + SEG_KBLOCKS - 1) / SEG_KBLOCKS;
         const int64_t mrow0 = (int64_t)(tile / p.tiles_n) * TILE_M + q * 32;   // first row of this warp
+        const int64_t store_row = mrow0 + sp * p.m_pad;   // split reductions: row block `sp` of the workspace
         const int nbase = (int)(tile % p.tiles_n) * p.tile_n + col0;
         // The accumulators start at the per-column addend (bias / folded BatchNormalization shift); the
         // per-column multiplier is already in the weights.  Warp-uniform 16-byte loads from the table in
@@ -801,11 +828,11 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
               __syncwarp();
               if (lane == 0) {
                 const int col = nbase + c * 32;
-                if (!(p.dbg & 2) && mrow0 < p.M && col < p.N) tma_store_2d(&map_y, sbuf, col, (int)mrow0);
+                if (!(p.dbg & 2) && mrow0 < p.M && col < p.N) tma_store_2d(&map_y, sbuf, col, (int)store_row);
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the other buffer's store has read it
                 if (use_res) {
-                  int nt = tile;
+                  int nt = tile;   // (a launch with a residual has splits == 1: unit == tile)
                   int nc = c + 1;
                   if (nc == nch) { nc = 0; nt += gridDim.x; }
                   if (nt < total_tiles) {
@@ -994,6 +1021,41 @@ __global__ void __launch_bounds__(256) split_tf32_transpose_kernel(const float* 
       }
     }
     __syncthreads();
+  }
+}
+
+// Second pass of a split reduction: y[m, n] = epilogue(sum over ranges of ws[range * m_pad + m, n]), ranges added in
+// ascending order (deterministic), then shift, residual and Relu as in the fused epilogue.  N % 4 == 0.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ ws, float* __restrict__ y,
+                                                            const float* __restrict__ shift, float shift_mul,
+                                                            const float* __restrict__ residual, int64_t res_stride,
+                                                            float res_mul, int relu, int64_t M, int N, int64_t m_pad,
+                                                            int splits) {
+  const int nv = N / 4;
+  const int64_t total = M * nv;
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  for (; i < total; i += step) {
+    const int64_t m = i / nv;
+    const int c = (int)(i - m * nv) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (shift) {
+      const float4 b = __ldg(reinterpret_cast<const float4*>(shift + c));
+      acc = make_float4(shift_mul * b.x, shift_mul * b.y, shift_mul * b.z, shift_mul * b.w);
+    }
+    for (int s = 0; s < splits; s++) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(ws + (s * m_pad + m) * N + c));
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (residual) {
+      const float4 r = __ldg(reinterpret_cast<const float4*>(residual + m * res_stride + c));
+      acc.x = fmaf(res_mul, r.x, acc.x); acc.y = fmaf(res_mul, r.y, acc.y);
+      acc.z = fmaf(res_mul, r.z, acc.z); acc.w = fmaf(res_mul, r.w, acc.w);
+    }
+    if (relu) {
+      acc.x = relu_nan(acc.x); acc.y = relu_nan(acc.y); acc.z = relu_nan(acc.z); acc.w = relu_nan(acc.w);
+    }
+    *reinterpret_cast<float4*>(y + m * N + c) = acc;
   }
 }
 
@@ -1254,23 +1316,39 @@ bool encode_a_map(TcState* st, const TcProblem& p, const float* x, CUtensorMap* 
   return r == CUDA_SUCCESS;
 }
 
-// Tile width for an [M, N] output: the widest tile is the cheapest per column (a 64-column MMA costs about
-// 0.65 of a 128-column one, a 32-column one about 0.45), but a small problem cut into wide tiles leaves most
-// SMs without work, so the estimate waves(tiles / SMs) x cost picks the width.
-int choose_tile_n(const wdc_context* ctx, int64_t m, int64_t n) {
+// Tile width and reduction split for an [M, N] output with `kblocks` K blocks.  The widest tile is the
+// cheapest per column (a 64-column MMA costs about 0.65 of a 128-column one, a 32-column one about 0.45),
+// but a small problem cut into wide tiles leaves most SMs without work.  Such a problem can also cut its
+// reduction into ranges that run as separate work units (each at least 8 K blocks long, at most 8 ranges);
+// the ranges' partial sums then go through a workspace and a second, memory-bound pass, charged here as a
+// twentieth of a tile.  The estimate waves(units / SMs) x cost / splits picks both.
+void choose_tiling(const wdc_context* ctx, int64_t m, int64_t n, int kblocks, bool may_split, int* tile_n,
+                   int* splits) {
   const int widest = pick_tile_n(n);
   const double cost[3] = {0.45, 0.65, 1.0};
-  int best = widest;
   double best_t = 1e300;
+  *tile_n = widest;
+  *splits = 1;
   for (int t = widest, i = widest == 128 ? 2 : widest == 64 ? 1 : 0; t >= 32; t >>= 1, i--) {
     const int64_t tiles = ceil_div64(m, TILE_M) * ceil_div64(n, t);
-    const double est = (double)ceil_div64(tiles, ctx->sm_count) * cost[i];
-    if (est < best_t - 1e-9) {
-      best_t = est;
-      best = t;
+    int smax = 1;
+    if (may_split && tiles * 2 <= ctx->sm_count) {
+      smax = (int)(ctx->sm_count / tiles);
+      if (smax > 8) smax = 8;
+      if (smax > kblocks / 8) smax = kblocks / 8;
+      if (smax < 1) smax = 1;
+    }
+    for (int sp = 1; sp <= smax; sp++) {
+      const int kbs = (kblocks + sp - 1) / sp;
+      if ((sp - 1) * kbs >= kblocks) continue;   // an empty last range
+      const double est = (double)ceil_div64(tiles * sp, ctx->sm_count) * cost[i] * kbs / kblocks + (sp > 1 ? 0.05 : 0.0);
+      if (est < best_t - 1e-9) {
+        best_t = est;
+        *tile_n = t;
+        *splits = sp;
+      }
     }
   }
-  return best;
 }
 
 int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, float* y, int c4_kw = 0,
@@ -1280,7 +1358,14 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
   if (s != WDC_OK) return s;
   p.scale = nullptr;  // folded into the split weights
   p.alpha = 1.f;
-  p.tile_n = choose_tile_n(ctx, p.M, p.N);
+  p.kblocks = (p.K + BLOCK_K - 1) / BLOCK_K;
+  {
+    // a split reduction needs the TMA paths on both sides (checked again below) and no first-layer mode
+    const bool may_split = !p.c4 && p.N % 4 == 0 && p.M < (1ll << 27) && tc_state(ctx)->encode_im2col != nullptr &&
+                           (((uintptr_t)p.shift | (uintptr_t)p.residual | (uintptr_t)y) & 15) == 0 &&
+                           (!p.residual || p.res_stride % 4 == 0) && !getenv("WDC_TC_NO_SPLITK");
+    choose_tiling(ctx, p.M, p.N, p.kblocks, may_split, &p.tile_n, &p.splits);
+  }
   const int mi = p.tile_n == 128 ? 2 : p.tile_n == 64 ? 1 : 0;
   if (!we->has_map[mi]) {
     const int r1 = encode_map(tc_state(ctx), &we->map_hi[mi], we->hi, we->rows, we->k, p.tile_n);
@@ -1295,7 +1380,6 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
   if (ceil_div64(p.M, TILE_M) * ceil_div64(p.N, p.tile_n) >= (1ll << 31) - 65536) return WDC_ERR_UNSUPPORTED;
   p.tiles_m = (int)ceil_div64(p.M, TILE_M);
   p.tiles_n = (int)ceil_div64(p.N, p.tile_n);
-  p.kblocks = (p.K + BLOCK_K - 1) / BLOCK_K;
   p.status = ctx->status_word;
   {
     static int dbg = -1;
@@ -1305,22 +1389,49 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
     }
     p.dbg = dbg;
   }
-  int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
-  int grid = (int)(tiles < ctx->sm_count ? tiles : ctx->sm_count);
   TcState* st = tc_state(ctx);
-  // output and residual as [M, N] matrices cut into 32-row x cw-column boxes for the epilogue warps
+  p.m_pad = (int64_t)p.tiles_m * TILE_M;
+  p.kbs = (p.kblocks + p.splits - 1) / p.splits;
+  // the epilogue of a split reduction belongs to the second pass
+  const float* ep_shift = p.shift;
+  const float* ep_residual = p.residual;
+  const int ep_relu = p.relu;
+  const float ep_shift_mul = p.shift_mul, ep_res_mul = p.res_mul;
+  const int64_t ep_res_stride = p.res_stride;
+  float* ws = nullptr;
+  CUtensorMap map_a;
+  bool a_by_tma = encode_a_map(st, p, x, &map_a);
+  if (p.splits > 1 && !a_by_tma) {   // geometry outside the im2col map: one range, gathering producers
+    p.splits = 1;
+    p.kbs = p.kblocks;
+  }
+  if (p.splits > 1) {
+    s = wdc_alloc(ctx, (int64_t)p.splits * p.m_pad * p.N * 4, (void**)&ws);
+    if (s != WDC_OK) return s;
+    p.shift = nullptr;
+    p.residual = nullptr;
+    p.relu = 0;
+  }
+  const int64_t units = (int64_t)p.tiles_m * p.tiles_n * p.splits;
+  int grid = (int)(units < ctx->sm_count ? units : ctx->sm_count);
+  // output (or workspace) and residual as row-major matrices cut into 32-row x cw-column boxes for the epilogue warps
   CUtensorMap map_y = w_map_hi, map_res = w_map_hi;
   {
     const int ncols = p.tile_n / 2, cw = ncols < 32 ? ncols : 32;
-    bool can = (p.N % 4 == 0) && p.M < (1ll << 31) && !(p.dbg & 64) && (((uintptr_t)p.scale | (uintptr_t)p.shift) & 15) == 0 &&
-               encode_rows_map(st, &map_y, y, p.M, p.N, p.N, cw) == 0;
+    bool can = (p.N % 4 == 0) && p.M < (1ll << 31) && !(p.dbg & 64) && (((uintptr_t)p.scale | (uintptr_t)p.shift) & 15) == 0;
+    if (can) {
+      if (p.splits > 1) can = encode_rows_map(st, &map_y, ws, (int64_t)p.splits * p.m_pad, p.N, p.N, cw) == 0;
+      else can = encode_rows_map(st, &map_y, y, p.M, p.N, p.N, cw) == 0;
+    }
     if (can && p.residual)
       can = p.res_stride % 4 == 0 && encode_rows_map(st, &map_res, p.residual, p.M, p.N, p.res_stride, cw) == 0;
     p.tma_epi = can ? 1 : 0;
   }
-  CUtensorMap map_a;
+  if (p.splits > 1 && !p.tma_epi) {
+    wdc_free(ctx, ws);
+    return wdc_fail(ctx, WDC_ERR_CUDA, "tensor map for the split-reduction workspace could not be encoded");
+  }
   const size_t smem = sizeof(SharedStorage) + 1024;
-  const bool a_by_tma = encode_a_map(st, p, x, &map_a);
   if (!a_by_tma && p.c4 == 2) return WDC_ERR_UNSUPPORTED;  // the paired layout exists only for the TMA path
   if (a_by_tma)
     tc_igemm_kernel<true><<<grid, NUM_THREADS, smem, ctx->stream>>>(p, x, w_map_hi, w_map_lo, map_a, map_y, map_res, y);
@@ -1328,7 +1439,16 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
     tc_igemm_kernel<false><<<grid, NUM_THREADS, smem, ctx->stream>>>(p, x, w_map_hi, w_map_lo, w_map_hi, map_y,
                                                                      map_res, y);
   ctx->n_tc_launch++;
-  return wdc_check_launch(ctx, "tc_igemm_kernel");
+  s = wdc_check_launch(ctx, "tc_igemm_kernel");
+  if (p.splits > 1) {
+    if (s == WDC_OK) {
+      splitk_reduce_kernel<<<grid_for(ctx, p.M * (p.N / 4), 256, 8), 256, 0, ctx->stream>>>(
+          ws, y, ep_shift, ep_shift_mul, ep_residual, ep_res_stride, ep_res_mul, ep_relu, p.M, p.N, p.m_pad, p.splits);
+      s = wdc_check_launch(ctx, "splitk_reduce_kernel");
+    }
+    wdc_free(ctx, ws);   // stream-ordered: reused only by work queued after the reduction
+  }
+  return s;
 }
 
 bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }

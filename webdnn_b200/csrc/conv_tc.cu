@@ -365,9 +365,19 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     }
     ss->ktab[kb] = e;
   }
-  if (p.tma_epi && p.N <= SHIFT_TAB)
-    for (int i = threadIdx.x; i < SHIFT_TAB + 128; i += NUM_THREADS)
+  if (p.tma_epi && p.N <= SHIFT_TAB) {
+    // entries a warp can touch: its first column (< tiles_n * tile_n) plus 64
+    const int used = p.tiles_n * p.tile_n + 64;
+    for (int i = threadIdx.x; i < used; i += NUM_THREADS)
       ss->shift_tab[i] = (p.shift && i < p.N) ? p.shift_mul * __ldg(p.shift + i) : 0.f;
+  }
+  if (threadIdx.x == 32) {
+    // descriptor fetches of the first TMA operations overlap the rest of the set-up
+    asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_w_hi) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_w_lo) : "memory");
+    if (kTmaA) asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_a) : "memory");
+    if (p.tma_epi) asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_y) : "memory");
+  }
   if (kTmaA && p.c4) {
     // 4-channel mode: planes of taps past the filter width are never loaded; their weights are zero,
     // so the operand only has to be finite

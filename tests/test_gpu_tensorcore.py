@@ -257,3 +257,14 @@ def test_split_reduction(cuda_context, n, cin, cout, size, k, stride, pad, res):
     assert max_err_rel_linf(split, want) <= TOL
     assert max_err_rel_linf(single, want) <= TOL
     assert max_err_rel_linf(split, single) <= 1e-5
+
+
+@pytest.mark.parametrize("n,cin,cout,size,k,stride,pad,dil", [
+    (2, 48, 64, (13, 15), 3, 1, 1, 1),     # 48 channels: one full and one half K block per tap
+    (1, 100, 32, (9, 9), 3, 2, 1, 1),      # 100 channels: the last block of a tap has 4 of 32
+    (2, 24, 40, (11, 7), 5, 1, 2, 1),      # fewer than 32 channels: every block is short
+    (1, 72, 128, (8, 8), 1, 1, 0, 1),      # 1x1
+    (1, 40, 64, (12, 12), 3, 1, 2, 2),     # dilation
+])
+def test_conv_channels_not_multiple_of_32(cuda_context, n, cin, cout, size, k, stride, pad, dil):
+    assert _conv_case(cuda_context, n, cin, cout, size, k, stride, pad, dil) <= TOL

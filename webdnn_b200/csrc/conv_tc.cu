@@ -660,8 +660,15 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
           mbar_arrive_expect_tx(&ss->full_bar[stage], bytes);
           int kr = kb0 + kb + rot;
           if (kr >= kb0 + kbn) kr -= kbn;
-          tma_load_2d(ss->w_hi[stage], &map_w_hi, &ss->full_bar[stage], kr * BLOCK_K, n0);
-          tma_load_2d(ss->w_lo[stage], &map_w_lo, &ss->full_bar[stage], kr * BLOCK_K, n0);
+          // K offset of the block in a weight row: blocks are counted per filter tap, and when the channel
+          // count is not a multiple of 32 a tap's last block is short (its tail columns meet zeros of A)
+          int kx0 = kr * BLOCK_K;
+          if (!p.c4 && p.cblocks * BLOCK_K != p.ch_in) {
+            const int tap = kr / p.cblocks;
+            kx0 = tap * p.ch_in + (kr - tap * p.cblocks) * BLOCK_K;
+          }
+          tma_load_2d(ss->w_hi[stage], &map_w_hi, &ss->full_bar[stage], kx0, n0);
+          tma_load_2d(ss->w_lo[stage], &map_w_lo, &ss->full_bar[stage], kx0, n0);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -1372,7 +1379,7 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
   if (s != WDC_OK) return s;
   p.scale = nullptr;  // folded into the split weights
   p.alpha = 1.f;
-  p.kblocks = (p.K + BLOCK_K - 1) / BLOCK_K;
+  p.kblocks = p.c4 ? p.K / BLOCK_K : p.k_h * p.k_w * p.cblocks;   // K blocks are counted per filter tap
   {
     // a split reduction needs the TMA paths on both sides (checked again below) and no first-layer mode
     const bool may_split = !p.c4 && p.N % 4 == 0 && p.M < (1ll << 27) && tc_state(ctx)->encode_im2col != nullptr &&
@@ -1499,7 +1506,7 @@ void wdc_tc_destroy(wdc_context* ctx) {
 int wdc_tc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, const float* w, const float* scale,
                   const float* shift, const float* residual, float* y) {
   const bool stem = d->group == 1 && d->ch_in <= 4 && d->k_w <= 8 && d->ch_out % 4 == 0;
-  if (!stem && (d->group != 1 || d->ch_in % BLOCK_K != 0 || d->ch_out % 4 != 0)) return WDC_ERR_UNSUPPORTED;
+  if (!stem && (d->group != 1 || d->ch_in % 4 != 0 || d->ch_out % 4 != 0)) return WDC_ERR_UNSUPPORTED;
   if (!aligned16(x) || !aligned16(w) || !aligned16(y) || (residual && !aligned16(residual))) return WDC_ERR_UNSUPPORTED;
   const int64_t K = d->ch_in * d->k_h * d->k_w;
   if (K > (1 << 30) || d->ch_out > (1 << 24)) return WDC_ERR_UNSUPPORTED;
@@ -1512,7 +1519,7 @@ int wdc_tc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, cons
   p.out_h = (int)d->out_h; p.out_w = (int)d->out_w; p.k_h = (int)d->k_h; p.k_w = (int)d->k_w;
   p.stride_h = (int)d->stride_h; p.stride_w = (int)d->stride_w; p.pad_t = (int)d->pad_t; p.pad_l = (int)d->pad_l;
   p.dil_h = (int)d->dil_h; p.dil_w = (int)d->dil_w;
-  p.cblocks = (int)(d->ch_in / BLOCK_K);
+  p.cblocks = (int)((d->ch_in + BLOCK_K - 1) / BLOCK_K);
   p.scale = scale; p.shift = shift; p.residual = residual; p.res_stride = d->ch_out;
   p.alpha = 1.f; p.shift_mul = 1.f; p.res_mul = 1.f; p.relu = d->relu;
   if (!stem) return launch_tc(ctx, p, x, w, y);

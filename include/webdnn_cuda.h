@@ -157,6 +157,9 @@ typedef struct wdc_conv_desc {
   int64_t ch_out, k_h, k_w, out_h, out_w;
   int64_t stride_h, stride_w, pad_t, pad_l, dil_h, dil_w, group;
   int relu;
+  int x_nchw; /* 1: x is NCHW [batch, ch_in, in_h, in_w] instead of NHWC.  Accepted only where the input is
+               * re-laid out anyway (ch_in <= 4, the network's first layer: the padding pass reads the planes
+               * directly and the separate NCHW -> NHWC conversion is saved); WDC_ERR_UNSUPPORTED elsewhere. */
 } wdc_conv_desc;
 int wdc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, const float* w,
                const float* scale, const float* shift, const float* residual, float* y);

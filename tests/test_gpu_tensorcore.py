@@ -268,3 +268,18 @@ def test_split_reduction(cuda_context, n, cin, cout, size, k, stride, pad, res):
 ])
 def test_conv_channels_not_multiple_of_32(cuda_context, n, cin, cout, size, k, stride, pad, dil):
     assert _conv_case(cuda_context, n, cin, cout, size, k, stride, pad, dil) <= TOL
+
+
+@pytest.mark.parametrize("n,cin,cout,size,k,stride,pad", [
+    (2, 3, 16, (20, 22), 5, 1, 2),     # stride 1: one 16-byte plane per tap
+    (2, 3, 64, (33, 31), 7, 2, 3),     # stride 2, odd sizes: pixel-pair planes
+    (1, 1, 8, (12, 12), 3, 1, 1),      # a single input channel
+    (3, 4, 32, (9, 14), 3, 2, 0),      # four channels, no padding
+])
+def test_first_layer_reads_nchw_input_directly(cuda_context, n, cin, cout, size, k, stride, pad):
+    """Few-channel first layers take the network's NCHW input as it is (no separate layout conversion
+    launch): one padding pass, one contraction."""
+    before = cuda_context.stats()["launches"]
+    assert _conv_case(cuda_context, n, cin, cout, size, k, stride, pad) <= TOL
+    # weight packing + weight split + padding pass + contraction (+ the output's conversion for the host)
+    assert cuda_context.stats()["launches"] - before <= 5

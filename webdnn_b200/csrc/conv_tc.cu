@@ -1081,23 +1081,26 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
 }
 
 // Stem mode operand preparation: 4 channels per pixel, 8 taps per filter row.
-__global__ void pad_channels4_kernel(const float* __restrict__ x, float* __restrict__ x4, int64_t pixels, int cin) {
+// `plane` = 0: x is NHWC (a pixel's channels are adjacent); > 0: x is NCHW with `plane` pixels per channel plane.
+__global__ void pad_channels4_kernel(const float* __restrict__ x, float* __restrict__ x4, int64_t pixels, int cin,
+                                     int64_t plane) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t step = (int64_t)gridDim.x * blockDim.x;
   for (; i < pixels; i += step) {
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float* s = x + i * cin;
+    const float* s = plane ? x + (i / plane) * plane * cin + i % plane : x + i * cin;
+    const int64_t cs = plane ? plane : 1;
     v.x = s[0];
-    if (cin > 1) v.y = s[1];
-    if (cin > 2) v.z = s[2];
-    if (cin > 3) v.w = s[3];
+    if (cin > 1) v.y = s[cs];
+    if (cin > 2) v.z = s[2 * cs];
+    if (cin > 3) v.w = s[3 * cs];
     reinterpret_cast<float4*>(x4)[i] = v;
   }
 }
 // Same with every image row shifted right by pad_l pixels into a zero-filled row of wp pixels: pixel pair
 // (2j, 2j+1) of the padded row is then the pair of taps (2j, 2j+1) of output column j for stride 2.
 __global__ void pad_channels4_rows_kernel(const float* __restrict__ x, float* __restrict__ x4, int64_t rows, int w,
-                                          int wp, int pad_l, int cin) {
+                                          int wp, int pad_l, int cin, int h_nchw) {
   int64_t total = rows * wp;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t step = (int64_t)gridDim.x * blockDim.x;
@@ -1106,11 +1109,14 @@ __global__ void pad_channels4_rows_kernel(const float* __restrict__ x, float* __
     const int px = (int)(i - r * wp) - pad_l;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     if (px >= 0 && px < w) {
-      const float* s = x + (r * w + px) * cin;
+      // h_nchw = 0: NHWC rows; > 0: NCHW with h_nchw rows per image (row r = image * h + y)
+      const int64_t plane = (int64_t)h_nchw * w;
+      const float* s = h_nchw ? x + (r / h_nchw) * plane * cin + (r % h_nchw) * w + px : x + (r * w + px) * cin;
+      const int64_t cs = h_nchw ? plane : 1;
       v.x = s[0];
-      if (cin > 1) v.y = s[1];
-      if (cin > 2) v.z = s[2];
-      if (cin > 3) v.w = s[3];
+      if (cin > 1) v.y = s[cs];
+      if (cin > 2) v.z = s[2 * cs];
+      if (cin > 3) v.w = s[3 * cs];
     }
     reinterpret_cast<float4*>(x4)[i] = v;
   }
@@ -1506,6 +1512,7 @@ void wdc_tc_destroy(wdc_context* ctx) {
 int wdc_tc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, const float* w, const float* scale,
                   const float* shift, const float* residual, float* y) {
   const bool stem = d->group == 1 && d->ch_in <= 4 && d->k_w <= 8 && d->ch_out % 4 == 0;
+  if (d->x_nchw && !stem) return WDC_ERR_UNSUPPORTED;
   if (!stem && (d->group != 1 || d->ch_in % 4 != 0 || d->ch_out % 4 != 0)) return WDC_ERR_UNSUPPORTED;
   if (!aligned16(x) || !aligned16(w) || !aligned16(y) || (residual && !aligned16(residual))) return WDC_ERR_UNSUPPORTED;
   const int64_t K = d->ch_in * d->k_h * d->k_w;
@@ -1534,9 +1541,10 @@ int wdc_tc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, cons
   if (s != WDC_OK) return s;
   if (pairs)
     pad_channels4_rows_kernel<<<grid_for(ctx, pixels, 256, 8), 256, 0, ctx->stream>>>(
-        x, x4, d->batch * d->in_h, (int)d->in_w, wp, (int)d->pad_l, (int)d->ch_in);
+        x, x4, d->batch * d->in_h, (int)d->in_w, wp, (int)d->pad_l, (int)d->ch_in, d->x_nchw ? (int)d->in_h : 0);
   else
-    pad_channels4_kernel<<<grid_for(ctx, pixels, 256, 8), 256, 0, ctx->stream>>>(x, x4, pixels, (int)d->ch_in);
+    pad_channels4_kernel<<<grid_for(ctx, pixels, 256, 8), 256, 0, ctx->stream>>>(x, x4, pixels, (int)d->ch_in,
+                                                                                 d->x_nchw ? d->in_h * d->in_w : 0);
   s = wdc_check_launch(ctx, "pad_channels4_kernel");
   if (s == WDC_OK) {
     p.c4 = pairs ? 2 : 1;

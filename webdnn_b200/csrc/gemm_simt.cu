@@ -219,6 +219,9 @@ extern "C" int wdc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float*
                           (double)(d->ch_in / d->group) * (double)d->k_h * (double)d->k_w);
   int s = wdc_tc_conv2d(ctx, d, x, w, scale, shift, residual, y);
   if (s != WDC_ERR_UNSUPPORTED) return s;
+  if (d->x_nchw)
+    return wdc_fail(ctx, WDC_ERR_UNSUPPORTED, "wdc_conv2d: an NCHW input is only taken by the first-layer path "
+                    "(ch_in <= 4, k_w <= 8, ch_out %% 4 == 0, group 1)");
   return wdc_simt_conv2d(ctx, d, x, w, scale, shift, residual, y);
 }
 

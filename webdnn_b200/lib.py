@@ -48,7 +48,7 @@ class GemmDesc(Structure):
 class ConvDesc(Structure):
     _fields_ = [(n, c_int64) for n in (
         "batch", "ch_in", "in_h", "in_w", "ch_out", "k_h", "k_w", "out_h", "out_w",
-        "stride_h", "stride_w", "pad_t", "pad_l", "dil_h", "dil_w", "group")] + [("relu", c_int)]
+        "stride_h", "stride_w", "pad_t", "pad_l", "dil_h", "dil_w", "group")] + [("relu", c_int), ("x_nchw", c_int)]
 
 
 class ConvTransposeDesc(Structure):

@@ -299,7 +299,11 @@ class CudaConv(base.Conv):
         elif rest:
             shift = rest.pop(0)  # plain Conv bias
         s = self.calc_shape(x.dims, w.dims)
-        xcl = context.channels_last(x)
+        # the first layer of an image network: its few-channel NCHW input is re-laid out inside the
+        # library anyway, so the separate NCHW -> NHWC conversion is skipped
+        direct = (x.layout == "nchw" and s["group"] == 1 and s["ch_in"] <= 4 and s["kernel_shape"][1] <= 8
+                  and s["ch_out"] % 4 == 0 and s["in_shape"][0] * s["in_shape"][1] > 1)
+        xcl = x if direct else context.channels_last(x)
         rcl = context.channels_last(residual) if residual is not None else None
         wp = _packed_weight(context, w)
         oh, ow = s["out_shape"]
@@ -308,7 +312,7 @@ class CudaConv(base.Conv):
                      ch_out=s["ch_out"], k_h=s["kernel_shape"][0], k_w=s["kernel_shape"][1], out_h=oh,
                      out_w=ow, stride_h=s["strides"][0], stride_w=s["strides"][1], pad_t=s["pads"][0],
                      pad_l=s["pads"][1], dil_h=s["dilations"][0], dil_w=s["dilations"][1],
-                     group=s["group"], relu=int(self.relu))
+                     group=s["group"], relu=int(self.relu), x_nchw=int(direct))
         context.conv2d(d, xcl, wp, scale, shift, rcl, y)
         if xcl is not x:
             xcl.dispose()

@@ -273,3 +273,47 @@ def test_config2_full_size_scaling_is_exact(cuda_context):
     (y1,) = run_cuda(model, [x], cuda_context)
     (y2,) = run_cuda(model, [2.0 * x], cuda_context)
     assert np.array_equal(y2.view(np.uint32), (2.0 * y1).view(np.uint32))
+
+
+@pytest.mark.parametrize("hidden,batch", [(64, 5), (24, 3)])
+def test_lstm_with_initial_state(cuda_context, hidden, batch):
+    """initial_h / initial_c (inputs 5 and 6; input 4, sequence_lens, is present and covers the whole
+    sequence) on the persistent kernel (hidden 64) and on the per-step path (hidden 24)."""
+    rng = np.random.default_rng(12)
+    T, I = 6, 16
+    lim = 1.0 / np.sqrt(hidden)
+    x = rng.standard_normal((T, batch, I)).astype(np.float32)
+    w = rng.uniform(-lim, lim, (1, 4 * hidden, I)).astype(np.float32)
+    r = rng.uniform(-lim, lim, (1, 4 * hidden, hidden)).astype(np.float32)
+    b = rng.uniform(-lim, lim, (1, 8 * hidden)).astype(np.float32)
+    lens = np.full(batch, T, np.int32)
+    h0 = rng.standard_normal((1, batch, hidden)).astype(np.float32)
+    c0 = rng.standard_normal((1, batch, hidden)).astype(np.float32)
+    model = single_op_model("LSTM", {"hidden_size": hidden, "direction": "forward"}, [x, w, r, b, lens, h0, c0],
+                            n_out=3, n_graph_inputs=1)
+    want = ref_runner.run_model(model, [x])
+    got = run_cuda(model, [x], cuda_context)
+    for g, wv in zip(got, want):
+        assert g.shape == wv.shape
+        assert max_err_rel_linf(g, wv) <= 1e-4
+
+
+def test_captured_run_of_a_transformer_graph(cuda_context):
+    """Capture and replay of the config-5 topology (fused linear layers, layer norms, attention with
+    reshapes and transposes driven by cpu-side shape constants)."""
+    from webdnn_b200.backend import CPUTensor
+    from webdnn_b200.runner import load
+    model = zoo.detr(batch=1, size=128, d=64, heads=4, enc_layers=1, dec_layers=1, ffn=128, queries=6, classes=9,
+                     width=16, blocks=(1, 1, 1, 1))
+    r = load(model, backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": cuda_context}})
+    xs = [zoo.make_input((1, 3, 128, 128), seed=s) for s in (1, 2)]
+    want = [[o.numpy() for o in r.run([CPUTensor.from_array(x)])] for x in xs]
+    cap = r.capture([CPUTensor.from_array(xs[0])])
+    try:
+        for x, w in zip(xs, want):
+            got = cap.run([CPUTensor.from_array(x)])
+            for g, wv in zip(got, w):
+                assert np.array_equal(g.numpy(), wv)
+    finally:
+        cap.dispose()
+    r.dispose()

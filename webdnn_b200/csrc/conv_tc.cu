@@ -60,6 +60,7 @@ constexpr int TILE_M = 128;
 constexpr int BLOCK_K = 32;           // fp32 elements per K block = one 128-byte swizzle row of W
 constexpr int STAGES = 3;             // W tiles in shared memory and A (hi, lo) column groups in TMEM
 constexpr int A_STAGES = 3;           // raw A tiles in shared memory (kTmaA)
+constexpr int A_STAGES_MAX = 6;       // tiles of at most 64 columns leave half of the W region free: 3 more A stages
 constexpr int NUM_A_WARPS = 4;
 constexpr int TMA_WARP = 4;
 constexpr int MMA_WARP = 5;
@@ -118,8 +119,9 @@ struct KEntry {
 
 struct __align__(1024) SharedStorage {
   // weight tiles first: each must start on a 1024-byte boundary for the 128B swizzle
-  unsigned char w_hi[STAGES][W_TILE_BYTES];
-  unsigned char w_lo[STAGES][W_TILE_BYTES];
+  // W_hi stages then W_lo stages, each tile_n x 128 bytes (16 KB slots for 128-column tiles; 8 KB slots for
+  // narrower tiles, whose unused 48 KB then hold three more raw A stages)
+  unsigned char w_region[2 * STAGES * W_TILE_BYTES];
   union {
     unsigned char a_raw[A_STAGES][A_TILE_BYTES];  // kTmaA: raw A tiles, 128B-swizzled rows of 32 floats
     KEntry ktab[KTAB];                          // gather kernels: per-K-block gather recipes
@@ -133,8 +135,8 @@ struct __align__(1024) SharedStorage {
   unsigned long long empty_bar[STAGES];
   unsigned long long seg_full_bar[NBUF];
   unsigned long long seg_empty_bar[NBUF];
-  unsigned long long a_full_bar[A_STAGES];
-  unsigned long long a_empty_bar[A_STAGES];
+  unsigned long long a_full_bar[A_STAGES_MAX];
+  unsigned long long a_empty_bar[A_STAGES_MAX];
   unsigned long long res_bar[NUM_EPI_WARPS][2];
   unsigned int tmem_base;
   volatile int abort_flag;
@@ -325,13 +327,22 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_tiles = p.tiles_m * p.tiles_n;
   const int total_units = total_tiles * p.splits;   // = total_tiles unless the reduction is split
+  // shared-memory stage addresses
+  const bool narrow = p.tile_n <= 64;
+  const uint32_t w_slot = narrow ? W_TILE_BYTES / 2 : W_TILE_BYTES;
+  const int a_stages = (kTmaA && narrow) ? A_STAGES_MAX : A_STAGES;
+  auto w_hi_ptr = [&](int st) { return ss->w_region + (uint32_t)st * w_slot; };
+  auto w_lo_ptr = [&](int st) { return ss->w_region + (uint32_t)(STAGES + st) * w_slot; };
+  auto a_ptr = [&](int st) {
+    return st < A_STAGES ? ss->a_raw[st] : ss->w_region + 2 * STAGES * (W_TILE_BYTES / 2) + (st - A_STAGES) * A_TILE_BYTES;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) {
       mbar_init(&ss->full_bar[s], NUM_A_WARPS + 1);
       mbar_init(&ss->empty_bar[s], 1);
     }
-    for (int s = 0; s < A_STAGES; s++) {
+    for (int s = 0; s < A_STAGES_MAX; s++) {
       mbar_init(&ss->a_full_bar[s], 1);
       mbar_init(&ss->a_empty_bar[s], NUM_A_WARPS);
     }
@@ -381,8 +392,9 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
   if (kTmaA && p.c4) {
     // 4-channel mode: planes of taps past the filter width are never loaded; their weights are zero,
     // so the operand only has to be finite
-    for (int i = threadIdx.x; i < A_STAGES * A_TILE_BYTES / 16; i += NUM_THREADS)
-      reinterpret_cast<float4*>(ss->a_raw[0])[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int st = 0; st < a_stages; st++)
+      for (int i = threadIdx.x; i < A_TILE_BYTES / 16; i += NUM_THREADS)
+        reinterpret_cast<float4*>(a_ptr(st))[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   if (warp == MMA_WARP) {
@@ -423,7 +435,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     for (int64_t g = 0; g < items; g++) {
       if (!mbar_wait(&ss->a_full_bar[as], aphase, ss, p.status, 11)) break;
       float4 v[8];
-      const unsigned char* tile = ss->a_raw[as] + row_off;
+      const unsigned char* tile = a_ptr(as) + row_off;
 #pragma unroll
       for (int j = 0; j < 8; j++)
         v[j] = *reinterpret_cast<const float4*>(
@@ -457,7 +469,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       __syncwarp();
       if (lane == 0) mbar_arrive(&ss->full_bar[stage]);
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
-      if (++as == A_STAGES) { as = 0; aphase ^= 1; }
+      if (++as == a_stages) { as = 0; aphase ^= 1; }
     }
   } else if (kTmaA && warp == ATMA_WARP) {
     // ===================================================================== A loader (im2col TMA)
@@ -492,12 +504,12 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
             if (lane == 0) mbar_arrive_expect_tx(&ss->a_full_bar[stage], (uint32_t)(nload * plane));
             __syncwarp(0xffu);
             if (lane < nload)
-              tma_load_im2col(ss->a_raw[stage] + lane * plane, &map_a, &ss->a_full_bar[stage], 0, cw, ch, (int)n,
+              tma_load_im2col(a_ptr(stage) + lane * plane, &map_a, &ss->a_full_bar[stage], 0, cw, ch, (int)n,
                               p.c4 == 2 ? lane : lane * p.dil_w, ky * p.dil_h);
             if (++ky == p.k_h) ky = 0;
           } else {
             mbar_arrive_expect_tx(&ss->a_full_bar[stage], (uint32_t)A_TILE_BYTES);
-            tma_load_im2col(ss->a_raw[stage], &map_a, &ss->a_full_bar[stage], c0, cw, ch, (int)n, kx * p.dil_w,
+            tma_load_im2col(a_ptr(stage), &map_a, &ss->a_full_bar[stage], c0, cw, ch, (int)n, kx * p.dil_w,
                             ky * p.dil_h);
             c0 += BLOCK_K;
             if (c0 >= p.ch_in) {
@@ -508,7 +520,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
               }
             }
           }
-          if (++stage == A_STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == a_stages) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -667,8 +679,8 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
             const int tap = kr / p.cblocks;
             kx0 = tap * p.ch_in + (kr - tap * p.cblocks) * BLOCK_K;
           }
-          tma_load_2d(ss->w_hi[stage], &map_w_hi, &ss->full_bar[stage], kx0, n0);
-          tma_load_2d(ss->w_lo[stage], &map_w_lo, &ss->full_bar[stage], kx0, n0);
+          tma_load_2d(w_hi_ptr(stage), &map_w_hi, &ss->full_bar[stage], kx0, n0);
+          tma_load_2d(w_lo_ptr(stage), &map_w_lo, &ss->full_bar[stage], kx0, n0);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -698,8 +710,8 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_hi = tmem_base + (uint32_t)(TMEM_A_COL0 + stage * 64);
           const uint32_t a_lo = a_hi + 32u;
-          const uint64_t dw_hi = make_smem_desc(smem_u32(ss->w_hi[stage]));
-          const uint64_t dw_lo = make_smem_desc(smem_u32(ss->w_lo[stage]));
+          const uint64_t dw_hi = make_smem_desc(smem_u32(w_hi_ptr(stage)));
+          const uint64_t dw_lo = make_smem_desc(smem_u32(w_lo_ptr(stage)));
 #pragma unroll
           for (int k = 0; k < BLOCK_K / 8; k++) {
             const uint64_t adv = (uint64_t)(k * 2);  // 8 tf32 = 32 bytes = 2 x 16-byte units of W

@@ -69,6 +69,7 @@ constexpr int A_TILE_BYTES = TILE_M * BLOCK_K * 4;  // 16 KB of raw fp32 A per s
 constexpr int EPI_WARP0 = 8;
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_THREADS = 16 * 32;
+constexpr int RES_L2_KBLOCKS = 4;   // residual L2 prefetch for launches with at most this many K blocks
 constexpr int SEG_KBLOCKS = 4;        // K blocks accumulated in TMEM before the partial sum is drained
 constexpr int NBUF = 2;               // TMEM segment accumulators of 128 columns
 constexpr int EPI_BUF_BYTES = 32 * 32 * 4;   // epilogue staging: 32 rows x 32 columns per buffer, 2 per warp
@@ -270,6 +271,13 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       :
       : "r"(smem_u32(smem_dst)), "l"((unsigned long long)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
+}
+// Asks L2 to fetch the box at (x, y) of a 2-D tensor map; nothing lands in shared memory.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+               :
+               : "l"((unsigned long long)map), "r"(x), "r"(y)
+               : "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
@@ -760,11 +768,23 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         mbar_arrive_expect_tx(&ss->res_bar[ew][0], chunk_bytes);
         tma_load_2d(ss->epi_buf[ew][0], &map_res, &ss->res_bar[ew][0], (int)(t0 % p.tiles_n) * p.tile_n + col0,
                     (int)((t0 / p.tiles_n) * TILE_M + q * 32));
+        if (nch == 2 && p.kblocks <= RES_L2_KBLOCKS)
+          tma_prefetch_l2_2d(&map_res, (int)(t0 % p.tiles_n) * p.tile_n + col0 + 32,
+                             (int)((t0 / p.tiles_n) * TILE_M + q * 32));
       }
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         int tile, sp, kb0, kbn;
         unit_of(p, u, tile, sp, kb0, kbn);
         nseg = (kbn + SEG_KBLOCKS - 1) / SEG_KBLOCKS;
+        // Short-K (memory-bound) launches: while this tile accumulates, L2 fetches the residual chunks of
+        // the warp's next tile.  Each staging buffer holds one chunk, so without this every chunk waits
+        // for a full trip to HBM.  Long-K launches hide that trip behind the MMAs and skip the extra requests.
+        if (use_res && lane == 0 && p.kblocks <= RES_L2_KBLOCKS && tile + (int)gridDim.x < total_tiles) {
+          const int nt = tile + (int)gridDim.x;
+          for (int c = 0; c < nch; c++)
+            tma_prefetch_l2_2d(&map_res, (int)(nt % p.tiles_n) * p.tile_n + col0 + c * 32,
+                               (int)((nt / p.tiles_n) * TILE_M + q * 32));
+        }
         const int64_t mrow0 = (int64_t)(tile / p.tiles_n) * TILE_M + q * 32;   // first row of this warp
         const int64_t store_row = mrow0 + sp * p.m_pad;   // split reductions: row block `sp` of the workspace
         const int nbase = (int)(tile % p.tiles_n) * p.tile_n + col0;

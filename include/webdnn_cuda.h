@@ -232,6 +232,24 @@ int wdc_conv_transpose2d(wdc_context* ctx, const wdc_convt_desc* d, const float*
 int wdc_instance_norm(wdc_context* ctx, const float* x, const float* scale, const float* bias, float* y,
                       int64_t batch, int64_t ch, int64_t area, double eps);
 
+/* Fused scaled-dot-product attention: y = softmax(scale * q k^T) v for every (batch, head), the [tq, tk]
+ * score matrix kept on chip (one pass over the keys with a running row maximum and sum).  Not an operator of
+ * the reference: it replaces the chain MatMul -> Mul -> Softmax -> MatMul that its graphs contain
+ * (operators/cpu/operators/standard/matmul.ts:11-111, binary7.ts:16-68, softmax.ts:15-59) and is checked
+ * against that chain.  Element (b, h, t, c) of q sits at q[b * q_sb + h * q_sh + t * q_st + c] (likewise k, v
+ * with tk rows and y with tq rows): head-split views of [batch, tokens, heads * dh] tensors need no transpose.
+ * dh is 32 or 64 (else WDC_ERR_UNSUPPORTED); strides are multiples of 4 floats, buffers 16-byte aligned. */
+typedef struct wdc_attention_desc {
+  int64_t batch, heads, tq, tk, dh;
+  int64_t q_sb, q_sh, q_st;
+  int64_t k_sb, k_sh, k_st;
+  int64_t v_sb, v_sh, v_st;
+  int64_t y_sb, y_sh, y_st;
+  float scale;
+} wdc_attention_desc;
+int wdc_attention(wdc_context* ctx, const wdc_attention_desc* d, const float* q, const float* k, const float* v,
+                  float* y);
+
 /* 8-bit weight codec of the WDN2 tensor container (core/tensorDecoder/decodeTensorEightbit.ts:36-61): `codes`
  * holds one byte per element (the inflated zlib stream, uploaded as bytes); out[i] = level[codes[i] & 127] * scale,
  * negated when bit 7 is set, bit-identical to the reference's table lookup.  Both buffers 16-byte aligned. */

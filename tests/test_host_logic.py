@@ -182,7 +182,12 @@ def test_transformer_fusions_layernorm_chain_and_matmul_bias():
     assert types.count("CudaMatMulBias") == 4 * 3 + 2 * 2 + 1 + 3
     relus = [n for n in m.graph.node if n.op_type == "CudaMatMulBias" and {a.name: a.i for a in n.attribute}["relu"]]
     assert len(relus) == 2 + 2                        # two feed-forward blocks, two hidden layers of the box head
-    assert types.count("MatMul") == 3 * 2            # scores and context of the three attention blocks stay
+    # the three attention blocks (scores, scale, softmax, context) are one node each; heads of 8 channels are
+    # not a size of the fused kernel, so the head split / merge around them stays in the graph
+    assert types.count("MatMul") == 0 and types.count("Softmax") == 0 and types.count("CudaAttention") == 3
+    att = {a.name: a for a in next(n for n in m.graph.node if n.op_type == "CudaAttention").attribute}
+    assert att["heads"].i == 0 and att["merge_heads"].i == 0 and abs(att["scale"].f - 8 ** -0.5) < 1e-7
+    assert types.count("Transpose") == 1 + 3 * 4     # token layout + (q, k, v, merge) per attention block
     ln = next(n for n in m.graph.node if n.op_type == "CudaLayerNorm")
     attrs = {a.name: a for a in ln.attribute}
     assert attrs["axis"].i == -1 and abs(attrs["epsilon"].f - 1e-5) < 1e-12 and len(ln.input) == 3
@@ -190,6 +195,36 @@ def test_transformer_fusions_layernorm_chain_and_matmul_bias():
     for n in m.graph.node:
         assert all(i in known for i in n.input), (n.op_type, n.name)
         known.update(n.output)
+
+
+def test_attention_rewrite_absorbs_the_head_split_and_merge():
+    m = zoo.detr(batch=2, size=64, d=64, heads=2, enc_layers=1, dec_layers=1, ffn=64, queries=5, classes=7, width=8,
+                 blocks=(1, 1, 1, 1))
+    model_transform(m, ["cuda", "cpu"])
+    types = [n.op_type for n in m.graph.node]
+    assert types.count("CudaAttention") == 3 and types.count("Transpose") == 1 and types.count("Reshape") == 1
+    assert not {"MatMul", "Softmax", "Mul"} & set(types)
+    for n in m.graph.node:
+        if n.op_type == "CudaAttention":
+            att = {a.name: a for a in n.attribute}
+            assert (att["batch"].i, att["heads"].i, att["head_size"].i, att["merge_heads"].i) == (2, 2, 32, 1)
+            assert abs(att["scale"].f - 32 ** -0.5) < 1e-7 and len(n.input) == 3
+    known = {vi.name for vi in m.graph.input} | {t.name for t in m.graph.initializer}
+    for n in m.graph.node:
+        assert all(i in known for i in n.input), (n.op_type, n.name)
+        known.update(n.output)
+
+
+def test_attention_with_an_outside_consumer_of_the_scores_is_left_alone():
+    from webdnn_b200.zoo import _Builder, _Transformer
+    b = _Builder(0)
+    t = _Transformer(b, 1, 64, 2, 16)
+    y = t.attention("x", "x", "x", 5, 5)
+    probs = next(n.output[0] for n in b.nodes if n.op_type == "Softmax")
+    m = b.model([("x", [1, 5, 64])], [(y, [1, 5, 64]), (probs, [2, 5, 5])])
+    model_transform(m, ["cuda", "cpu"])
+    types = [n.op_type for n in m.graph.node]
+    assert "CudaAttention" not in types and types.count("MatMul") == 2 and types.count("Softmax") == 1
 
 
 def test_layernorm_chain_with_an_outside_consumer_is_left_alone():

@@ -1,0 +1,239 @@
+// Fused scaled-dot-product attention: Y = softmax(scale * Q K^T) V per (batch, head), one pass over
+// the keys with a running row maximum and row sum, so the [tq, tk] score matrix never reaches HBM.
+//
+// The reference has no such operator: its graphs spell attention as MatMul -> Mul -> Softmax ->
+// MatMul (operators/cpu/operators/standard/matmul.ts:11-111, binary7.ts:16-68, softmax.ts:15-59),
+// which is what the parity tests compare against.  All arithmetic here is fp32 on the CUDA cores
+// (fp32 FMAs, expf): head sizes of 32 or 64 make each contraction a few hundred MFLOP, and the
+// chain it replaces is bound by the HBM traffic of the score matrix, not by arithmetic.
+//
+// One CTA of 128 threads owns 64 query rows of one head and walks the keys in chunks of 64:
+//   S phase : thread (tx = tid % 16, ty = tid / 16) computes the 8 x 4 scores of queries ty + 8 i and
+//             keys tx + 16 j from the Q and K tiles in shared memory; the row maximum and sum are
+//             reduced over the 16 lanes that share a row; exp(s - max) goes to the P tile.
+//   PV phase: thread (ox = tid % (DH / 4), oy = tid / (DH / 4)) accumulates a 4 x 4 (DH 32) or two 4 x 4
+//             (DH 64) blocks of the output from the P tile and the V tile, after rescaling by
+//             exp(old max - new max).
+// Rows of Q / K past the end read as zero, keys past tk get a score of -inf (weight 0), rows past tq
+// are not stored.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int ATT_BQ = 64;        // query rows per CTA
+constexpr int ATT_BK = 64;        // keys per chunk
+constexpr int ATT_THREADS = 128;
+constexpr int ATT_PS = 80;        // row stride of the P tile (floats): rows ty and ty + 1 land in different banks
+
+struct AttProblem {
+  const float *q, *k, *v;
+  float* y;
+  int64_t q_sb, q_sh, q_st, k_sb, k_sh, k_st, v_sb, v_sh, v_st, y_sb, y_sh, y_st;
+  int heads, tq, tk;
+  float scale;
+};
+
+template <int DH>
+__global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttProblem p) {
+  constexpr int QS = DH + 4;      // row stride of the Q and K tiles: 16-byte rows land on distinct bank groups
+  constexpr int OX = DH / 4;      // threads along the head dimension in the PV phase (each owns 4 columns)
+  constexpr int OY = ATT_THREADS / OX;   // thread rows in the PV phase
+  constexpr int OR = ATT_BQ / OY;        // query rows per thread in the PV phase (4 or 8)
+  extern __shared__ __align__(16) float smem[];
+  float* Qs = smem;                       // [BQ][QS]
+  float* Ks = Qs + ATT_BQ * QS;           // [BK][QS]
+  float* Vs = Ks + ATT_BK * QS;           // [BK][DH]
+  float* Ps = Vs + ATT_BK * DH;           // [BQ][PS]
+  float* alpha_s = Ps + ATT_BQ * ATT_PS;  // [BQ] rescale factor of the chunk, then the final row sums
+
+  const int tid = threadIdx.x;
+  const int bh = blockIdx.y;
+  const int b = bh / p.heads, h = bh - b * p.heads;
+  const int q0 = blockIdx.x * ATT_BQ;
+  const float* qb = p.q + b * p.q_sb + h * p.q_sh;
+  const float* kb = p.k + b * p.k_sb + h * p.k_sh;
+  const float* vb = p.v + b * p.v_sb + h * p.v_sh;
+  float* yb = p.y + b * p.y_sb + h * p.y_sh;
+
+  // Q tile: each row is DH floats = DH / 4 float4
+  for (int i = tid; i < ATT_BQ * (DH / 4); i += ATT_THREADS) {
+    const int r = i / (DH / 4), c4 = i - r * (DH / 4);
+    float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (q0 + r < p.tq) val = __ldg(reinterpret_cast<const float4*>(qb + (int64_t)(q0 + r) * p.q_st) + c4);
+    *reinterpret_cast<float4*>(Qs + r * QS + c4 * 4) = val;
+  }
+
+  const int tx = tid & 15, ty = tid >> 4;
+  const int ox = tid % OX, oy = tid / OX;
+  float m_run[8], l_run[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) { m_run[i] = -INFINITY; l_run[i] = 0.f; }
+  float o[OR][4];
+#pragma unroll
+  for (int r = 0; r < OR; r++)
+#pragma unroll
+    for (int c = 0; c < 4; c++) o[r][c] = 0.f;
+
+  for (int k0 = 0; k0 < p.tk; k0 += ATT_BK) {
+    __syncthreads();   // the previous chunk's tiles have been read (and Q is in place on the first pass)
+    for (int i = tid; i < ATT_BK * (DH / 4); i += ATT_THREADS) {
+      const int r = i / (DH / 4), c4 = i - r * (DH / 4);
+      float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+      if (k0 + r < p.tk) {
+        kv = __ldg(reinterpret_cast<const float4*>(kb + (int64_t)(k0 + r) * p.k_st) + c4);
+        vv = __ldg(reinterpret_cast<const float4*>(vb + (int64_t)(k0 + r) * p.v_st) + c4);
+      }
+      *reinterpret_cast<float4*>(Ks + r * QS + c4 * 4) = kv;
+      *reinterpret_cast<float4*>(Vs + r * DH + c4 * 4) = vv;
+    }
+    __syncthreads();
+
+    // ---- S phase
+    float s[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) s[i][j] = 0.f;
+#pragma unroll
+    for (int d = 0; d < DH; d += 4) {
+      float4 kk[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) kk[j] = *reinterpret_cast<const float4*>(Ks + (tx + 16 * j) * QS + d);
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const float4 qq = *reinterpret_cast<const float4*>(Qs + (ty + 8 * i) * QS + d);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          s[i][j] = fmaf(qq.x, kk[j].x, s[i][j]);
+          s[i][j] = fmaf(qq.y, kk[j].y, s[i][j]);
+          s[i][j] = fmaf(qq.z, kk[j].z, s[i][j]);
+          s[i][j] = fmaf(qq.w, kk[j].w, s[i][j]);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        s[i][j] = (k0 + tx + 16 * j < p.tk) ? s[i][j] * p.scale : -INFINITY;
+        mx = fmaxf(mx, s[i][j]);
+      }
+#pragma unroll
+      for (int w = 1; w < 16; w <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, w));
+      const float m_new = fmaxf(m_run[i], mx);
+      // every chunk holds at least one real key, so m_new is finite unless the scores themselves are not
+      const float a = expf(m_run[i] - m_new);
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float e = expf(s[i][j] - m_new);
+        sum += e;
+        Ps[(ty + 8 * i) * ATT_PS + tx + 16 * j] = e;
+      }
+#pragma unroll
+      for (int w = 1; w < 16; w <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
+      l_run[i] = l_run[i] * a + sum;
+      m_run[i] = m_new;
+      if (tx == 0) alpha_s[ty + 8 * i] = a;
+    }
+    __syncthreads();
+
+    // ---- PV phase
+#pragma unroll
+    for (int r = 0; r < OR; r++) {
+      const float a = alpha_s[oy * OR + r];
+#pragma unroll
+      for (int c = 0; c < 4; c++) o[r][c] *= a;
+    }
+#pragma unroll 4
+    for (int kk4 = 0; kk4 < ATT_BK; kk4 += 4) {
+      float4 vv[4];
+#pragma unroll
+      for (int t = 0; t < 4; t++) vv[t] = *reinterpret_cast<const float4*>(Vs + (kk4 + t) * DH + ox * 4);
+#pragma unroll
+      for (int r = 0; r < OR; r++) {
+        const float4 pp = *reinterpret_cast<const float4*>(Ps + (oy * OR + r) * ATT_PS + kk4);
+        o[r][0] = fmaf(pp.x, vv[0].x, o[r][0]); o[r][1] = fmaf(pp.x, vv[0].y, o[r][1]);
+        o[r][2] = fmaf(pp.x, vv[0].z, o[r][2]); o[r][3] = fmaf(pp.x, vv[0].w, o[r][3]);
+        o[r][0] = fmaf(pp.y, vv[1].x, o[r][0]); o[r][1] = fmaf(pp.y, vv[1].y, o[r][1]);
+        o[r][2] = fmaf(pp.y, vv[1].z, o[r][2]); o[r][3] = fmaf(pp.y, vv[1].w, o[r][3]);
+        o[r][0] = fmaf(pp.z, vv[2].x, o[r][0]); o[r][1] = fmaf(pp.z, vv[2].y, o[r][1]);
+        o[r][2] = fmaf(pp.z, vv[2].z, o[r][2]); o[r][3] = fmaf(pp.z, vv[2].w, o[r][3]);
+        o[r][0] = fmaf(pp.w, vv[3].x, o[r][0]); o[r][1] = fmaf(pp.w, vv[3].y, o[r][1]);
+        o[r][2] = fmaf(pp.w, vv[3].z, o[r][2]); o[r][3] = fmaf(pp.w, vv[3].w, o[r][3]);
+      }
+    }
+  }
+
+  // final row sums to the PV threads
+  __syncthreads();
+  if (tx == 0) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) alpha_s[ty + 8 * i] = l_run[i];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < OR; r++) {
+    const int row = q0 + oy * OR + r;
+    if (row < p.tq) {
+      const float l = alpha_s[oy * OR + r];
+      *reinterpret_cast<float4*>(yb + (int64_t)row * p.y_st + ox * 4) =
+          make_float4(o[r][0] / l, o[r][1] / l, o[r][2] / l, o[r][3] / l);
+    }
+  }
+}
+
+template <int DH>
+size_t attention_smem() {
+  return sizeof(float) * (size_t)(ATT_BQ * (DH + 4) + ATT_BK * (DH + 4) + ATT_BK * DH + ATT_BQ * ATT_PS + ATT_BQ);
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+extern "C" int wdc_attention(wdc_context* ctx, const wdc_attention_desc* d, const float* q, const float* k,
+                             const float* v, float* y) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_attention: null context");
+  wdc_note_write(ctx, y);
+  WDC_REQUIRE(ctx, d && q && k && v && y, "wdc_attention: null argument");
+  WDC_REQUIRE(ctx, d->batch > 0 && d->heads > 0 && d->tq > 0 && d->tk > 0, "wdc_attention: bad shape");
+  if (d->dh != 32 && d->dh != 64)
+    return wdc_fail(ctx, WDC_ERR_UNSUPPORTED, "wdc_attention: head size %lld (supported: 32, 64)", (long long)d->dh);
+  WDC_REQUIRE(ctx, d->batch * d->heads <= 65535 && d->tq < (1ll << 31) - ATT_BQ && d->tk < (1ll << 31) - ATT_BK,
+              "wdc_attention: shape exceeds the grid");
+  // rows are read and written as float4
+  const int64_t strides[12] = {d->q_sb, d->q_sh, d->q_st, d->k_sb, d->k_sh, d->k_st,
+                               d->v_sb, d->v_sh, d->v_st, d->y_sb, d->y_sh, d->y_st};
+  for (int i = 0; i < 12; i++)
+    WDC_REQUIRE(ctx, strides[i] >= 0 && strides[i] % 4 == 0, "wdc_attention: strides must be non-negative multiples of 4");
+  WDC_REQUIRE(ctx, aligned16(q) && aligned16(k) && aligned16(v) && aligned16(y),
+              "wdc_attention: buffers must be 16-byte aligned");
+  DeviceGuard g(ctx->device);
+  AttProblem p;
+  p.q = q; p.k = k; p.v = v; p.y = y;
+  p.q_sb = d->q_sb; p.q_sh = d->q_sh; p.q_st = d->q_st;
+  p.k_sb = d->k_sb; p.k_sh = d->k_sh; p.k_st = d->k_st;
+  p.v_sb = d->v_sb; p.v_sh = d->v_sh; p.v_st = d->v_st;
+  p.y_sb = d->y_sb; p.y_sh = d->y_sh; p.y_st = d->y_st;
+  p.heads = (int)d->heads; p.tq = (int)d->tq; p.tk = (int)d->tk;
+  p.scale = d->scale;
+  dim3 grid((unsigned)((d->tq + ATT_BQ - 1) / ATT_BQ), (unsigned)(d->batch * d->heads));
+  ProfScope prof(ctx, 4.0 * (double)d->batch * d->heads * d->tq * d->tk * d->dh);
+  if (d->dh == 32) {
+    attention_kernel<32><<<grid, ATT_THREADS, attention_smem<32>(), ctx->stream>>>(p);   // 47 KB: no opt-in needed
+  } else {
+    static bool opted_in[64] = {};   // per device: more than 48 KB of dynamic shared memory needs the attribute
+    WDC_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, "wdc_attention: device index out of range");
+    if (!opted_in[ctx->device]) {
+      WDC_CUDA(ctx, cudaFuncSetAttribute(attention_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)attention_smem<64>()));
+      opted_in[ctx->device] = true;
+    }
+    attention_kernel<64><<<grid, ATT_THREADS, attention_smem<64>(), ctx->stream>>>(p);
+  }
+  return wdc_check_launch(ctx, "attention_kernel");
+}

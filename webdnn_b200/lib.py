@@ -56,6 +56,11 @@ class ConvTransposeDesc(Structure):
                                        "out_h", "out_w", "stride_h", "stride_w", "pad_t", "pad_l", "dil_h", "dil_w")]
 
 
+class AttentionDesc(Structure):
+    _fields_ = [(n, c_int64) for n in ("batch", "heads", "tq", "tk", "dh", "q_sb", "q_sh", "q_st", "k_sb", "k_sh",
+                                       "k_st", "v_sb", "v_sh", "v_st", "y_sb", "y_sh", "y_st")] + [("scale", c_float)]
+
+
 class PoolDesc(Structure):
     _fields_ = [(n, c_int64) for n in (
         "batch", "ch", "in_h", "in_w", "out_h", "out_w", "k_h", "k_w", "stride_h", "stride_w",
@@ -79,6 +84,7 @@ SIGNATURES = {
     "wdc_conv_transpose2d": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "wdc_instance_norm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                   ctypes.c_double]),
+    "wdc_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "wdc_decode_eightbit": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_float]),
     "wdc_capture_begin": (c_int, [c_void_p]),
     "wdc_capture_end": (c_int, [c_void_p, POINTER(c_void_p)]),

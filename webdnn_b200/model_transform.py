@@ -13,6 +13,10 @@ unchanged:
   (the bias and the Relu move into the contraction's epilogue).
 * the decomposed LayerNormalization chain over the last axis (``ReduceMean``, ``Sub``, ``Mul``/``Pow``,
   ``ReduceMean``, ``Add`` epsilon, ``Sqrt``, ``Div``, ``Mul`` gamma, ``Add`` beta) -> ``CudaLayerNorm``.
+* ``MatMul``(q, ``Transpose``(k)) [-> ``Mul``/``Div`` by a constant scalar] -> ``Softmax`` over the last
+  axis -> ``MatMul``(., v) on rank-3 tensors -> ``CudaAttention``; the head split in front of q, k, v
+  (``Reshape`` [b, t, h, c] -> ``Transpose`` 0,2,1,3 -> ``Reshape`` [b*h, t, c]) and the head merge behind the
+  result are absorbed as strides when their shapes are constants.
 
 The private op types are registered like a custom operator (``example/custom_operator/twice.ts``),
 the same way the offline WebGL passes rename ``op_type`` to ``ConvReshapeWebGL`` / ``MatMulNT141``.
@@ -146,14 +150,128 @@ def _match_layernorm(mean_node: Node, inits, consumers, graph_outputs, removed):
     return [mean_node, sub, sq, var, add, sqrt, div, mul, addb], fused
 
 
+ATTENTION_HEAD_SIZES = (32, 64)   # head sizes of the fused kernel (wdc_attention)
+
+
+def _const_ints(name, inits):
+    t = inits.get(name)
+    if t is None:
+        return None
+    return [int(v) for v in np.asarray(t.array).reshape(-1)]
+
+
+def _perm(n: Node):
+    a = [a for a in n.attribute if a.name == "perm"]
+    return list(a[0].ints) if a else None
+
+
+def _match_attention(softmax: Node, inits, consumers, producers, graph_outputs, removed):
+    """Matches scaled-dot-product attention around a last-axis ``Softmax``; returns (nodes to drop,
+    last node of the chain, fused node) or None.  Every intermediate value has exactly one consumer
+    and is not a graph output."""
+    axis = [a for a in softmax.attribute if a.name == "axis"]
+    if not axis or axis[0].i != -1 or len(softmax.input) != 1:
+        return None   # the default axis flattens instead (opset < 13); -1 means the same in every opset
+
+    def sole(tensor):
+        c = [x for x in consumers.get(tensor, []) if id(x) not in removed]
+        return c[0] if len(c) == 1 and tensor not in graph_outputs else None
+
+    def prod(tensor):
+        n = producers.get(tensor)
+        return n if n is not None and id(n) not in removed and sole(tensor) is not None else None
+
+    chain = [softmax]
+    scale = 1.0
+    up = prod(softmax.input[0])
+    if up is not None and up.op_type in ("Mul", "Div") and len(up.input) == 2:
+        a, b = up.input
+        const = b if b in inits else (a if a in inits and up.op_type == "Mul" else None)
+        if const is None or inits[const].array.size != 1 or inits[const].data_type != FLOAT:
+            return None
+        c = float(np.float32(np.asarray(inits[const].array).reshape(-1)[0]))
+        if up.op_type == "Div":
+            if c == 0.0:
+                return None
+            c = float(np.float32(1.0 / c))
+        scale = c
+        chain.append(up)
+        up = prod(a if const == b else b)
+    if up is None or up.op_type != "MatMul" or len(up.input) != 2:
+        return None
+    qk = up
+    chain.append(qk)
+    kt = prod(qk.input[1])
+    if kt is None or kt.op_type != "Transpose" or _perm(kt) != [0, 2, 1]:
+        return None
+    chain.append(kt)
+    pv = sole(softmax.output[0])
+    if pv is None or pv.op_type != "MatMul" or len(pv.input) != 2 or pv.input[0] != softmax.output[0]:
+        return None
+    chain.append(pv)
+    srcs = {"q": qk.input[0], "k": kt.input[0], "v": pv.input[1]}
+    if any(t in inits for t in srcs.values()):
+        return None
+
+    # head split in front of an operand: Reshape [b, t, h, c] -> Transpose 0,2,1,3 -> Reshape [b*h, t, c]
+    split = {}
+    for key, t in list(srcs.items()):
+        r2 = prod(t)
+        if r2 is None or r2.op_type != "Reshape" or len(r2.input) != 2:
+            continue
+        tr = prod(r2.input[0])
+        if tr is None or tr.op_type != "Transpose" or _perm(tr) != [0, 2, 1, 3]:
+            continue
+        r1 = prod(tr.input[0])
+        if r1 is None or r1.op_type != "Reshape" or len(r1.input) != 2:
+            continue
+        s1, s2 = _const_ints(r1.input[1], inits), _const_ints(r2.input[1], inits)
+        if (s1 is None or s2 is None or len(s1) != 4 or len(s2) != 3 or min(s1) <= 0
+                or s2 != [s1[0] * s1[2], s1[1], s1[3]] or s1[3] not in ATTENTION_HEAD_SIZES):
+            continue
+        split[key] = (s1, [r1, tr, r2])
+    # the three operands must agree on (batch, heads) to be read through strides
+    if (len(split) == 3 and len({(v[0][0], v[0][2], v[0][3]) for v in split.values()}) == 1
+            and split["k"][0][1] == split["v"][0][1]):
+        for key in ("q", "k", "v"):
+            srcs[key] = split[key][1][0].input[0]
+            chain.extend(split[key][1])
+        b, _, h, dh = split["q"][0]
+    else:
+        split = {}
+        b = h = dh = 0
+
+    out = pv.output[0]
+    last = pv
+    merged = 0
+    if split:
+        # head merge behind the result: Reshape [b, h, t, c] -> Transpose 0,2,1,3 -> Reshape [b, t, h*c]
+        r1 = sole(out)
+        tr = sole(r1.output[0]) if r1 is not None and r1.op_type == "Reshape" and len(r1.input) == 2 else None
+        r2 = sole(tr.output[0]) if tr is not None and tr.op_type == "Transpose" and _perm(tr) == [0, 2, 1, 3] else None
+        if r2 is not None and r2.op_type == "Reshape" and len(r2.input) == 2:
+            s1, s2 = _const_ints(r1.input[1], inits), _const_ints(r2.input[1], inits)
+            tq, c = split["q"][0][1], split["q"][0][3]
+            if s1 == [b, h, tq, c] and s2 == [b, tq, h * c]:
+                chain.extend([r1, tr, r2])
+                out, last, merged = r2.output[0], r2, 1
+    attrs = [make_attr("scale", scale), make_attr("batch", b), make_attr("heads", h), make_attr("head_size", dh),
+             make_attr("merge_heads", merged)]
+    fused = Node("CudaAttention", [srcs["q"], srcs["k"], srcs["v"]], [out], qk.name or qk.output[0], attrs)
+    return chain, last, fused
+
+
 def _fuse_cuda(model: Model) -> None:
     g = model.graph
     inits = {t.name: t for t in g.initializer}
     graph_outputs = {vi.name for vi in g.output}
     consumers: Dict[str, List[Node]] = {}
+    producers: Dict[str, Node] = {}
     for n in g.node:
         for i in n.input:
             consumers.setdefault(i, []).append(n)
+        for o in n.output:
+            producers[o] = n
 
     removed = set()
 
@@ -164,6 +282,15 @@ def _fuse_cuda(model: Model) -> None:
         return None
 
     replace_at: Dict[int, Node] = {}  # id(last node of chain) -> fused node
+    # attention first: its matcher looks at plain MatMul / Reshape / Transpose nodes on both sides
+    for n in g.node:
+        if n.op_type == "Softmax" and id(n) not in removed:
+            m = _match_attention(n, inits, consumers, producers, graph_outputs, removed)
+            if m is not None:
+                chain, last, fused = m
+                for c in chain:
+                    removed.add(id(c))
+                replace_at[id(last)] = fused
     for n in g.node:
         if id(n) in removed:
             continue

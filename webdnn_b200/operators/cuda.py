@@ -20,7 +20,7 @@ from typing import List
 import numpy as np
 
 from ..backend import NP_DTYPE, CPUTensor, CudaTensor, WebDNNCudaContext
-from ..lib import BINARY_OPS, REDUCE_KINDS, UNARY_OPS, ConvDesc, ConvTransposeDesc, GemmDesc, PoolDesc
+from ..lib import BINARY_OPS, REDUCE_KINDS, UNARY_OPS, AttentionDesc, ConvDesc, ConvTransposeDesc, GemmDesc, PoolDesc
 from ..operator_table import OperatorEntry
 from . import base
 from .base import (OperatorImpl, array_prod, broadcast_multi, broadcast_uni, get_attr_float, get_attr_int,
@@ -247,6 +247,81 @@ class CudaMatMulBias(OperatorImpl):
             context.gemm(d, a, w, b, y)
         if a is not inputs[0]:
             a.dispose()
+        return [y]
+
+
+class CudaAttention(OperatorImpl):
+    """softmax(scale * Q K^T) V as one launch (load-time rewrite of MatMul -> Mul -> Softmax -> MatMul;
+    matmul.ts:11-111, binary7.ts:16-68, softmax.ts:15-59 give the reference semantics).
+
+    Inputs are either rank-3 [batch*heads, tokens, c] tensors (``heads`` attribute 0), or the tensors
+    in front of the head split, [batch, tokens, heads*c] in memory, read through strides.  With
+    ``merge_heads`` the result is written as [batch, tq, heads*c], else as [batch*heads, tq, c]."""
+
+    def __init__(self):
+        super().__init__("cuda")
+
+    def initialize(self, attribute):
+        self.scale = get_attr_float(attribute, "scale", 1.0)
+        self.batch = get_attr_int(attribute, "batch", 0)
+        self.heads = get_attr_int(attribute, "heads", 0)
+        self.head_size = get_attr_int(attribute, "head_size", 0)
+        self.merge = get_attr_int(attribute, "merge_heads", 0) != 0
+
+    def run(self, context, inputs, n_outputs):
+        context.asserts_cuda_tensor_array(inputs)
+        q, k, v = (context.canonical(t) for t in inputs)
+        owned = [t for t, o in zip((q, k, v), inputs) if t is not o]
+        if any(t.data_type != "float32" for t in (q, k, v)):
+            raise TypeError("only float32 is supported")
+        if self.heads:
+            b, h = self.batch, self.heads
+            if k.length != v.length:
+                raise ValueError("CudaAttention: operand sizes do not match the head split")
+            c = self.head_size
+            if c <= 0 or q.length % (b * h * c) or k.length % (b * h * c):
+                raise ValueError("CudaAttention: operand sizes do not match the head split")
+            tq, tk = q.length // (b * h * c), k.length // (b * h * c)
+            sq = (tq * h * c, c, h * c)
+            sk = (tk * h * c, c, h * c)
+        else:
+            if q.ndim != 3 or k.ndim != 3 or v.ndim != 3:
+                raise ValueError("CudaAttention: operands must have rank 3")
+            b, h = q.dims[0], 1
+            tq, c = q.dims[1], q.dims[2]
+            tk = k.dims[1]
+            if k.dims != [b, tk, c] or v.dims != [b, tk, c]:
+                raise ValueError("CudaAttention: operand shapes do not match")
+            sq = (tq * c, 0, c)
+            sk = (tk * c, 0, c)
+        if self.merge:
+            y = context.empty_tensor([b, tq, h * c], "float32")
+            sy = (tq * h * c, c, h * c)
+        else:
+            y = context.empty_tensor([b * h, tq, c], "float32")
+            sy = (h * tq * c, tq * c, c)
+        if y.length:
+            if c in (32, 64):
+                d = AttentionDesc(batch=b, heads=h, tq=tq, tk=tk, dh=c,
+                                  q_sb=sq[0], q_sh=sq[1], q_st=sq[2], k_sb=sk[0], k_sh=sk[1], k_st=sk[2],
+                                  v_sb=sk[0], v_sh=sk[1], v_st=sk[2], y_sb=sy[0], y_sh=sy[1], y_st=sy[2],
+                                  scale=self.scale)
+                context._call("wdc_attention", byref(d), _p(q), _p(k), _p(v), _p(y))
+            elif self.heads:
+                raise ValueError("CudaAttention: a head split is only absorbed for head sizes 32 and 64")
+            else:
+                # other head sizes: the same chain as three launches (the scale rides on the first contraction)
+                sc = context.empty_tensor([b, tq, tk], "float32")
+                context.gemm(GemmDesc(batch=b, m=tq, n=tk, k=c, sab=tq * c, sa0=c, sa1=1, sbb=tk * c, sb0=1, sb1=c,
+                                      sc0=0, sc1=0, alpha=self.scale, beta=0.0, relu=0), q, k, None, sc)
+                pr = context.empty_tensor([b, tq, tk], "float32")
+                context._call("wdc_softmax", _p(sc), _p(pr), b * tq, tk)
+                sc.dispose()
+                context.gemm(GemmDesc(batch=b, m=tq, n=c, k=tk, sab=tq * tk, sa0=tk, sa1=1, sbb=tk * c, sb0=c, sb1=1,
+                                      sc0=0, sc1=0, alpha=1.0, beta=0.0, relu=0), pr, v, None, y)
+                pr.dispose()
+        for t in owned:
+            t.dispose()
         return [y]
 
 
@@ -977,6 +1052,7 @@ def get_op_entries() -> List[OperatorEntry]:
         E("Gemm", 1, None, "cuda", CudaGemm),
         E("CudaGemmRelu", 1, None, "cuda", lambda: CudaGemm(relu=True)),
         E("CudaMatMulBias", 1, None, "cuda", CudaMatMulBias),
+        E("CudaAttention", 1, None, "cuda", CudaAttention),
         E("MatMul", 1, None, "cuda", CudaMatMul),
         E("Conv", 1, None, "cuda", CudaConv),
         E("CudaConvFused", 1, None, "cuda", lambda: CudaConv(fused=True)),

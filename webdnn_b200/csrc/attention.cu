@@ -35,18 +35,23 @@ struct AttProblem {
   float scale;
 };
 
+// CTAs per SM the register and shared-memory budgets are sized for: a launch of a few hundred equal CTAs
+// (640 for 64 heads of 625 queries) must be resident at once, or a second partial wave nearly doubles its time.
 template <int DH>
-__global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttProblem p) {
+constexpr int att_min_ctas() { return DH == 32 ? 4 : 3; }
+
+template <int DH>
+__global__ void __launch_bounds__(ATT_THREADS, att_min_ctas<DH>()) attention_kernel(const AttProblem p) {
   constexpr int QS = DH + 4;      // row stride of the Q and K tiles: 16-byte rows land on distinct bank groups
   constexpr int OX = DH / 4;      // threads along the head dimension in the PV phase (each owns 4 columns)
   constexpr int OY = ATT_THREADS / OX;   // thread rows in the PV phase
   constexpr int OR = ATT_BQ / OY;        // query rows per thread in the PV phase (4 or 8)
   extern __shared__ __align__(16) float smem[];
   float* Qs = smem;                       // [BQ][QS]
-  float* Ks = Qs + ATT_BQ * QS;           // [BK][QS]
-  float* Vs = Ks + ATT_BK * QS;           // [BK][DH]
-  float* Ps = Vs + ATT_BK * DH;           // [BQ][PS]
-  float* alpha_s = Ps + ATT_BQ * ATT_PS;  // [BQ] rescale factor of the chunk, then the final row sums
+  float* Vs = Qs + ATT_BQ * QS;           // [BK][DH]
+  float* alpha_s = Vs + ATT_BK * DH;      // [BQ] rescale factor of the chunk, then the final row sums
+  float* Ks = alpha_s + ATT_BQ;           // [BK][QS] during the S phase ...
+  float* Ps = Ks;                         // ... [BQ][PS] during the PV phase (same memory)
 
   const int tid = threadIdx.x;
   const int bh = blockIdx.y;
@@ -113,6 +118,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttProblem
         }
       }
     }
+    __syncthreads();   // every thread has read the K tile: the P tile may overwrite it
 #pragma unroll
     for (int i = 0; i < 8; i++) {
       float mx = -INFINITY;
@@ -188,7 +194,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttProblem
 
 template <int DH>
 size_t attention_smem() {
-  return sizeof(float) * (size_t)(ATT_BQ * (DH + 4) + ATT_BK * (DH + 4) + ATT_BK * DH + ATT_BQ * ATT_PS + ATT_BQ);
+  const int kp = ATT_BK * (DH + 4) > ATT_BQ * ATT_PS ? ATT_BK * (DH + 4) : ATT_BQ * ATT_PS;   // K and P tiles share
+  return sizeof(float) * (size_t)(ATT_BQ * (DH + 4) + ATT_BK * DH + ATT_BQ + kp);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -224,7 +231,7 @@ extern "C" int wdc_attention(wdc_context* ctx, const wdc_attention_desc* d, cons
   dim3 grid((unsigned)((d->tq + ATT_BQ - 1) / ATT_BQ), (unsigned)(d->batch * d->heads));
   ProfScope prof(ctx, 4.0 * (double)d->batch * d->heads * d->tq * d->tk * d->dh);
   if (d->dh == 32) {
-    attention_kernel<32><<<grid, ATT_THREADS, attention_smem<32>(), ctx->stream>>>(p);   // 47 KB: no opt-in needed
+    attention_kernel<32><<<grid, ATT_THREADS, attention_smem<32>(), ctx->stream>>>(p);   // 38 KB: no opt-in needed
   } else {
     static bool opted_in[64] = {};   // per device: more than 48 KB of dynamic shared memory needs the attribute
     WDC_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, "wdc_attention: device index out of range");

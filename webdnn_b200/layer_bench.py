@@ -1,6 +1,8 @@
-"""Times wdc_conv2d on single convolution shapes (the ResNet-50 layers at a given batch).
+"""Times wdc_conv2d on single convolution shapes (the ResNet-50 layers at a given batch), or
+wdc_attention on the attention shapes of the DETR-style configuration.
 
     python -m webdnn_b200.layer_bench [--batch 256] [--only l4.c2,l1.c3] [--reps 5]
+    python -m webdnn_b200.layer_bench --attention [--batch 8] [--only enc] [--reps 5]
 
 Prints, per layer, the mean device time of the contraction launch (CUDA events recorded by the
 library around each launch), algorithmic TFLOP/s, the tensor-issue rate (3 MMAs per algorithmic
@@ -14,7 +16,9 @@ import argparse
 import numpy as np
 
 from .backend import CPUTensor, WebDNNCudaContext
-from .lib import ConvDesc
+from ctypes import byref, c_void_p
+
+from .lib import AttentionDesc, ConvDesc
 
 # name, ch_in, ch_out, input size, kernel, stride, pad, residual, occurrences in ResNet-50 v1.5
 LAYERS = [
@@ -45,9 +49,47 @@ LAYERS = [
 ]
 
 
+# name, query tokens, key tokens, heads, head size, occurrences in the 6 + 6 layer transformer (800x800 input)
+ATTENTION = [
+    ("enc self 625x625", 625, 625, 8, 32, 6),
+    ("dec cross 100x625", 100, 625, 8, 32, 6),
+    ("dec self 100x100", 100, 100, 8, 32, 6),
+]
+
+
+def attention_bench(ctx: WebDNNCudaContext, batch: int, only, reps: int) -> None:
+    rng = np.random.default_rng(0)
+    for name, tq, tk, h, c, count in ATTENTION:
+        if only and not any(name.startswith(o) for o in only):
+            continue
+        dm = h * c
+        q, k, v = (ctx.move_tensor(CPUTensor.from_array(rng.standard_normal((batch, t, dm)).astype(np.float32)))
+                   for t in (tq, tk, tk))
+        y = ctx.empty_tensor([batch, tq, dm])
+        d = AttentionDesc(batch=batch, heads=h, tq=tq, tk=tk, dh=c, q_sb=tq * dm, q_sh=c, q_st=dm, k_sb=tk * dm,
+                          k_sh=c, k_st=dm, v_sb=tk * dm, v_sh=c, v_st=dm, y_sb=tq * dm, y_sh=c, y_st=dm,
+                          scale=c ** -0.5)
+        call = lambda: ctx._call("wdc_attention", byref(d), *(c_void_p(t.ptr) for t in (q, k, v, y)))
+        for _ in range(2):
+            call()
+        ctx.profile_enable(True)
+        for _ in range(reps):
+            call()
+        ms, _, fl = ctx.profile_read()
+        ctx.profile_enable(False)
+        ms /= reps
+        flops = fl / reps
+        nbytes = 4 * (q.length + k.length + v.length + y.length)
+        print(f"{name:22s} batch {batch}: {ms * 1e3:8.1f} us  {flops / ms / 1e9:6.2f} TFLOP/s fp32 algorithmic  "
+              f"{nbytes / 1e6:6.1f} MB of operands  x{count}")
+        for t in (q, k, v, y):
+            t.dispose()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--batch", type=int, default=256)
+    ap.add_argument("--batch", type=int, default=0, help="default 256 (convolutions) or 8 (attention)")
+    ap.add_argument("--attention", action="store_true")
     ap.add_argument("--only", default="")
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--tf32-peak", type=float, default=752.0, help="TFLOP/s used for the issue-rate column")
@@ -55,7 +97,11 @@ def main() -> None:
     only = [s for s in args.only.split(",") if s]
     ctx = WebDNNCudaContext()
     ctx.initialize()
-    B = args.batch
+    if args.attention:
+        attention_bench(ctx, args.batch or 8, only, args.reps)
+        ctx.close()
+        return
+    B = args.batch or 256
     total = 0.0
     weighted = 0.0
     for name, cin, cout, hw, k, s, pad, res, count in LAYERS:

@@ -33,7 +33,7 @@ if ROOT not in sys.path:
 METRIC = "resnet50_fp32_inference_images_per_sec"
 # dram__bytes_read.sum + dram__bytes_write.sum of the 54 tc_igemm launches of one batch-256 step, divided by 54
 # (profiles/resnet50_b256_contraction_dram_traffic.md); the algorithmic bytes of the same launches are 28.06 GB.
-CONTRACTION_DRAM_BYTES_PER_LAUNCH_B256 = 25.180e9 / 54
+CONTRACTION_DRAM_BYTES_PER_LAUNCH_B256 = 25.166e9 / 54
 
 
 class ClockSampler:

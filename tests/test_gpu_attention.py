@@ -48,6 +48,27 @@ def test_contiguous_heads_match_the_operator_chain(cuda_context, bh, tq, tk, dh)
         t.dispose()
 
 
+def test_full_size_encoder_block_through_head_strides(cuda_context):
+    """The encoder self-attention of the DETR-style configuration at its full size (batch 8, 8 heads of 32 channels,
+    625 tokens), operands laid out [batch, tokens, heads * 32] and read through strides, result written merged."""
+    b, h, t, c = 8, 8, 625, 32
+    rng = np.random.default_rng(5)
+    q, k, v = (rng.standard_normal((b, t, h * c)).astype(np.float32) for _ in range(3))
+    scale = float(np.float32(c ** -0.5))
+    heads = lambda a: np.ascontiguousarray(a.reshape(b, t, h, c).transpose(0, 2, 1, 3).reshape(b * h, t, c))
+    want = _oracle_chain(heads(q), heads(k), heads(v), scale).reshape(b, h, t, c).transpose(0, 2, 1, 3).reshape(b, t, h * c)
+    ctx = cuda_context
+    dq, dk, dv = (_device(ctx, a) for a in (q, k, v))
+    y = ctx.empty_tensor([b, t, h * c], "float32")
+    st = dict(sb=t * h * c, sh=c, st=h * c)
+    d = AttentionDesc(batch=b, heads=h, tq=t, tk=t, dh=c, scale=scale,
+                      **{f"{n}_{key}": val for n in "qkvy" for key, val in st.items()})
+    ctx._call("wdc_attention", byref(d), *(c_void_p(x.ptr) for x in (dq, dk, dv, y)))
+    assert max_err_rel_linf(y.get_data().reshape(b, t, h * c), want) <= TOL
+    for x in (dq, dk, dv, y):
+        x.dispose()
+
+
 def test_sharp_softmax_rows_and_large_scores(cuda_context):
     """Scores spread over hundreds of units: the running maximum has to move between key chunks."""
     rng = np.random.default_rng(7)

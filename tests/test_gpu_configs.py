@@ -262,6 +262,24 @@ def test_config3_full_batch_properties(cuda_context):
     assert max_err_rel_linf(got[:4], small) <= 1e-5
 
 
+def test_config5_full_size_properties(cuda_context):
+    """The DETR-style network at its full size (800x800 input, 625 tokens, d = 256, 8 heads, 6 + 6 layers), where the
+    CPU oracle would need minutes: the batch holds the same image twice, so both rows of each output must agree
+    (images are independent: convolution rows, attention heads and LayerNorm rows never mix batch entries), boxes
+    come out of a Sigmoid, and the whole graph runs on the device with one node per attention block."""
+    img = zoo.make_input((1, 3, 800, 800))
+    model = zoo.detr(batch=2, size=800)
+    (logits, boxes), r = run_cuda(model, [np.concatenate([img, img])], cuda_context, return_runner=True)
+    kinds = [k for _, k, _ in r.node_backends]
+    assert all(b == "cuda" for _, _, b in r.node_backends)
+    assert kinds.count("CudaAttention") == 18 and "Softmax" not in kinds and "MatMul" not in kinds
+    r.dispose()
+    assert logits.shape == (2, 100, 92) and boxes.shape == (2, 100, 4)
+    assert np.isfinite(logits).all() and (boxes > 0).all() and (boxes < 1).all()
+    assert max_err_rel_linf(logits[1], logits[0]) <= 1e-5 and max_err_rel_linf(boxes[1], boxes[0]) <= 1e-5
+    assert np.ptp(logits[0], axis=0).max() > 0          # the queries do not collapse to one answer
+
+
 def test_config2_full_size_scaling_is_exact(cuda_context):
     """Convolution is linear: with bias-free weights, doubling the input doubles every product of the
     3xTF32 split exactly (powers of two do not touch mantissas), so the output doubles bit for bit."""

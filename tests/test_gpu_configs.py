@@ -335,3 +335,26 @@ def test_captured_run_of_a_transformer_graph(cuda_context):
     finally:
         cap.dispose()
     r.dispose()
+
+
+@pytest.mark.parametrize("res_shape,rows", [((2, 40, 48), 80), ((1, 40, 48), 80), ((2, 1, 48), 80), ((3, 7, 48), 21)])
+def test_linear_layer_with_residual_sum(cuda_context, res_shape, rows):
+    """x + (MatMul(a, W) + b): one launch when the residual has the result's shape (bias and residual both in the
+    contraction's epilogue), the reference's separate broadcasting Add otherwise."""
+    from webdnn_b200.zoo import _Builder
+    b = _Builder(5)
+    lead = (2, 40) if rows == 80 else (3, 7)
+    w = b.init("w", b.he((64, 48), 64))
+    bias = b.init("bias", b.bias(48))
+    lin = b.node("Add", [b.node("MatMul", ["a", w])[0], bias])[0]
+    y = b.node("Add", ["r", lin])[0]
+    out_shape = list(np.broadcast_shapes(lead + (48,), res_shape))
+    model = b.model([("a", list(lead) + [64]), ("r", list(res_shape))], [(y, out_shape)])
+    rng = np.random.default_rng(2)
+    xs = [rng.standard_normal(lead + (64,)).astype(np.float32), rng.standard_normal(res_shape).astype(np.float32)]
+    want = ref_runner.run_model(model, xs)
+    got, r = run_cuda(model, xs, cuda_context, return_runner=True)
+    assert [k for _, k, _ in r.node_backends] == ["CudaMatMulBias"]
+    r.dispose()
+    assert list(got[0].shape) == out_shape == list(want[0].shape)
+    assert max_err_rel_linf(got[0], want[0]) <= 1e-4

@@ -182,6 +182,11 @@ def test_transformer_fusions_layernorm_chain_and_matmul_bias():
     assert types.count("CudaMatMulBias") == 4 * 3 + 2 * 2 + 1 + 3
     relus = [n for n in m.graph.node if n.op_type == "CudaMatMulBias" and {a.name: a.i for a in n.attribute}["relu"]]
     assert len(relus) == 2 + 2                        # two feed-forward blocks, two hidden layers of the box head
+    # the residual sums x + linear(...) in front of each LayerNormalization ride on the linear layer, except the
+    # decoder's first, whose other operand is a constant of the graph (the zero target)
+    with_res = [n for n in m.graph.node if n.op_type == "CudaMatMulBias"
+                and {a.name: a.i for a in n.attribute}["has_residual"]]
+    assert len(with_res) == 4 and all(len(n.input) == 4 for n in with_res)
     # the three attention blocks (scores, scale, softmax, context) are one node each; heads of 8 channels are
     # not a size of the fused kernel, so the head split / merge around them stays in the graph
     assert types.count("MatMul") == 0 and types.count("Softmax") == 0 and types.count("CudaAttention") == 3

@@ -9,8 +9,8 @@ unchanged:
   Bias and the BatchNormalization parameters are folded (in float64, once) into a per-channel
   scale/shift pair stored as new initializers; weights are left untouched.
 * ``Gemm`` + ``Relu`` -> ``CudaGemmRelu``.
-* ``MatMul`` by a constant 2-D matrix + ``Add`` of a constant vector [+ ``Relu``] -> ``CudaMatMulBias``
-  (the bias and the Relu move into the contraction's epilogue).
+* ``MatMul`` by a constant 2-D matrix + ``Add`` of a constant vector [+ ``Relu`` | + ``Add`` of another
+  activation] -> ``CudaMatMulBias`` (bias, Relu and the residual sum move into the contraction's epilogue).
 * the decomposed LayerNormalization chain over the last axis (``ReduceMean``, ``Sub``, ``Mul``/``Pow``,
   ``ReduceMean``, ``Add`` epsilon, ``Sqrt``, ``Div``, ``Mul`` gamma, ``Add`` beta) -> ``CudaLayerNorm``.
 * ``MatMul``(q, ``Transpose``(k)) [-> ``Mul``/``Div`` by a constant scalar] -> ``Softmax`` over the last
@@ -368,8 +368,21 @@ def _fuse_cuda(model: Model) -> None:
                 relu = True
                 chain.append(nx2)
                 out = nx2.output[0]
-            fused = Node("CudaMatMulBias", [n.input[0], n.input[1], other], [out], n.name or n.output[0],
-                         [make_attr("relu", int(relu))])
+            inputs = [n.input[0], n.input[1], other]
+            residual = 0
+            if not relu:
+                # x + linear(...) of a residual block: the sum moves into the contraction's epilogue too (the
+                # operator checks at run time that the shapes are equal, and adds separately otherwise)
+                nx3 = sole_consumer(out)
+                if nx3 is not None and nx3.op_type == "Add" and len(nx3.input) == 2 and out in nx3.input:
+                    res = nx3.input[0] if nx3.input[1] == out else nx3.input[1]
+                    if res != out and res not in inits and res != n.input[0]:
+                        inputs.append(res)
+                        residual = 1
+                        chain.append(nx3)
+                        out = nx3.output[0]
+            fused = Node("CudaMatMulBias", inputs, [out], n.name or n.output[0],
+                         [make_attr("relu", int(relu)), make_attr("has_residual", residual)])
             for c in chain:
                 removed.add(id(c))
             replace_at[id(chain[-1])] = fused

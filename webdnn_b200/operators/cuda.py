@@ -221,16 +221,21 @@ class CudaMatMul(base.MatMul):
 
 
 class CudaMatMulBias(OperatorImpl):
-    """``MatMul(A, W) + b`` [+ Relu] in one launch: A [..., k] (leading dims stacked into rows), W a
-    constant [k, n], b a constant vector of n (load-time rewrite of MatMul + Add, matmul.ts:11-111 and
-    binary7.ts broadcasting for the reference semantics)."""
+    """``MatMul(A, W) + b`` [+ Relu] [+ residual] in one launch: A [..., k] (leading dims stacked into rows), W a
+    constant [k, n], b a constant vector of n, residual an activation of the result's shape (load-time rewrite of
+    MatMul + Add [+ Relu | + Add], matmul.ts:11-111 and binary7.ts broadcasting for the reference semantics).
+
+    With a residual the launch goes through ``wdc_conv2d`` as a 1x1 convolution over the rows (its epilogue takes a
+    per-column addend and a residual tensor together); W is transposed to [n, k] once and kept with the weight."""
 
     def __init__(self):
         super().__init__("cuda")
         self.relu = False
+        self.has_residual = False
 
     def initialize(self, attribute):
         self.relu = get_attr_int(attribute, "relu", 0) != 0
+        self.has_residual = get_attr_int(attribute, "has_residual", 0) != 0
 
     def run(self, context, inputs, n_outputs):
         context.asserts_cuda_tensor_array(inputs)
@@ -240,13 +245,32 @@ class CudaMatMulBias(OperatorImpl):
         if a.ndim < 1 or a.dims[-1] != k:
             raise ValueError("CudaMatMulBias: inner dimensions do not match")
         m = a.length // k
-        d = GemmDesc(batch=1, m=m, n=n, k=k, sab=0, sa0=k, sa1=1, sbb=0, sb0=n, sb1=1, sc0=0, sc1=1,
-                     alpha=1.0, beta=1.0, relu=int(self.relu))
-        y = context.empty_tensor(list(a.dims[:-1]) + [n], "float32")
-        if y.length:
+        out_dims = list(a.dims[:-1]) + [n]
+        res = context.canonical(inputs[3]) if self.has_residual else None
+        owned = [t for t, o in ((a, inputs[0]), (res, inputs[3] if self.has_residual else None)) if t is not o]
+        y = context.empty_tensor(out_dims, "float32")
+        fused_res = res is not None and list(res.dims) == out_dims and res.data_type == "float32" and m < 2 ** 31
+        if y.length and fused_res:
+            wt = w.aux.get("nk")
+            if wt is None:
+                wt = context.empty_tensor([n, k], "float32")
+                context.strided_copy(w, wt, [n, k], [1, n], 0, [k, 1], 0)
+                w.aux["nk"] = wt
+            d = ConvDesc(batch=1, ch_in=k, in_h=1, in_w=m, ch_out=n, k_h=1, k_w=1, out_h=1, out_w=m, stride_h=1,
+                         stride_w=1, pad_t=0, pad_l=0, dil_h=1, dil_w=1, group=1, relu=int(self.relu), x_nchw=0)
+            context.conv2d(d, a, wt, None, b, res, y)
+        elif y.length:
+            d = GemmDesc(batch=1, m=m, n=n, k=k, sab=0, sa0=k, sa1=1, sbb=0, sb0=n, sb1=1, sc0=0, sc1=1,
+                         alpha=1.0, beta=1.0, relu=int(self.relu))
             context.gemm(d, a, w, b, y)
-        if a is not inputs[0]:
-            a.dispose()
+        for t in owned:
+            t.dispose()
+        if res is not None and not fused_res:
+            # shapes differ (the Add broadcasts): keep the reference's two steps
+            add = CudaBinary7("Add")
+            out = add.run(context, [y, inputs[3]], 1)
+            y.dispose()
+            return out
         return [y]
 
 

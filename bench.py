@@ -212,6 +212,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     if world > 1:
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
+        # NCCL's own log lines (its version banner, NCCL_DEBUG output) go to stderr: stdout carries the JSON line only
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
 
     B = args.batch

@@ -36,6 +36,9 @@ METRIC = "resnet50_fp32_inference_images_per_sec"
 CONTRACTION_DRAM_BYTES_PER_LAUNCH_B256 = 25.166e9 / 54
 
 
+RESULT_OUT = sys.stdout   # where the JSON line goes; main() re-points it at the process's original stdout
+
+
 class ClockSampler:
     """Samples SM clock and throttle reasons of one GPU while a region runs: NVML queries from a thread of this
     process every 20 ms (read-only), or, where the NVML binding is missing, lines of ``nvidia-smi -lms``.
@@ -198,7 +201,7 @@ def run_reference(args, rank: int) -> None:
         "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference is TypeScript and cannot run here (no Node.js); this is the C restatement of its "
                 "cpu backend (oracle/cpu_ops.c), OpenMP over independent outputs",
-    }))
+    }), file=RESULT_OUT, flush=True)
 
 
 def run_ours(args, rank: int, local_rank: int, world: int) -> None:
@@ -328,7 +331,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             v, cores, dt = cpu_port_images_per_sec(args.cpu_images)
             line["cpu_baseline"] = {"value": v, "unit": "images/s", "cores": cores, "kind": "port",
                                     "sample": f"{args.cpu_images} images of the same network and init, {dt:.1f} s"}
-        print(json.dumps(line))
+        print(json.dumps(line), file=RESULT_OUT, flush=True)
     x_dev.dispose()
     runner.dispose()
     ctx.close()
@@ -352,14 +355,21 @@ def main() -> None:
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.impl == "reference":
-        run_reference(args, rank)
-        return
-    if world != args.gpus and world == 1 and args.gpus > 1:
+    if args.impl != "reference" and world != args.gpus and world == 1 and args.gpus > 1:
         # launched without torchrun: re-exec under it
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                "--master-addr", "127.0.0.1", "--master-port", "29541", os.path.abspath(__file__)] + sys.argv[1:]
         sys.exit(subprocess.call(cmd))
+    # stdout carries the one JSON line and nothing else: whatever libraries print there from native code (NCCL's
+    # version banner, for one) is sent to stderr by pointing descriptor 1 at it; the JSON line goes to a duplicate
+    # of the original descriptor
+    global RESULT_OUT
+    sys.stdout.flush()
+    RESULT_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
     run_ours(args, rank, local_rank, world)
 
 

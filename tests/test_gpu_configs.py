@@ -358,3 +358,32 @@ def test_linear_layer_with_residual_sum(cuda_context, res_shape, rows):
     r.dispose()
     assert list(got[0].shape) == out_shape == list(want[0].shape)
     assert max_err_rel_linf(got[0], want[0]) <= 1e-4
+
+
+def test_graph_replay_option_serves_later_runs_from_a_recorded_graph(cuda_context):
+    """backendOptions.cuda.graphReplay: the first run() goes node by node, the second records the run and replays
+    it, later ones replay; results equal the node-by-node runner bit for bit, and an input of another shape goes
+    node by node again (its own signature)."""
+    from webdnn_b200.backend import CPUTensor
+    from webdnn_b200.runner import load
+    model = zoo.resnet50(2, size=64, width=16, classes=10)
+    plain = load(model, backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": cuda_context}})
+    fast = load(model, backend_order=["cuda", "cpu"],
+                backend_options={"cuda": {"context": cuda_context, "graphReplay": True}})
+    for i in range(4):
+        x = zoo.make_input((2, 3, 64, 64), seed=10 + i)
+        want = plain.run([CPUTensor.from_array(x)])[0].numpy()
+        got = fast.run([CPUTensor.from_array(x)])[0].numpy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), i
+        assert fast.graph_replays == max(0, i)
+    fast.dispose()
+    plain.dispose()
+    # a graph with a node that must run on the host keeps running node by node
+    host_model = single_op_model("Shape", {}, [np.zeros((2, 3), np.float32)])
+    r = load(host_model, backend_order=["cuda", "cpu"],
+             backend_options={"cuda": {"context": cuda_context, "graphReplay": True}})
+    for _ in range(3):
+        out = r.run([CPUTensor.from_array(np.zeros((2, 3), np.float32))])[0].numpy()
+        assert out.tolist() == [2, 3]
+    assert r.graph_replays == 0
+    r.dispose()

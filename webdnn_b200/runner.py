@@ -65,6 +65,14 @@ class Runner:
         self.inputs_without_initializer = []
         self.node_backends: List[tuple] = []      # (node name, op type, backend) of the last run
         self.node_performances: List[dict] = []
+        # backendOptions.cuda.graphReplay: the second run() with host inputs of a given signature (shapes and
+        # dtypes) is recorded as a CUDA graph, and every later run() with that signature replays it
+        self.graph_replay = False
+        self.graph_replays = 0                    # run() calls served by a replay
+        self._captured: Dict[tuple, "CapturedRun"] = {}
+        self._seen: Dict[tuple, int] = {}
+        self._uncapturable = False
+    MAX_CAPTURED_SIGNATURES = 4                   # each recorded run keeps its own activation memory
 
     # ---- runnerImpl.ts:88-134
     DEVICE_DECODE_MIN_ELEMENTS = 4096  # 8-bit initializers at least this large are decoded on the device
@@ -177,6 +185,21 @@ class Runner:
         tensors, which the caller must dispose."""
         if self.model is None or not self.loaded:
             raise RuntimeError("not initialized")
+        if (self.graph_replay and not measure_performance and not outputs_on_device
+                and len(inputs) == len(self.inputs_without_initializer) and all(t.backend == "cpu" for t in inputs)):
+            sig = tuple((tuple(t.dims), t.data_type) for t in inputs)
+            cap = self._captured.get(sig)
+            if cap is None and not self._uncapturable and self._seen.get(sig, 0) >= 1 \
+                    and len(self._captured) < self.MAX_CAPTURED_SIGNATURES:
+                try:
+                    cap = self._captured[sig] = self.capture(inputs)
+                except Exception as e:   # e.g. a node on the cpu backend: keep running node by node
+                    logger.warning("graph replay disabled for this runner: %s", e)
+                    self._uncapturable = True
+            if cap is not None:
+                self.graph_replays += 1
+                return cap.run(inputs)
+            self._seen[sig] = self._seen.get(sig, 0) + 1
         graph = self.model.graph
         tensors_for_backends: Dict[str, Dict[str, object]] = {b: {} for b in BACKENDS}
         for name, tensor in self.initializer_tensors.items():
@@ -291,6 +314,9 @@ class Runner:
         return [n for n in self.node_backends if n[2] == backend]
 
     def dispose(self) -> None:
+        for cap in self._captured.values():
+            cap.dispose()
+        self._captured.clear()
         for kv in self.copied_initializer_tensors.values():
             for t in kv.values():
                 t.dispose()
@@ -367,5 +393,6 @@ def load(source: Union[str, bytes, Model], backend_order: Optional[Sequence[str]
         raise RuntimeError("No backend available: " + "; ".join(errors))
     order = [succeeded] if succeeded == "cpu" else [succeeded, "cpu"]
     runner = Runner(order, contexts)
+    runner.graph_replay = succeeded == "cuda" and bool(backend_options.get("cuda", {}).get("graphReplay", False))
     runner.load_model(source, onnx_basename)
     return runner

@@ -413,11 +413,11 @@ int orc_reduce_axis(int kind, int final, const float* X, float* Y, int64_t outer
       const float* p = X + o * red * inner + in;
       switch (kind) {
         case R_MAX:
-          s = p[0];
+          s = red > 0 ? p[0] : NAN;   /* empty axis: element 0 is undefined in the reference -> NaN */
           for (int64_t r = 1; r < red; r++) { double v = p[r * inner]; if (v > s) s = v; }
           break;
         case R_MIN:
-          s = p[0];
+          s = red > 0 ? p[0] : NAN;
           for (int64_t r = 1; r < red; r++) { double v = p[r * inner]; if (v < s) s = v; }
           break;
         case R_PROD:

@@ -107,7 +107,8 @@ def run_node(node, ins: List[np.ndarray], opset: int) -> List[np.ndarray]:
     if t == "Flatten":
         if a.get("axis", 1) != 1:
             raise ValueError("Flatten: only axis === 1 is supported")
-        return [ins[0].reshape(ins[0].shape[0], -1)]
+        d = ins[0].shape   # flatten.ts:11-18: [dims[0], product of the rest], also when a dimension is 0
+        return [ins[0].reshape(d[0], int(np.prod(d[1:], dtype=np.int64)))]
     if t == "Reshape":
         shape = [int(v) for v in ins[1].reshape(-1)]
         allowzero = a.get("allowzero", 0) != 0

@@ -48,7 +48,7 @@ def test_case_matches_oracle_and_golden(cuda_context, name):
     for g, w, gold in zip(got, want, case["outputs"]):
         assert list(g.shape) == list(w.shape), (g.shape, w.shape)
         if w.dtype == np.int32:
-            assert np.array_equal(g, w)
+            assert np.array_equal(g, w, equal_nan=True), (op, g, w)
             continue
         if case["op"] in EXACT_UNARY or case["op"] in ("MaxPool", "ReduceMax", "ReduceMin", "Pad", "Tile"):
             assert np.array_equal(g.view(np.uint32), w.view(np.uint32)), name
@@ -224,3 +224,35 @@ def test_pad_negative_pads_crop_and_int32(cuda_context):
     model.graph.input[0].elem_type = 6
     (y,) = run_cuda(model, [x], cuda_context)
     assert np.array_equal(y, ops.pad(x, pads.tolist(), "constant", -7))
+
+
+EMPTY_CASES = {
+    "Relu": ({}, [np.zeros((0, 4), np.float32)], 13),
+    "Transpose": ({"perm": [1, 0]}, [np.zeros((0, 4), np.float32)], 13),
+    "Concat": ({"axis": 0}, [np.zeros((0, 4), np.float32), np.ones((2, 4), np.float32)], 13),
+    "MatMul": ({}, [np.zeros((0, 4), np.float32), np.ones((4, 3), np.float32)], 13),
+    "Gemm": ({}, [np.zeros((0, 4), np.float32), np.ones((4, 3), np.float32), np.ones((3,), np.float32)], 13),
+    "ReduceSum": ({"axes": [0], "keepdims": 0}, [np.zeros((0, 4), np.float32)], 11),
+    "ReduceMax": ({"axes": [0], "keepdims": 1}, [np.zeros((0, 4), np.float32)], 11),
+    "ReduceMean": ({"axes": [0], "keepdims": 0}, [np.zeros((0, 4), np.float32)], 11),
+    "ReduceProd": ({"axes": [1], "keepdims": 0}, [np.zeros((3, 0, 2), np.float32)], 11),
+    "Softmax": ({"axis": -1}, [np.zeros((0, 4), np.float32)], 11),
+    "Flatten": ({}, [np.zeros((0, 4, 2), np.float32)], 13),
+    "GlobalAveragePool": ({}, [np.zeros((0, 3, 2, 2), np.float32)], 13),
+    "Conv": ({"kernel_shape": [1, 1]}, [np.zeros((0, 4, 3, 3), np.float32), np.ones((2, 4, 1, 1), np.float32)], 13),
+    "MaxPool": ({"kernel_shape": [2, 2]}, [np.zeros((0, 4, 4, 4), np.float32)], 13),
+}
+
+
+@pytest.mark.parametrize("op", sorted(EMPTY_CASES))
+def test_empty_batch(cuda_context, op):
+    """Tensors with a zero dimension: same shapes and, for reductions over an empty axis, the same values as the
+    oracle (sum 0, product 1, mean 0/0 = NaN, max of nothing = NaN like the reference's typed-array store)."""
+    attrs, ins, opset = EMPTY_CASES[op]
+    n_run = 1 if op in ("MatMul", "Gemm", "Conv") else len(ins)
+    model = single_op_model(op, attrs, ins, opset=opset, n_graph_inputs=n_run)
+    want = ref_runner.run_model(model, ins[:n_run])
+    got = run_cuda(model, ins[:n_run], cuda_context)
+    for g, w in zip(got, want):
+        assert list(g.shape) == list(w.shape), (op, g.shape, w.shape)
+        assert np.array_equal(g, w, equal_nan=True), (op, g, w)

@@ -193,7 +193,8 @@ __global__ void __launch_bounds__(256) reduce_cols_kernel(int kind, int final, c
       s = 0;
       for (int64_t r = 0; r < red; r++) s += (double)x[o * red + r];
     } else if (kind == R_MAX || kind == R_MIN) {
-      s = p[0];
+      // an empty axis: the reference starts from element 0, which does not exist (undefined -> NaN in the typed array)
+      s = red > 0 ? (double)p[0] : (double)NAN;
       for (int64_t r = 1; r < red; r++) s = red_combine(kind, s, (double)p[r * inner]);
     } else {
       s = (kind == R_PROD) ? 1.0 : 0.0;
@@ -208,9 +209,9 @@ extern "C" int wdc_reduce_axis(wdc_context* ctx, int kind, int final, const floa
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_reduce_axis: null context");
   wdc_note_write(ctx, y);
   WDC_REQUIRE(ctx, kind >= R_SUM && kind <= R_SUMSQUARE, "wdc_reduce_axis: unknown kind %d", kind);
-  WDC_REQUIRE(ctx, outer >= 0 && red > 0 && inner > 0, "wdc_reduce_axis: bad shape");
-  if (outer == 0) return WDC_OK;
-  WDC_REQUIRE(ctx, x && y, "wdc_reduce_axis: null buffer");
+  WDC_REQUIRE(ctx, outer >= 0 && red >= 0 && inner >= 0, "wdc_reduce_axis: bad shape");
+  if (outer == 0 || inner == 0) return WDC_OK;
+  WDC_REQUIRE(ctx, y && (x || red == 0), "wdc_reduce_axis: null buffer");
   DeviceGuard g(ctx->device);
   if (inner == 1 && red >= 64) {
     reduce_rows_kernel<<<grid_for(ctx, outer * 32, 256, 8), 256, 0, ctx->stream>>>(kind, final, x, y,

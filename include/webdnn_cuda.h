@@ -204,7 +204,8 @@ int wdc_argmax(wdc_context* ctx, const float* x, int32_t* y, int64_t outer, int6
 
 /* ---- data movement --------------------------------------------------------------------------
  * dst (dense row-major over dims, starting at element dst_off with strides dstr) <- src at
- * element src_off with strides sstr; 4-byte elements, ndim <= 6.  Serves Transpose
+ * element src_off with strides sstr (source strides may be negative: Slice with a negative step);
+ * 4-byte elements, ndim <= 6.  Serves Transpose
  * (operators/cpu/operators/standard/transpose.ts:12-169), Slice (slice.ts:12-90), Concat
  * (concat.ts:21-77), Split, Tile and NCHW<->NHWC conversion; replaces kernel_copy
  * (src/shader/wasm/src/kernels/standard/copy.cpp:6-8) where a layout really changes. */

@@ -799,8 +799,7 @@ class CudaSlice(OperatorImpl):
             soff += start * x.strides[ax]
         y = context.empty_tensor(out_dims, x.data_type)
         if y.length:
-            if any(s < 0 for s in sstr):
-                raise ValueError("Slice: negative steps are not supported on cuda")
+            # a negative step is a negative source stride from the (clamped) start element
             context.strided_copy(x, y, out_dims, sstr, soff, y.strides, 0)
         if x is not inputs[0]:
             x.dispose()

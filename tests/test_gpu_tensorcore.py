@@ -283,3 +283,87 @@ def test_first_layer_reads_nchw_input_directly(cuda_context, n, cin, cout, size,
     assert _conv_case(cuda_context, n, cin, cout, size, k, stride, pad) <= TOL
     # weight packing + weight split + padding pass + contraction (+ the output's conversion for the host)
     assert cuda_context.stats()["launches"] - before <= 5
+
+
+@pytest.mark.parametrize("seed", range(32))
+def test_fused_block_random_sweep(cuda_context, seed):
+    """Conv (+bias) -> BatchNormalization -> Add(residual) -> Relu as one fused launch, over random channel counts
+    (multiples of 4, also far from multiples of 32; 1 and 3 for first-layer shapes), square kernels of 1..7, strides
+    1..3, pads 0..3, dilation 1..2, image sizes from a handful of pixels to several tiles, with and without each
+    epilogue part; the unfused oracle chain is the expectation."""
+    from webdnn_b200.zoo import _Builder
+    rng = np.random.default_rng(500 + seed)
+    first_layer = seed % 8 == 7
+    cin = int(rng.choice([1, 3])) if first_layer else int(rng.choice([4, 8, 12, 20, 36, 64, 100, 160, 256]))
+    cout = int(rng.choice([4, 12, 32, 60, 64, 128, 200, 260]))
+    k = int(rng.integers(1, 8)) if first_layer else int(rng.choice([1, 1, 2, 3, 3, 5]))
+    stride = int(rng.integers(1, 4))
+    pad = int(rng.integers(0, min(k, 4)))
+    dil = 1 if first_layer else int(rng.integers(1, 3))
+    size = int(rng.integers((k - 1) * dil + 1, (k - 1) * dil + 40))
+    n = int(rng.integers(1, 5))
+    use_bias, use_bn, use_res, use_relu = (bool(v) for v in rng.integers(0, 2, 4))
+    b = _Builder(seed)
+    h = b.conv("x", cin, cout, k, stride=stride, pad=pad, bias=use_bias, dilation=dil)
+    if use_bn:
+        h = b.bn(h, cout)
+    out = (size + 2 * pad - dil * (k - 1) - 1) // stride + 1
+    ins = [("x", [n, cin, size, size])]
+    feeds = [rng.standard_normal((n, cin, size, size)).astype(np.float32)]
+    if use_res:
+        h = b.node("Add", [h, "r"])[0]
+        ins.append(("r", [n, cout, out, out]))
+        feeds.append(rng.standard_normal((n, cout, out, out)).astype(np.float32))
+    if use_relu:
+        h = b.node("Relu", [h])[0]
+    model = b.model(ins, [(h, [n, cout, out, out])])
+    (want,) = ref_runner.run_model(model, feeds)
+    before = cuda_context.stats()["tensor_core_launches"]
+    (got,), r = run_cuda(model, feeds, cuda_context, return_runner=True)
+    kinds = [kd for _, kd, _ in r.node_backends]
+    r.dispose()
+    assert len(kinds) == 1 or not (use_bias or use_bn or use_res or use_relu) or kinds == ["CudaConvFused"], kinds
+    desc = dict(cin=cin, cout=cout, k=k, stride=stride, pad=pad, dil=dil, size=size, n=n, bias=use_bias, bn=use_bn,
+                res=use_res, relu=use_relu)
+    assert got.shape == want.shape, desc
+    assert max_err_rel_linf(got, want) <= TOL, desc
+    if cin % 4 == 0 and cout % 4 == 0:
+        assert cuda_context.stats()["tensor_core_launches"] > before, desc
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_gemm_matmul_random_sweep(cuda_context, seed):
+    """Gemm with every C form (none, scalar, row, column, full), alpha / beta, transA / transB, and MatMul with a
+    constant or a run-time right operand and stacked left operands, over random sizes on both sides of the
+    tensor-core kernel's limits (k % 4, k >= 32, m >= 32)."""
+    rng = np.random.default_rng(900 + seed)
+    m = int(rng.choice([1, 5, 31, 32, 33, 100, 129, 300]))
+    n = int(rng.choice([1, 4, 10, 36, 64, 100, 130, 257]))
+    k = int(rng.choice([3, 8, 32, 36, 50, 64, 100, 260]))
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    bm = (rng.standard_normal((k, n)) / np.sqrt(k)).astype(np.float32)
+    if seed % 2 == 0:
+        ta, tb = int(rng.integers(0, 2)), int(rng.integers(0, 2))
+        c_form = ["none", "scalar", "row", "col", "full"][int(rng.integers(0, 5))]
+        c = {"none": None, "scalar": rng.standard_normal((1,)), "row": rng.standard_normal((n,)),
+             "col": rng.standard_normal((m, 1)), "full": rng.standard_normal((m, n))}[c_form]
+        ins = [np.ascontiguousarray(a.T) if ta else a, np.ascontiguousarray(bm.T) if tb else bm]
+        if c is not None:
+            ins.append(c.astype(np.float32))
+        attrs = dict(alpha=float(rng.choice([1.0, 0.5, -2.0])), beta=float(rng.choice([1.0, 0.0, 0.25])), transA=ta,
+                     transB=tb)
+        const_w = bool(rng.integers(0, 2))
+        model = single_op_model("Gemm", attrs, ins, n_graph_inputs=1 if const_w else len(ins), opset=11)
+        feeds = ins[:1] if const_w else ins
+        desc = dict(op="Gemm", m=m, n=n, k=k, c=c_form, const_w=const_w, **attrs)
+    else:
+        lead = [(), (3,), (5,)][int(rng.integers(0, 3))]      # result rank <= 3, like the reference
+        a = rng.standard_normal(lead + (m, k)).astype(np.float32)
+        const_w = bool(rng.integers(0, 2))
+        model = single_op_model("MatMul", {}, [a, bm], n_graph_inputs=1 if const_w else 2)
+        feeds = [a] if const_w else [a, bm]
+        desc = dict(op="MatMul", lead=lead, m=m, n=n, k=k, const_w=const_w)
+    (want,) = ref_runner.run_model(model, feeds)
+    (got,) = run_cuda(model, feeds, cuda_context)
+    assert got.shape == want.shape, desc
+    assert max_err_rel_linf(got, want) <= TOL, desc

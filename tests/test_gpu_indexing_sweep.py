@@ -124,6 +124,22 @@ CASES = {
                                     [_rand((1, 3, 7, 8)), _rand((5, 3, 2, 3), 1)], n_run=1, exact=False),
 }
 
+# row operators over many lengths (warp kernels up to 1024 elements, block kernels beyond) and every reduction kind
+for _len in (1, 2, 31, 33, 256, 1024, 1025, 4097):
+    CASES[f"softmax_len{_len}"] = _check("Softmax", {"axis": -1}, [_rand((3, _len), _len) * 3], exact=False)
+    CASES[f"layernorm_len{_len}"] = _check("LayerNormalization", {"axis": -1, "epsilon": 1e-5},
+                                           [_rand((5, _len), _len), _rand((_len,), 1), _rand((_len,), 2)],
+                                           n_run=1, opset=17, exact=False)
+for _kind in ("ReduceSum", "ReduceMean", "ReduceMax", "ReduceMin", "ReduceProd", "ReduceL1", "ReduceL2",
+              "ReduceLogSum", "ReduceLogSumExp", "ReduceSumSquare"):
+    _x = np.abs(_rand((3, 4, 5, 6), 7)) + 0.5 if "Log" in _kind else _rand((3, 4, 5, 6), 7)
+    CASES[f"{_kind.lower()}_axes13_keep"] = _check(_kind, {"axes": [1, 3], "keepdims": 1}, [_x], opset=11, exact=False)
+    CASES[f"{_kind.lower()}_axis_last_drop"] = _check(_kind, {"axes": [-1], "keepdims": 0}, [_x], opset=11, exact=False)
+    CASES[f"{_kind.lower()}_all"] = _check(_kind, {"keepdims": 0}, [_x], opset=11, exact=False)
+CASES["reducesum_long_rows"] = _check("ReduceSum", {"axes": [1], "keepdims": 0}, [_rand((7, 5000), 3)], opset=11,
+                                      exact=False)
+CASES["reducemax_long_cols"] = _check("ReduceMax", {"axes": [0], "keepdims": 0}, [_rand((3000, 9), 3)], opset=11)
+
 
 @pytest.mark.parametrize("name", sorted(CASES))
 def test_variant(cuda_context, name):

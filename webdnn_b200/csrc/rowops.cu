@@ -270,17 +270,60 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const float* __rest
   }
 }
 
+// Rows longer than 1024 elements: one CTA of 256 threads per row, the row read three times (it stays in L2 / L1
+// between the passes), the same rounding points as above.
+__device__ __forceinline__ double block_sum_d(double v, double* scratch) {
+  v = warp_sum_d(v);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  __syncthreads();                 // scratch may still be read from the previous reduction
+  if (lane == 0) scratch[w] = v;
+  __syncthreads();
+  double t = 0;
+  for (int i = 0; i < (int)(blockDim.x >> 5); i++) t += scratch[i];   // same order in every thread
+  return t;
+}
+__global__ void __launch_bounds__(256) layernorm_block_kernel(const float* __restrict__ x,
+                                                              const float* __restrict__ gamma,
+                                                              const float* __restrict__ beta,
+                                                              float* __restrict__ y, int64_t outer, int64_t len,
+                                                              float eps) {
+  __shared__ double scratch[8];
+  for (int64_t row = blockIdx.x; row < outer; row += gridDim.x) {
+    const float* xr = x + row * len;
+    double s = 0;
+    for (int64_t c = threadIdx.x; c < len; c += blockDim.x) s += (double)xr[c];
+    const float mean = (float)(block_sum_d(s, scratch) / (double)len);
+    double q = 0;
+    for (int64_t c = threadIdx.x; c < len; c += blockDim.x) {
+      const float d = xr[c] - mean;            // Sub
+      const float sq = d * d;                  // Mul / Pow 2
+      q += (double)sq;
+    }
+    const float var = (float)(block_sum_d(q, scratch) / (double)len);  // ReduceMean
+    const float den = sqrtf(var + eps);                                   // Add, Sqrt
+    float* yr = y + row * len;
+    for (int64_t c = threadIdx.x; c < len; c += blockDim.x) {
+      float r = (xr[c] - mean) / den;          // Sub, Div
+      if (gamma) r = r * gamma[c];             // Mul
+      if (beta) r = r + beta[c];               // Add
+      yr[c] = r;
+    }
+  }
+}
+
 extern "C" int wdc_layernorm(wdc_context* ctx, const float* x, const float* gamma, const float* beta,
                              float* y, int64_t outer, int64_t len, float eps) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_layernorm: null context");
   wdc_note_write(ctx, y);
   WDC_REQUIRE(ctx, outer >= 0 && len > 0, "wdc_layernorm: bad shape");
-  if (len > 1024)
-    return wdc_fail(ctx, WDC_ERR_UNSUPPORTED, "wdc_layernorm: rows longer than 1024 (%lld) not supported",
-                    (long long)len);
   if (outer == 0) return WDC_OK;
   WDC_REQUIRE(ctx, x && y, "wdc_layernorm: null buffer");
   DeviceGuard g(ctx->device);
+  if (len > 1024) {
+    const int64_t cap = (int64_t)ctx->sm_count * 8;
+    layernorm_block_kernel<<<(int)(outer < cap ? outer : cap), 256, 0, ctx->stream>>>(x, gamma, beta, y, outer, len, eps);
+    return wdc_check_launch(ctx, "layernorm_block_kernel");
+  }
   int grid = grid_for(ctx, outer * 32, 256, 8);
   int l = (int)len;
 #define LN(IT) layernorm_warp_kernel<IT><<<grid, 256, 0, ctx->stream>>>(x, gamma, beta, y, outer, l, eps)

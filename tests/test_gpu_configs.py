@@ -135,6 +135,8 @@ def test_config5_detr_style(cuda_context, batch):
     (4, 8, 32, 1024),    # persistent kernel, 8 units per CTA
     (6, 2, 8, 24),       # hidden size not a multiple of 16: per-step path
     (3, 70, 16, 32),     # batch above 64: per-step path
+    (1, 1, 5, 32),       # one step, one row, input size outside the tensor-core kernel's limits
+    (2, 5, 7, 64),       # odd input size
 ])
 def test_lstm_shapes(cuda_context, seq, batch, inp, hidden):
     model = zoo.lstm(seq, batch, inp, hidden)

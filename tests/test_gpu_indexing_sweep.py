@@ -140,6 +140,22 @@ CASES["reducesum_long_rows"] = _check("ReduceSum", {"axes": [1], "keepdims": 0},
                                       exact=False)
 CASES["reducemax_long_cols"] = _check("ReduceMax", {"axes": [0], "keepdims": 0}, [_rand((3000, 9), 3)], opset=11)
 
+# the operators added last: ConvTranspose and InstanceNormalization over attribute forms
+for _i, (_cin, _cout, _k, _s, _p, _d, _g, _op) in enumerate([
+        (4, 6, 3, 2, 1, 1, 1, 1), (6, 4, 2, 2, 0, 1, 2, 0), (3, 5, 3, 1, 1, 2, 1, 0), (8, 8, 4, 3, 2, 1, 4, 2),
+        (2, 3, 1, 1, 0, 1, 1, 0), (5, 2, 5, 2, 2, 1, 1, 1)]):
+    _attrs = {"kernel_shape": [_k, _k], "strides": [_s, _s], "pads": [_p] * 4, "dilations": [_d, _d], "group": _g}
+    if _op:
+        _attrs["output_padding"] = [min(_op, _s - 1)] * 2
+    CASES[f"convtranspose_v{_i}"] = _check(
+        "ConvTranspose", _attrs, [_rand((2, _cin, 5, 6), _i), _rand((_cin, _cout // _g, _k, _k), _i + 1) * 0.3,
+                                  _rand((_cout,), _i + 2)], n_run=1, exact=False)
+for _i, (_shape, _eps) in enumerate([((2, 3, 4, 5), 1e-5), ((1, 7, 1, 1), 1e-3), ((3, 2, 33, 31), 1e-5),
+                                     ((2, 5, 64, 64), 0.1)]):
+    CASES[f"instancenorm_v{_i}"] = _check("InstanceNormalization", {"epsilon": _eps},
+                                          [_rand(_shape, _i) * 2 + 1, _rand((_shape[1],), 9), _rand((_shape[1],), 8)],
+                                          n_run=1, exact=False)
+
 
 @pytest.mark.parametrize("name", sorted(CASES))
 def test_variant(cuda_context, name):

@@ -14,6 +14,11 @@ from ..onnx_io import Attribute, clip_long
 
 
 # ---- operatorUtil.ts:19-133 --------------------------------------------------------------
+# The reference's getAttrFloat / getAttrInt / getAttrString throw only when the field is null, and a message
+# decoded by its protobuf binding never has null scalar fields: onnx/onnx.js:137-153 gives AttributeProto.f = 0,
+# i = 0 and s = empty as prototype defaults.  So an attribute that is present but stored under another type reads
+# as 0 / 0 / "" there (instancenormalization.ts:18 reads a float epsilon with getAttrInt and gets 0), and the same
+# holds here.
 def _get_attr(attribute: Sequence[Attribute], name: str) -> Optional[Attribute]:
     for a in attribute:
         if a.name == name:
@@ -25,18 +30,14 @@ def get_attr_float(attribute, name: str, default: float) -> float:
     a = _get_attr(attribute, name)
     if a is None:
         return default
-    if a.f is None:
-        raise ValueError(f"Attribute {name} is not float")
-    return a.f
+    return a.f if a.f is not None else 0.0
 
 
 def get_attr_int(attribute, name: str, default: int) -> int:
     a = _get_attr(attribute, name)
     if a is None:
         return default
-    if a.i is None:
-        raise ValueError(f"Attribute {name} is not int")
-    return clip_long(a.i)
+    return clip_long(a.i) if a.i is not None else 0
 
 
 def get_attr_ints(attribute, name: str, default: List[int]) -> List[int]:
@@ -50,9 +51,7 @@ def get_attr_string(attribute, name: str, default: str) -> str:
     a = _get_attr(attribute, name)
     if a is None:
         return default
-    if a.s is None:
-        raise ValueError(f"Attribute {name} is not string")
-    return a.s.decode("utf-8")
+    return a.s.decode("utf-8") if a.s is not None else ""
 
 
 def get_attr_tensor(attribute, name: str):

@@ -3,6 +3,7 @@ wdc_attention on the attention shapes of the DETR-style configuration.
 
     python -m webdnn_b200.layer_bench [--batch 256] [--only l4.c2,l1.c3] [--reps 5]
     python -m webdnn_b200.layer_bench --attention [--batch 8] [--only enc] [--reps 5]
+    python -m webdnn_b200.layer_bench --streaming [--reps 20]     # HBM-bound operators, GB/s of algorithmic bytes
 
 Prints, per layer, the mean device time of the contraction launch (CUDA events recorded by the
 library around each launch), algorithmic TFLOP/s, the tensor-issue rate (3 MMAs per algorithmic
@@ -86,10 +87,70 @@ def attention_bench(ctx: WebDNNCudaContext, batch: int, only, reps: int) -> None
             t.dispose()
 
 
+# name, op type, attributes, input shapes, opset, algorithmic bytes as a multiple of the first input's bytes
+STREAMING = [
+    ("Relu 256 MB", "Relu", {}, [(64, 1024, 1024)], 13, 2.0),
+    ("Sigmoid 256 MB", "Sigmoid", {}, [(64, 1024, 1024)], 13, 2.0),
+    ("Add 2 x 256 MB", "Add", {}, [(64, 1024, 1024), (64, 1024, 1024)], 13, 3.0),
+    ("Add bias [.., 1024] + [1024]", "Add", {}, [(64, 1024, 1024), (1024,)], 13, 2.0),
+    ("Softmax rows of 625", "Softmax", {"axis": -1}, [(64, 1000, 625)], 13, 2.0),
+    ("Softmax rows of 4096", "Softmax", {"axis": -1}, [(16384, 4096)], 13, 2.0),
+    ("LayerNormalization rows of 256", "LayerNormalization", {"axis": -1}, [(262144, 256), (256,), (256,)], 17, 2.0),
+    ("LayerNormalization rows of 4096", "LayerNormalization", {"axis": -1}, [(16384, 4096), (4096,), (4096,)], 17, 2.0),
+    ("ReduceMean last axis of 1024", "ReduceMean", {"axes": [-1], "keepdims": 1}, [(65536, 1024)], 11, 1.0),
+    ("Transpose [64,1024,1024] 0,2,1", "Transpose", {"perm": [0, 2, 1]}, [(64, 1024, 1024)], 13, 2.0),
+    ("Transpose heads [8,625,8,32] 0,2,1,3", "Transpose", {"perm": [0, 2, 1, 3]}, [(64, 625, 8, 32)], 13, 2.0),
+    ("GlobalAveragePool [256,2048,7,7]", "GlobalAveragePool", {}, [(256, 2048, 7, 7)], 13, 1.0),
+]
+
+
+def streaming_bench(ctx: WebDNNCudaContext, only, reps: int, hbm_peak: float) -> None:
+    import time
+
+    from . import onnx_io
+    from .runner import load
+    print("| operator | ms | GB/s of algorithmic bytes | of the measured HBM copy peak |")
+    print("|---|---:|---:|---:|")
+    for name, op, attrs, shapes, opset, factor in STREAMING:
+        if only and not any(name.startswith(o) for o in only):
+            continue
+        names = [f"in{i}" for i in range(len(shapes))]
+        node = onnx_io.make_node(op, names, ["out"], name=op, **attrs)
+        g = onnx_io.Graph("g", [node], [], [onnx_io.ValueInfo(n, onnx_io.FLOAT, list(sh)) for n, sh in zip(names, shapes)],
+                          [onnx_io.ValueInfo("out", onnx_io.FLOAT, [])])
+        runner = load(onnx_io.Model(g, opset_import=[("", opset)]), backend_order=["cuda", "cpu"],
+                      backend_options={"cuda": {"context": ctx}})
+        dev = []
+        for sh in shapes:
+            t = ctx.empty_tensor(list(sh))
+            ctx._call("wdc_fill_u32", c_void_p(t.ptr), 0x3F000000, t.length)   # 0.5
+            dev.append(t)
+
+        def step():
+            for o in runner.run(dev, outputs_on_device=True):
+                o.dispose()
+
+        for _ in range(3):
+            step()
+        ctx.sync()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            step()
+        ctx.sync()
+        ms = (time.perf_counter() - t0) / reps * 1e3
+        gbs = factor * dev[0].length * 4 / ms / 1e6
+        print(f"| {name} | {ms:.3f} | {gbs:.0f} | {gbs / hbm_peak * 100:.0f}% |")
+        for t in dev:
+            t.dispose()
+        runner.dispose()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=0, help="default 256 (convolutions) or 8 (attention)")
     ap.add_argument("--attention", action="store_true")
+    ap.add_argument("--streaming", action="store_true")
+    ap.add_argument("--hbm-peak", type=float, default=6542.0, help="GB/s used for the fraction column of --streaming")
     ap.add_argument("--only", default="")
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--tf32-peak", type=float, default=752.0, help="TFLOP/s used for the issue-rate column")
@@ -99,6 +160,10 @@ def main() -> None:
     ctx.initialize()
     if args.attention:
         attention_bench(ctx, args.batch or 8, only, args.reps)
+        ctx.close()
+        return
+    if args.streaming:
+        streaming_bench(ctx, only, max(args.reps, 10), args.hbm_peak)
         ctx.close()
         return
     B = args.batch or 256

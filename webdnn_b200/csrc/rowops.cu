@@ -49,11 +49,12 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const float* __restri
       s += v[i];
     }
     s = warp_sum(s);
+    const float inv = 1.f / s;   // one division per row; e * (1 / s) is within an ulp of e / s
     float* yr = y + row * len;
 #pragma unroll
     for (int i = 0; i < ITEMS; i++) {
       int c = i * 32 + lane;
-      if (c < len) yr[c] = v[i] / s;
+      if (c < len) yr[c] = v[i] * inv;
     }
   }
 }
@@ -95,8 +96,8 @@ __global__ void __launch_bounds__(512) softmax_block_kernel(const float* __restr
       if (lane == 0) bcast = t;
     }
     __syncthreads();
-    s = bcast;
-    for (int64_t c = threadIdx.x; c < len; c += blockDim.x) yr[c] = yr[c] / s;
+    s = 1.f / bcast;
+    for (int64_t c = threadIdx.x; c < len; c += blockDim.x) yr[c] = yr[c] * s;
     __syncthreads();
   }
 }
@@ -117,6 +118,8 @@ extern "C" int wdc_softmax(wdc_context* ctx, const float* x, float* y, int64_t o
     else if (len <= 128) SM(4);
     else if (len <= 256) SM(8);
     else if (len <= 512) SM(16);
+    else if (len <= 640) SM(20);
+    else if (len <= 768) SM(24);
     else SM(32);
 #undef SM
     return wdc_check_launch(ctx, "softmax_warp_kernel");
@@ -255,13 +258,13 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const float* __rest
       q += c < len ? (double)sq : 0.0;
     }
     float var = (float)(warp_sum_d(q) / (double)len);  // ReduceMean
-    float den = sqrtf(var + eps);                       // Add, Sqrt
+    float rden = 1.f / sqrtf(var + eps);                // Add, Sqrt; the Div as a multiplication (within an ulp)
     float* yr = y + row * len;
 #pragma unroll
     for (int i = 0; i < ITEMS; i++) {
       int c = i * 32 + lane;
       if (c < len) {
-        float r = v[i] / den;                  // Div
+        float r = v[i] * rden;                 // Div
         if (gamma) r = r * gamma[c];           // Mul
         if (beta) r = r + beta[c];             // Add
         yr[c] = r;
@@ -300,10 +303,10 @@ __global__ void __launch_bounds__(256) layernorm_block_kernel(const float* __res
       q += (double)sq;
     }
     const float var = (float)(block_sum_d(q, scratch) / (double)len);  // ReduceMean
-    const float den = sqrtf(var + eps);                                   // Add, Sqrt
+    const float rden = 1.f / sqrtf(var + eps);                            // Add, Sqrt; Div as a multiplication
     float* yr = y + row * len;
     for (int64_t c = threadIdx.x; c < len; c += blockDim.x) {
-      float r = (xr[c] - mean) / den;          // Sub, Div
+      float r = (xr[c] - mean) * rden;         // Sub, Div
       if (gamma) r = r * gamma[c];             // Mul
       if (beta) r = r + beta[c];               // Add
       yr[c] = r;

@@ -141,6 +141,26 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi"}
 
 
+def bind_to_gpu_cpus(gpu_index: int):
+    """Multi-GPU runs: keep this rank's threads, and so the pinned host buffers it allocates, on the CPUs NVML lists
+    as local to its GPU (same NUMA node and PCIe root), so that eight ranks' input transfers do not cross sockets.
+    Reads the topology only; returns the number of CPUs bound to, or None when NVML or the call is unavailable."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(gpu_index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {64 * w + b for w, m in enumerate(mask) for b in range(64) if (int(m) >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
 def measure_tf32_peak(device: int) -> float:
     """cuBLAS TF32 8192^3 matmul, best of 10, TFLOP/s: the denominator of the tensor roofline."""
     import torch
@@ -212,9 +232,11 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     from webdnn_b200.runner import load
 
     dist = None
+    affinity = None
     if world > 1:
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
+        affinity = bind_to_gpu_cpus(local_rank)
         # NCCL's own log lines (its version banner, NCCL_DEBUG output) go to stderr: stdout carries the JSON line only
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
@@ -308,7 +330,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
             "warmup": max(args.warmup, 3), "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": f"ResNet-50 v1.5 [B,3,224,224] fp32 through runner.run(), B={B} per GPU",
-                       "global_batch": B * world, "replicas": world,
+                       "global_batch": B * world, "replicas": world, "cpus_per_rank": affinity,
                        "l2": "inputs (154 MB) and activations exceed the 126 MB L2; no flush",
                        "precision": os.environ.get("WDC_PRECISION", "default")},
             "e2e": {"value": e2e_value, "unit": "images/s", "ms_per_step": e2e_ms / args.steps,

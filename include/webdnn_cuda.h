@@ -74,10 +74,27 @@ int wdc_wait_upload(wdc_context* ctx, int64_t ticket);
 int wdc_copy(wdc_context* ctx, void* dst, const void* src, int64_t bytes);
 int wdc_fill_u32(wdc_context* ctx, void* dst, uint32_t value, int64_t count);
 int wdc_sync(wdc_context* ctx);
+/* Per-context options, the device side of `backendOptions.cuda` (InitOption.backendOptions, index.ts:26-30):
+ *   "precision" 0 = tf32x3: every fp32 multiply-add of a tensor-core contraction is three TF32 MMAs on split
+ *                   operands (fp32-class accuracy, the default); 1 = tf32x1: one MMA on truncated operands
+ *                   (three times the tensor-pipe rate, about 1e-3 relative error per layer);
+ *   "split_k"   1 = small outputs with long reductions may be cut into K ranges (default), 0 = never;
+ *   "pdl"       1 = contraction launches are programmatic dependent launches, so that a launch's set-up
+ *                   overlaps the tail of the launch before it (default), 0 = plain stream order;
+ *   "nvtx"      1 = wdc_range_push / wdc_range_pop emit NVTX ranges (default 0).
+ * Unknown names and out-of-range values return WDC_ERR_INVALID.  A captured graph keeps the options that were
+ * in force while it was captured. */
+int wdc_set_option(wdc_context* ctx, const char* name, int64_t value);
+/* Named ranges around a caller's work (one per graph node: "name(opType)"), the counterpart of the per-node
+ * records the reference's runner logs (core/runnerImpl.ts:487-489, 534-541).  No-ops unless option "nvtx" is 1. */
+int wdc_range_push(wdc_context* ctx, const char* name);
+int wdc_range_pop(wdc_context* ctx);
 /* cudaStream_t of the context, for callers that record their own events around launches. */
 void* wdc_stream(wdc_context* ctx);
 /* out[0..n): bytes_in_use, high_water_bytes, reserved_bytes, allocs, frees, launches,
- * h2d_bytes, d2h_bytes, tensor_core_launches (launches of the tcgen05 contraction kernel). */
+ * h2d_bytes, d2h_bytes, tensor_core_launches (launches of the tcgen05 contraction kernel),
+ * then, only when n > 9 (it costs a driver call): device_free_bytes, device_total_bytes as
+ * cudaMemGetInfo reports them for the context's GPU (-1 if that query fails). */
 int wdc_stats(wdc_context* ctx, int64_t* out, int n);
 int wdc_reset_stats(wdc_context* ctx);
 /* Per-family device timing.  While enabled, every contraction launch (wdc_gemm / wdc_conv2d) is
@@ -267,13 +284,23 @@ int wdc_lstm(wdc_context* ctx, const float* X, const float* W, const float* R, c
              const float* h0, const float* c0, float* Y, float* Yh, float* Yc, int64_t T,
              int64_t Bt, int64_t I, int64_t H);
 
+/* Self-test of the error path of bounded device waits (the reference's counterpart is the exception path of
+ * core/runnerImpl.ts:511-520: a failing operator is reported, the runner object stays usable).  Enqueues the
+ * persistent LSTM kernel on a small internal problem whose first step can never complete, with limit_ns
+ * (1 us .. 1 s) as the limit of its waits: the kernel gives up after that time, records its status and returns.
+ * The call itself returns WDC_OK; the next wdc_sync / wdc_download returns WDC_ERR_DEVICE_WAIT once, and the
+ * context keeps working afterwards. */
+int wdc_selftest_device_wait(wdc_context* ctx, int64_t limit_ns);
+
 /* wdc_lstm for callers that cannot allocate device memory while they run (a host that owns all GPU memory in
  * its own pool, a real-time loop, a sandbox without cudaMalloc): same arguments and results as wdc_lstm, but the
  * scratch is a fixed 4 MiB array inside the library image (held on every GPU that loads the library, until exit)
  * and no cudaMalloc / cudaFree / allocating routine is called.  Limit: batch * 4 * hidden_size <= 1 048 576,
- * otherwise WDC_ERR_UNSUPPORTED.  The first call on a device looks the array's address up; make it before any
- * stream capture.  Calls on one device share the array: calls that overlap on the GPU race.  This entry point has
- * no counterpart in the reference. */
+ * otherwise WDC_ERR_UNSUPPORTED.  The array's address is looked up, and the modules of the kernels this entry
+ * point launches are loaded, by wdc_create for its device: that is the moment the driver sets the 4 MiB aside, so
+ * create the context at start-up.  (If a device's address is still unknown when the call runs, the call looks it
+ * up itself; such a first call must come before any stream capture.)  Calls on one device share the array: calls
+ * that overlap on the GPU race.  This entry point has no counterpart in the reference. */
 int wdc_lstm_static(wdc_context* ctx, const float* X, const float* W, const float* R, const float* bias,
                     const float* h0, const float* c0, float* Y, float* Yh, float* Yc, int64_t T,
                     int64_t Bt, int64_t I, int64_t H);

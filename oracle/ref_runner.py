@@ -235,10 +235,21 @@ def run_model(model: onnx_io.Model, inputs: Sequence[np.ndarray], return_all: bo
     for vi, arr in zip(free_inputs, inputs):
         values[vi.name] = _c(arr)
     opset = int(model.opset_import[0][1])
-    for node in g.node:
+    # like the reference's runner (runnerImpl.ts:523-532) an intermediate value is dropped after its last consumer,
+    # unless every value was asked for; without this a batch-32 ResNet-50 keeps several GB of activations alive
+    last_use: Dict[str, int] = {}
+    for i, node in enumerate(g.node):
+        for n in node.input:
+            last_use[n] = i
+    keep = init_names | {vi.name for vi in g.output} | {vi.name for vi in free_inputs}
+    for i, node in enumerate(g.node):
         outs = run_node(node, [values[n] for n in node.input], opset)
         for name, arr in zip(node.output, outs):
             values[name] = arr
+        if not return_all:
+            for n in node.input:
+                if last_use.get(n) == i and n not in keep:
+                    values.pop(n, None)
     if return_all:
         return values
     return [values[vi.name] for vi in g.output]

@@ -389,3 +389,61 @@ def test_graph_replay_option_serves_later_runs_from_a_recorded_graph(cuda_contex
         assert out.tolist() == [2, 3]
     assert r.graph_replays == 0
     r.dispose()
+
+
+def _with_logits(model):
+    """Adds the input of the final Softmax as a second graph output: the softmax of a random-init ResNet-50 is
+    one-hot (logits ~ 4e4), so the logits carry the signal."""
+    from webdnn_b200 import onnx_io
+    logits_name = model.graph.node[-1].input[0]
+    model.graph.output.append(onnx_io.ValueInfo(logits_name, onnx_io.FLOAT, []))
+    return model
+
+
+def test_config3_batch32_against_the_oracle(cuda_context):
+    """ResNet-50 at the batch each GPU gets when 256 images are split over 8 GPUs: every logit and every softmax
+    value of all 32 images against the CPU oracle (conv.ts:134-333, gemm.ts:21-61, softmax.ts:39-57)."""
+    model = _with_logits(zoo.resnet50(32))
+    x = zoo.make_input((32, 3, 224, 224))
+    want, want_logits = ref_runner.run_model(model, [x])
+    (got, got_logits), r = run_cuda(model, [x], cuda_context, return_runner=True)
+    _all_on_cuda(r)
+    r.dispose()
+    assert got_logits.shape == (32, 1000)
+    assert max_err_rel_linf(got_logits, want_logits) <= TOL
+    assert max_err_rel_linf(got, want) <= TOL
+
+
+def test_config3_batch256_rows_against_the_oracle(cuda_context):
+    """The benchmark's own configuration (batch 256).  Images are independent, so the oracle runs on 8 rows picked
+    across the batch (first, last, and six between: different tiles, waves and CTAs of every launch) and those
+    rows of the batch-256 CUDA run must match it."""
+    rows = [0, 31, 77, 128, 129, 200, 254, 255]
+    x = zoo.make_input((256, 3, 224, 224))
+    (got, got_logits), r = run_cuda(_with_logits(zoo.resnet50(256)), [x], cuda_context, return_runner=True)
+    _all_on_cuda(r)
+    r.dispose()
+    want, want_logits = ref_runner.run_model(_with_logits(zoo.resnet50(len(rows))), [np.ascontiguousarray(x[rows])])
+    assert max_err_rel_linf(got_logits[rows], want_logits) <= TOL
+    assert max_err_rel_linf(got[rows], want) <= TOL
+    assert np.isfinite(got_logits).all()
+
+
+def test_config5_full_size_against_the_oracle(cuda_context):
+    """The DETR-style network at its stated size (800x800 input, 625 tokens, d = 256, 8 heads of 32, 6 + 6 layers,
+    100 queries), batch 1, both outputs against the CPU oracle's decomposed graph (matmul.ts:63-111,
+    binary7.ts:16-68, softmax.ts:39-57 for every attention block).  The head size of 32 takes the fused attention
+    kernel: this is where that kernel meets the oracle inside a whole graph."""
+    model = zoo.detr(batch=1, size=800)
+    x = zoo.make_input((1, 3, 800, 800))
+    want = ref_runner.run_model(model, [x])
+    before = cuda_context.stats()["launches"]
+    got, r = run_cuda(model, [x], cuda_context, return_runner=True)
+    _all_on_cuda(r)
+    kinds = [k for _, k, _ in r.node_backends]
+    assert kinds.count("CudaAttention") == 18 and "Softmax" not in kinds and "MatMul" not in kinds
+    r.dispose()
+    assert cuda_context.stats()["launches"] > before
+    assert [g.shape for g in got] == [(1, 100, 92), (1, 100, 4)]
+    for g, w in zip(got, want):
+        assert max_err_rel_linf(g, w) <= TOL

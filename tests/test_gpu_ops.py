@@ -256,3 +256,28 @@ def test_empty_batch(cuda_context, op):
     for g, w in zip(got, want):
         assert list(g.shape) == list(w.shape), (op, g.shape, w.shape)
         assert np.array_equal(g, w, equal_nan=True), (op, g, w)
+
+
+@pytest.mark.parametrize("addend_shape", [(1, 32, 9, 9), (3, 32, 1, 1), (3, 1, 9, 9), (3, 32, 9, 9), (32, 1, 1)])
+@pytest.mark.parametrize("relu", [False, True])
+def test_conv_bn_add_with_a_broadcasting_addend(cuda_context, addend_shape, relu):
+    """Conv + BatchNormalization + Add [+ Relu] is rewritten to one CudaConvFused node whatever the second operand of
+    the Add is; only an addend of exactly the output's shape may ride in the epilogue.  A broadcasting Add
+    (binary7.ts:16-68 broadcasts multidirectionally) must give the reference's numbers and shape."""
+    from webdnn_b200 import zoo
+    b = zoo._Builder(5)
+    h = b.bn(b.conv("input", 16, 32, 3, 1, 1, bias=True), 32)
+    h = b.node("Add", [h, "addend"])[0]
+    if relu:
+        h = b.node("Relu", [h])[0]
+    model = b.model([("input", [3, 16, 9, 9]), ("addend", list(addend_shape))], [(h, [3, 32, 9, 9])])
+    rng = np.random.default_rng(8)
+    x = rng.standard_normal((3, 16, 9, 9)).astype(np.float32)
+    a = rng.standard_normal(addend_shape).astype(np.float32)
+    (want,) = ref_runner.run_model(model, [x, a])
+    (got,), r = run_cuda(model, [x, a], cuda_context, return_runner=True)
+    _check_all_on_cuda(r)
+    assert [t for _, t, _ in r.node_backends] == ["CudaConvFused"]
+    r.dispose()
+    assert got.shape == want.shape == (3, 32, 9, 9)
+    assert max_err_rel_linf(got, want) <= TOL

@@ -103,6 +103,36 @@ def test_split_precision_is_fp32_class(cuda_context):
     assert max_err_rel_linf(got, want) <= 1e-5
 
 
+def test_precision_option_selects_single_pass_tf32(cuda_context):
+    """backendOptions.cuda.precision = "tf32x1": one MMA per multiply-add on operands cut to 10 mantissa bits.  On
+    the values of the test above it must be visibly worse than the default (else the option did nothing) and still
+    TF32-class (< 2e-3); switching back restores fp32-class results.  Unknown values are refused."""
+    from webdnn_b200.lib import CudaBackendError
+    ctx = cuda_context
+    rng = np.random.default_rng(3)
+    m, n, k = 128, 64, 512
+    a = (1.0 + rng.uniform(0, 1, (m, k)) * 2.0 ** -9).astype(np.float32)
+    b = (1.0 + rng.uniform(0, 1, (n, k)) * 2.0 ** -9).astype(np.float32)
+    model = single_op_model("Gemm", {"transB": 1}, [a, b])
+    (want,) = ref_runner.run_model(model, [a, b])
+    try:
+        ctx.set_precision("tf32x1")
+        before = ctx.stats()["tensor_core_launches"]
+        (one,) = run_cuda(model, [a, b], ctx)
+        assert ctx.stats()["tensor_core_launches"] > before
+    finally:
+        ctx.set_precision("tf32x3")
+    (three,) = run_cuda(model, [a, b], ctx)
+    e1, e3 = max_err_rel_linf(one, want), max_err_rel_linf(three, want)
+    assert e3 <= 1e-5 and 1e-4 < e1 < 2e-3, (e1, e3)
+    with pytest.raises(ValueError):
+        ctx.set_precision("fp16")
+    with pytest.raises(CudaBackendError, match="precision is 0"):
+        ctx.set_option("precision", 7)
+    with pytest.raises(CudaBackendError, match="unknown option"):
+        ctx.set_option("no_such_option", 1)
+
+
 def test_weight_split_cache_follows_buffer_lifetime(cuda_context):
     """The cached hi/lo split of a weight buffer must not outlive the buffer: a new tensor that lands
     on the same address with other values has to give the new result."""
@@ -144,6 +174,81 @@ def test_weight_split_cache_sees_in_place_writes(cuda_context):
     want[:, n // 2:] = 0
     assert max_err_rel_linf(dy.get_data().reshape(m, n), want) <= TOL
     for t in (da, db, dy, half):
+        t.dispose()
+
+
+def test_weight_split_cache_sees_a_write_that_starts_before_the_operand(cuda_context):
+    """B sits at an offset inside a larger allocation.  Rewriting the whole allocation from its base starts before
+    the cached operand and covers it: the next contraction must see the new values, and so must one after a
+    wdc_gemm whose C aliases Y (the in-place accumulate of the CUDA-core kernel)."""
+    from ctypes import byref, c_void_p
+    from webdnn_b200.backend import CPUTensor
+    from webdnn_b200.lib import GemmDesc
+    ctx = cuda_context
+    rng = np.random.default_rng(15)
+    m, n, k, lead = 64, 64, 128, 4096   # B starts `lead` floats into its allocation
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    big = rng.standard_normal(lead + n * k).astype(np.float32)
+    da, dbig = ctx.move_tensor(CPUTensor.from_array(a)), ctx.move_tensor(CPUTensor.from_array(big))
+    dy = ctx.empty_tensor([m, n])
+    d = GemmDesc(batch=1, m=m, n=n, k=k, sab=0, sa0=k, sa1=1, sbb=0, sb0=1, sb1=k, sc0=0, sc1=0, alpha=1.0, beta=0.0,
+                 relu=0)
+
+    def gemm_at_offset():
+        ctx._call("wdc_gemm", byref(d), c_void_p(da.ptr), c_void_p(dbig.ptr + 4 * lead), None, c_void_p(dy.ptr))
+        return dy.get_data().reshape(m, n).copy()
+
+    b = big[lead:].reshape(n, k)
+    assert max_err_rel_linf(gemm_at_offset(), a @ b.T) <= TOL
+    big2 = rng.standard_normal(lead + n * k).astype(np.float32)
+    dbig.set_data(big2)                                  # upload from the base of the allocation
+    assert max_err_rel_linf(gemm_at_offset(), a @ big2[lead:].reshape(n, k).T) <= TOL
+    ctx.unary(16, dbig, dbig)                            # Relu in place over the whole allocation, from its base
+    b3 = np.maximum(big2[lead:], 0).reshape(n, k)
+    y3 = gemm_at_offset()
+    assert max_err_rel_linf(y3, a @ b3.T) <= TOL
+    # Y = A B^T + Y through the public entry point: C == Y
+    d2 = GemmDesc(batch=1, m=m, n=n, k=k, sab=0, sa0=k, sa1=1, sbb=0, sb0=1, sb1=k, sc0=n, sc1=1, alpha=1.0, beta=1.0,
+                  relu=0)
+    ctx._call("wdc_gemm", byref(d2), c_void_p(da.ptr), c_void_p(dbig.ptr + 4 * lead), c_void_p(dy.ptr), c_void_p(dy.ptr))
+    assert max_err_rel_linf(dy.get_data().reshape(m, n), 2.0 * (a.astype(np.float64) @ b3.T)) <= TOL
+    for t in (da, dbig, dy):
+        t.dispose()
+
+
+def test_captured_graph_goes_stale_when_its_weight_is_rewritten(cuda_context):
+    """A captured run holds the addresses of the cached weight splits.  Rewriting the weight drops the split, so a
+    replay would read freed memory: wdc_graph_launch must refuse instead, and a fresh capture works again."""
+    from webdnn_b200.backend import CPUTensor
+    from webdnn_b200.lib import CudaBackendError, GemmDesc
+    ctx = cuda_context
+    rng = np.random.default_rng(16)
+    m, n, k = 128, 64, 64
+    a = rng.standard_normal((m, k)).astype(np.float32)
+    b = rng.standard_normal((n, k)).astype(np.float32)
+    da, db = ctx.move_tensor(CPUTensor.from_array(a)), ctx.move_tensor(CPUTensor.from_array(b))
+    dy = ctx.empty_tensor([m, n])
+    d = GemmDesc(batch=1, m=m, n=n, k=k, sab=0, sa0=k, sa1=1, sbb=0, sb0=1, sb1=k, sc0=0, sc1=0, alpha=1.0, beta=0.0,
+                 relu=0)
+    ctx.gemm(d, da, db, None, dy)          # one-time split happens here
+    ctx.capture_begin()
+    ctx.gemm(d, da, db, None, dy)
+    g = ctx.capture_end()
+    ctx.graph_launch(g)
+    assert max_err_rel_linf(dy.get_data().reshape(m, n), a @ b.T) <= TOL
+    b2 = rng.standard_normal((n, k)).astype(np.float32)
+    db.set_data(b2)
+    with pytest.raises(CudaBackendError, match="capture the run again"):
+        ctx.graph_launch(g)
+    ctx.graph_destroy(g)
+    ctx.gemm(d, da, db, None, dy)
+    ctx.capture_begin()
+    ctx.gemm(d, da, db, None, dy)
+    g = ctx.capture_end()
+    ctx.graph_launch(g)
+    assert max_err_rel_linf(dy.get_data().reshape(m, n), a @ b2.T) <= TOL
+    ctx.graph_destroy(g)
+    for t in (da, db, dy):
         t.dispose()
 
 
@@ -241,8 +346,7 @@ def test_split_reduction(cuda_context, n, cin, cout, size, k, stride, pad, res):
     warm.dispose()
     outs = []
     for no_split in (False, True):
-        if no_split:
-            os.environ["WDC_TC_NO_SPLITK"] = "1"
+        ctx.set_option("split_k", 0 if no_split else 1)
         try:
             dy = ctx.empty_tensor([n, cout, oh, ow], layout="nhwc")
             before = ctx.stats()["launches"]
@@ -251,7 +355,7 @@ def test_split_reduction(cuda_context, n, cin, cout, size, k, stride, pad, res):
             outs.append((ctx.canonical(dy).get_data().reshape(n, cout, oh, ow), launches))
             dy.dispose()
         finally:
-            os.environ.pop("WDC_TC_NO_SPLITK", None)
+            ctx.set_option("split_k", 1)
     (split, l_split), (single, l_single) = outs
     assert l_split == l_single + 1, (l_split, l_single)    # the reduction pass really ran
     assert max_err_rel_linf(split, want) <= TOL

@@ -243,3 +243,21 @@ def test_layernorm_chain_with_an_outside_consumer_is_left_alone():
     model_transform(m, ["cuda", "cpu"])
     types = [n.op_type for n in m.graph.node]
     assert "CudaLayerNorm" not in types and types.count("ReduceMean") == 2
+
+
+def test_lstm_rejects_what_the_kernels_do_not_implement():
+    """Non-default activations, clip, layout=1, input_forget and a reverse direction must raise at initialize():
+    the kernels compute the operator's defaults only and would otherwise return the default's numbers."""
+    from webdnn_b200.operators.cuda import CudaLSTM
+    ok = onnx_io.make_node("LSTM", ["x", "w", "r"], ["y"], hidden_size=8, direction="forward",
+                           activations=["Sigmoid", "Tanh", "Tanh"])
+    CudaLSTM().initialize(ok.attribute)
+    for bad in (dict(activations=["Relu", "Tanh", "Tanh"]), dict(clip=3.0), dict(layout=1), dict(input_forget=1),
+                dict(direction="reverse"), dict(activation_alpha=[0.5])):
+        node = onnx_io.make_node("LSTM", ["x", "w", "r"], ["y"], hidden_size=8, **bad)
+        with pytest.raises(ValueError):
+            CudaLSTM().initialize(node.attribute)
+    # the attribute list survives the wire format
+    rt = onnx_io.decode_model(onnx_io.encode_model(onnx_io.Model(onnx_io.Graph("g", [ok], [], [], []))))
+    acts = [a for a in rt.graph.node[0].attribute if a.name == "activations"][0]
+    assert [s.decode() for s in acts.strings] == ["Sigmoid", "Tanh", "Tanh"]

@@ -1,4 +1,4 @@
-"""GPU: the allocation-free LSTM entry point against the regular one, through the C ABI.
+"""GPU: the allocation-free LSTM entry point against the CPU oracle and the regular entry point, through the C ABI.
 
 wdc_lstm_static exists for hosts that may not allocate device memory while running (their own memory pool owns the
 GPU, a real-time loop, a sandbox): its scratch is a fixed array inside the library.  This file is named so that
@@ -12,22 +12,26 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 
+LSTM_TOL = 1e-3   # the LSTM tolerance of the suite, relative to the output's largest magnitude
 
-def _run(ctx, entry, x, w, r, b):
+
+def _upload(ctx, arrays):
     from webdnn_b200.backend import CPUTensor
-    T, Bt, I = x.shape
-    H = r.shape[-1]
-    dx, dw, dr, db = (ctx.move_tensor(CPUTensor.from_array(a)) for a in (x, w, r, b))
+    return [ctx.move_tensor(CPUTensor.from_array(a)) for a in arrays]
+
+
+def _call(ctx, entry, dev_in, shape):
+    """One call of `entry` on resident operands; returns the three output tensors (still on the device)."""
+    T, Bt, I, H = shape
+    dx, dw, dr, db = dev_in
     y, yh, yc = ctx.empty_tensor([T, 1, Bt, H]), ctx.empty_tensor([1, Bt, H]), ctx.empty_tensor([1, Bt, H])
     p = lambda t: c_void_p(t.ptr)
     ctx._call(entry, p(dx), p(dw), p(dr), p(db), None, None, p(y), p(yh), p(yc), T, Bt, I, H)
-    out = [t.get_data().copy() for t in (y, yh, yc)]
-    for t in (dx, dw, dr, db, y, yh, yc):
-        t.dispose()
-    return out
+    return [y, yh, yc]
 
 
-def test_static_scratch_lstm_matches_arena_lstm_twice(cuda_context):
+def test_static_scratch_lstm_matches_oracle_twice(cuda_context):
+    from oracle import ops as oracle_ops
     ctx = cuda_context
     rng = np.random.default_rng(21)
     T, Bt, I, H = 12, 16, 64, 96
@@ -37,16 +41,30 @@ def test_static_scratch_lstm_matches_arena_lstm_twice(cuda_context):
     b = rng.uniform(-lim, lim, (1, 8 * H)).astype(np.float32)
     for call in range(2):  # second call: different input, scratch still holds the first call's last step
         x = rng.standard_normal((T, Bt, I)).astype(np.float32)
-        want = _run(ctx, "wdc_lstm", x, w, r, b)
-        allocs_before = ctx.stats()["allocs"]
-        reserved_before = ctx.stats()["reserved_bytes"]
-        dx_tensors = 7  # the test's own input/output tensors are the only arena allocations
-        got = _run(ctx, "wdc_lstm_static", x, w, r, b)
-        assert ctx.stats()["allocs"] - allocs_before == dx_tensors
-        assert ctx.stats()["reserved_bytes"] == reserved_before
-        for g, e in zip(got, want):
+        oracle = oracle_ops.lstm(x, w[0], r[0], b[0])
+        dev_in = _upload(ctx, (x, w, r, b))
+        arena_outs = _call(ctx, "wdc_lstm", dev_in, (T, Bt, I, H))
+        arena = [t.get_data().copy() for t in arena_outs]
+        for t in arena_outs:
+            t.dispose()
+        ctx.sync()
+        before = ctx.stats(device_memory=True)
+        outs = _call(ctx, "wdc_lstm_static", dev_in, (T, Bt, I, H))
+        ctx.sync()
+        after = ctx.stats(device_memory=True)
+        # the three output tensors of this test are the only arena allocations, the arena did not grow, and
+        # (second call, when every module is certainly loaded) the GPU's free memory did not move at all
+        assert after["allocs"] - before["allocs"] == 3
+        assert after["reserved_bytes"] == before["reserved_bytes"]
+        if call == 1:
+            assert after["device_free_bytes"] == before["device_free_bytes"]
+        got = [t.get_data().copy() for t in outs]
+        for t in dev_in + outs:
+            t.dispose()
+        for g, e, a in zip(got, oracle, arena):
             scale = np.abs(e).max()
-            assert np.abs(g.astype(np.float64) - e).max() <= 1e-3 * scale, call  # the LSTM tolerance of the suite
+            assert np.abs(g.astype(np.float64) - e.reshape(g.shape)).max() <= LSTM_TOL * scale, ("oracle", call)
+            assert np.abs(g.astype(np.float64) - a).max() <= LSTM_TOL * scale, ("wdc_lstm", call)
 
 
 def test_static_scratch_limit_is_enforced(cuda_context):

@@ -234,6 +234,8 @@ class WebDNNCudaContext:
         self.arena_bytes = arena_bytes
         self._L = None
         self.handle = None
+        self.precision = "tf32x3"
+        self.profile = False      # backendOptions.cuda.profile: NVTX range "name(opType)" around every node
 
     # --- lifecycle
     def initialize(self) -> None:
@@ -279,15 +281,36 @@ class WebDNNCudaContext:
     def stream_handle(self) -> int:
         return self._L.lib.wdc_stream(self.handle)
 
-    def stats(self) -> Dict[str, int]:
-        out = (ctypes.c_int64 * 9)()
-        self._call("wdc_stats", out, 9)
+    def stats(self, device_memory: bool = False) -> Dict[str, int]:
+        """Arena and traffic counters; with device_memory also the GPU's free / total bytes (cudaMemGetInfo)."""
+        n = 11 if device_memory else 9
+        out = (ctypes.c_int64 * n)()
+        self._call("wdc_stats", out, n)
         keys = ["bytes_in_use", "high_water_bytes", "reserved_bytes", "allocs", "frees", "launches",
-                "h2d_bytes", "d2h_bytes", "tensor_core_launches"]
-        return dict(zip(keys, list(out)))
+                "h2d_bytes", "d2h_bytes", "tensor_core_launches", "device_free_bytes", "device_total_bytes"]
+        return dict(zip(keys[:n], list(out)))
 
     def reset_stats(self) -> None:
         self._call("wdc_reset_stats")
+
+    PRECISIONS = {"tf32x3": 0, "tf32x1": 1}
+
+    def set_option(self, name: str, value: int) -> None:
+        """wdc_set_option: "precision" (0 tf32x3 / 1 tf32x1), "split_k", "pdl", "nvtx"."""
+        self._call("wdc_set_option", name.encode("utf-8"), int(value))
+
+    def set_precision(self, precision: str) -> None:
+        """backendOptions.cuda.precision: "tf32x3" (default, fp32-class accuracy) or "tf32x1"."""
+        if precision not in self.PRECISIONS:
+            raise ValueError(f"precision must be one of {sorted(self.PRECISIONS)}, not {precision!r}")
+        self.set_option("precision", self.PRECISIONS[precision])
+        self.precision = precision
+
+    def range_push(self, name: str) -> None:
+        self._call("wdc_range_push", name.encode("utf-8"))
+
+    def range_pop(self) -> None:
+        self._call("wdc_range_pop")
 
     def profile_enable(self, on: bool) -> None:
         self._call("wdc_profile_enable", int(on))
@@ -318,6 +341,9 @@ class WebDNNCudaContext:
     def asserts_cuda_tensor(self, t) -> None:
         if not isinstance(t, CudaTensor):
             raise TypeError("tensor is not CudaTensor")
+        if t.context is not self:
+            # another context's arena (possibly another GPU): its memory is not ordered with this stream
+            raise TypeError("CudaTensor belongs to another cuda context")
 
     def asserts_cuda_tensor_array(self, tensors) -> None:
         for t in tensors:

@@ -57,7 +57,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
             sys.stderr.write(f"--- {src}\n{out}\n")
     if failed:
         raise RuntimeError("nvcc compilation failed")
-    cmd = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-lcuda", "-gencode", "arch=compute_100a,code=sm_100a"]
+    cmd = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-lcuda", "-ldl", "-gencode", "arch=compute_100a,code=sm_100a"]
     subprocess.run(cmd, check=True)
     return LIB_PATH
 

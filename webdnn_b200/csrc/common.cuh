@@ -46,6 +46,13 @@ struct wdc_context {
   // arena that the finished graph keeps: replays reuse exactly the addresses the capture saw.
   wdc_arena* capture_arena = nullptr;
   std::vector<wdc_arena*> graph_arenas;   // arenas owned by finished graphs (and by failed captures)
+  std::vector<struct wdc_graph*> live_graphs;   // finished graphs not yet destroyed
+  int64_t split_seq = 0;                  // creation counter of the tensor-core path's cached operand splits
+  // wdc_set_option
+  int opt_precision = 0;                  // 0: tf32x3 (fp32-class accuracy), 1: tf32x1 (one pass, ~1e-3 relative)
+  int opt_split_k = 1;                    // 1: small outputs with long reductions may be cut into K ranges
+  int opt_pdl = 1;                        // 1: contraction launches use programmatic dependent launch
+  int opt_nvtx = 0;                       // 1: wdc_range_push / wdc_range_pop emit NVTX ranges
   // second stream for host-to-device transfers that overlap the kernels of `stream`
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t copy_fence = nullptr;             // recorded on `stream`, waited by `copy_stream`
@@ -126,10 +133,21 @@ int wdc_tc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, cons
 int wdc_tc_gemm(wdc_context* ctx, const wdc_gemm_desc* d, const float* A, const float* B,
                 const float* C, float* Y);
 void wdc_tc_destroy(wdc_context* ctx);
-// Drops the cached hi/lo split of a weight matrix when its buffer is freed or overwritten.
-void wdc_tc_evict(wdc_context* ctx, const void* ptr);
-// Every entry point that writes device memory reports the start of its output here: operand splits
-// cached by the tensor-core path for a buffer that contains that address are dropped.
-inline void wdc_note_write(wdc_context* ctx, const void* ptr) {
-  if (ctx && ptr && ctx->tc_state) wdc_tc_evict(ctx, ptr);
+// Looks up the device address of wdc_lstm_static's scratch array for ctx's (current) device (lstm.cu).
+int wdc_lstm_static_setup(wdc_context* ctx);
+// Drops every cached hi/lo split whose source (weight matrix or per-channel scale vector) overlaps the
+// written range.  The range is [ptr, ptr + bytes) widened to the whole arena allocation that contains ptr:
+// a write may start before a cached operand and still cover it, and a kernel never writes across two
+// allocations, so "anything in the allocation that was written to" is the safe extent.  For memory that
+// did not come from wdc_alloc only the given byte range counts (bytes == 0: the start address alone).
+void wdc_tc_evict(wdc_context* ctx, const void* ptr, int64_t bytes);
+// Every entry point that writes device memory reports its output here (the start; the length where it is
+// cheap to know).
+inline void wdc_note_write(wdc_context* ctx, const void* ptr, int64_t bytes = 0) {
+  if (ctx && ptr && ctx->tc_state) wdc_tc_evict(ctx, ptr, bytes);
 }
+// Extent [*lo, *hi) of the live arena allocation (of any arena of the context) that contains p; false if none.
+bool wdc_arena_extent(wdc_context* ctx, const void* p, const char** lo, const char** hi);
+// A cached split with creation number `born` has been dropped: captured graphs recorded while it existed
+// hold its address and must not be replayed any more (wdc_graph_launch then fails).
+void wdc_graphs_note_evicted(wdc_context* ctx, int64_t born);

@@ -3,6 +3,8 @@
 #include <cstdio>
 #include <cstring>
 
+#include <nvtx3/nvToolsExt.h>   // header-only: ranges reach a profiler only when one has injected its library
+
 #include "common.cuh"
 
 static std::string g_last_error;  // for failures before a context exists
@@ -49,6 +51,8 @@ extern "C" int wdc_device_count(int* count) {
   return WDC_OK;
 }
 
+__global__ void fill_u32_kernel(uint32_t* dst, uint32_t v, int64_t n);
+
 extern "C" int wdc_create(int device, int64_t arena_limit_bytes, wdc_context** out) {
   if (!out) return wdc_fail(nullptr, WDC_ERR_INVALID, "wdc_create: null output");
   *out = nullptr;
@@ -80,6 +84,18 @@ extern "C" int wdc_create(int device, int64_t arena_limit_bytes, wdc_context** o
     return s;
   }
   memset(ctx->status_word_host, 0, 256);
+  // wdc_lstm_static's scratch array: its address is resolved (and its module loaded, which is when the
+  // driver sets the array aside) here, so that the entry point itself never reaches an allocator
+  int s = wdc_lstm_static_setup(ctx);
+  if (s == WDC_OK) {
+    cudaFuncAttributes fa;   // this file's module too (wdc_fill_u32 is part of that entry point's sequence)
+    s = wdc_check_cuda(ctx, cudaFuncGetAttributes(&fa, fill_u32_kernel), "cudaFuncGetAttributes");
+  }
+  if (s != WDC_OK) {
+    g_last_error = ctx->last_error;
+    wdc_destroy(ctx);
+    return s;
+  }
   *out = ctx;
   return WDC_OK;
 }
@@ -177,10 +193,33 @@ extern "C" int wdc_alloc(wdc_context* ctx, int64_t bytes, void** dptr) {
   return WDC_OK;
 }
 
+bool wdc_arena_extent(wdc_context* ctx, const void* p, const char** lo, const char** hi) {
+  std::lock_guard<std::mutex> lk(ctx->mu);
+  const char* q = (const char*)p;
+  auto search = [&](wdc_arena* a) -> bool {
+    for (auto& s : a->slabs) {
+      if (q < s.base || q >= s.base + s.size) continue;
+      auto it = s.blocks.upper_bound((int64_t)(q - s.base));
+      if (it == s.blocks.begin()) return false;
+      --it;
+      if (it->second.free) return false;
+      *lo = s.base + it->first;
+      *hi = *lo + it->second.size;
+      return true;
+    }
+    return false;
+  };
+  if (search(&ctx->arena)) return true;
+  if (ctx->capture_arena && search(ctx->capture_arena)) return true;
+  for (wdc_arena* g : ctx->graph_arenas)
+    if (search(g)) return true;
+  return false;
+}
+
 extern "C" int wdc_free(wdc_context* ctx, void* dptr) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_free: null context");
   if (!dptr) return WDC_OK;
-  wdc_tc_evict(ctx, dptr);
+  wdc_tc_evict(ctx, dptr, 0);   // widened to the block's extent
   std::lock_guard<std::mutex> lk(ctx->mu);
   wdc_arena* owner = &ctx->arena;
   if (ctx->arena.live.find(dptr) == ctx->arena.live.end()) {
@@ -244,7 +283,7 @@ extern "C" int wdc_upload(wdc_context* ctx, void* dst, const void* host, int64_t
     return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_upload: bad argument");
   if (bytes == 0) return WDC_OK;
   DeviceGuard g(ctx->device);
-  wdc_tc_evict(ctx, dst);
+  wdc_tc_evict(ctx, dst, bytes);
   WDC_CUDA(ctx, cudaMemcpyAsync(dst, host, (size_t)bytes, cudaMemcpyHostToDevice, ctx->stream));
   ctx->h2d_bytes += bytes;
   return WDC_OK;
@@ -259,7 +298,7 @@ extern "C" int wdc_upload_async(wdc_context* ctx, void* dst, const void* host, i
     WDC_CUDA(ctx, cudaEventCreateWithFlags(&ctx->copy_fence, cudaEventDisableTiming));
     for (auto& ev : ctx->upload_done) WDC_CUDA(ctx, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
   }
-  wdc_tc_evict(ctx, dst);
+  wdc_tc_evict(ctx, dst, bytes);
   // dst comes from the arena, whose reuse is ordered on `stream`: the transfer may start only after
   // everything already queued there (a previous tenant of this memory may still be read)
   WDC_CUDA(ctx, cudaEventRecord(ctx->copy_fence, ctx->stream));
@@ -291,7 +330,17 @@ struct wdc_graph {
   cudaGraph_t graph = nullptr;
   cudaGraphExec_t exec = nullptr;
   wdc_arena* arena = nullptr;  // owns every buffer the captured launches touch that was allocated while capturing
+  // The recorded launches hold the addresses of the tensor-core path's cached operand splits (hi/lo copies of
+  // the weights).  split_seq = the context's split counter when the capture ended: if a split that is that old
+  // is dropped later (its weight was rewritten or freed), the graph would read freed memory, so it goes stale.
+  int64_t split_seq = 0;
+  bool stale = false;
 };
+
+void wdc_graphs_note_evicted(wdc_context* ctx, int64_t born) {
+  for (wdc_graph* g : ctx->live_graphs)
+    if (born <= g->split_seq) g->stale = true;
+}
 
 extern "C" int wdc_capture_begin(wdc_context* ctx) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_capture_begin: null context");
@@ -331,7 +380,9 @@ extern "C" int wdc_capture_end(wdc_context* ctx, wdc_graph** out) {
   gr->graph = graph;
   gr->exec = exec;
   gr->arena = arena;
+  gr->split_seq = ctx->split_seq;
   ctx->graph_arenas.push_back(arena);
+  ctx->live_graphs.push_back(gr);
   *out = gr;
   return WDC_OK;
 }
@@ -339,6 +390,9 @@ extern "C" int wdc_capture_end(wdc_context* ctx, wdc_graph** out) {
 extern "C" int wdc_graph_launch(wdc_context* ctx, wdc_graph* graph) {
   if (!ctx || !graph || !graph->exec) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_graph_launch: bad argument");
   if (ctx->capture_arena) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_graph_launch: a capture is open");
+  if (graph->stale)
+    return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_graph_launch: a weight or scale buffer the captured run uses was "
+                    "rewritten or freed after the capture; destroy this graph and capture the run again");
   DeviceGuard g(ctx->device);
   WDC_CUDA(ctx, cudaGraphLaunch(graph->exec, ctx->stream));
   ctx->n_launch++;
@@ -350,6 +404,8 @@ extern "C" int wdc_graph_destroy(wdc_context* ctx, wdc_graph* graph) {
   if (!graph) return WDC_OK;
   DeviceGuard g(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  for (size_t i = 0; i < ctx->live_graphs.size(); i++)
+    if (ctx->live_graphs[i] == graph) ctx->live_graphs.erase(ctx->live_graphs.begin() + i--);
   if (graph->exec) cudaGraphExecDestroy(graph->exec);
   if (graph->graph) cudaGraphDestroy(graph->graph);
   if (graph->arena) {
@@ -400,7 +456,7 @@ extern "C" int wdc_copy(wdc_context* ctx, void* dst, const void* src, int64_t by
     return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_copy: bad argument");
   if (bytes == 0) return WDC_OK;
   DeviceGuard g(ctx->device);
-  wdc_tc_evict(ctx, dst);
+  wdc_tc_evict(ctx, dst, bytes);
   WDC_CUDA(ctx, cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDeviceToDevice, ctx->stream));
   return WDC_OK;
 }
@@ -414,21 +470,62 @@ __global__ void fill_u32_kernel(uint32_t* dst, uint32_t v, int64_t n) {
 extern "C" int wdc_fill_u32(wdc_context* ctx, void* dst, uint32_t value, int64_t count) {
   if (!ctx || count < 0 || (count > 0 && !dst))
     return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_fill_u32: bad argument");
-  wdc_note_write(ctx, dst);
+  wdc_note_write(ctx, dst, count * 4);
   if (count == 0) return WDC_OK;
   DeviceGuard g(ctx->device);
   fill_u32_kernel<<<grid_for(ctx, count, 256), 256, 0, ctx->stream>>>((uint32_t*)dst, value, count);
   return wdc_check_launch(ctx, "fill_u32_kernel");
 }
 
+extern "C" int wdc_set_option(wdc_context* ctx, const char* name, int64_t value) {
+  if (!ctx || !name) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_set_option: null argument");
+  const std::string n(name);
+  if (n == "precision") {
+    if (value != 0 && value != 1)
+      return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_set_option: precision is 0 (tf32x3) or 1 (tf32x1), not %lld", (long long)value);
+    ctx->opt_precision = (int)value;
+  } else if (n == "split_k") {
+    ctx->opt_split_k = value != 0;
+  } else if (n == "pdl") {
+    ctx->opt_pdl = value != 0;
+  } else if (n == "nvtx") {
+    ctx->opt_nvtx = value != 0;
+  } else {
+    return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_set_option: unknown option '%s'", name);
+  }
+  return WDC_OK;
+}
+
+extern "C" int wdc_range_push(wdc_context* ctx, const char* name) {
+  if (!ctx || !name) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_range_push: null argument");
+  if (ctx->opt_nvtx) nvtxRangePushA(name);
+  return WDC_OK;
+}
+
+extern "C" int wdc_range_pop(wdc_context* ctx) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_range_pop: null context");
+  if (ctx->opt_nvtx) nvtxRangePop();
+  return WDC_OK;
+}
+
 extern "C" void* wdc_stream(wdc_context* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
 
 extern "C" int wdc_stats(wdc_context* ctx, int64_t* out, int n) {
   if (!ctx || !out || n < 0) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_stats: bad argument");
-  int64_t v[9] = {ctx->arena.in_use, ctx->arena.high_water, ctx->arena.reserved, ctx->n_alloc,
-                  ctx->n_free,       ctx->n_launch,         ctx->h2d_bytes,      ctx->d2h_bytes,
-                  ctx->n_tc_launch};
-  for (int i = 0; i < n && i < 9; i++) out[i] = v[i];
+  int64_t v[11] = {ctx->arena.in_use, ctx->arena.high_water, ctx->arena.reserved, ctx->n_alloc,
+                   ctx->n_free,       ctx->n_launch,         ctx->h2d_bytes,      ctx->d2h_bytes,
+                   ctx->n_tc_launch,  -1,                    -1};
+  if (n > 9) {   // device-wide figures (every process and library on the GPU counts), asked only when wanted
+    DeviceGuard g(ctx->device);
+    size_t free_b = 0, total_b = 0;
+    if (cudaMemGetInfo(&free_b, &total_b) == cudaSuccess) {
+      v[9] = (int64_t)free_b;
+      v[10] = (int64_t)total_b;
+    } else {
+      cudaGetLastError();
+    }
+  }
+  for (int i = 0; i < n && i < 11; i++) out[i] = v[i];
   return WDC_OK;
 }
 
@@ -470,7 +567,7 @@ extern "C" int wdc_peer_copy(wdc_context* dst_ctx, void* dst, wdc_context* src_c
                              int64_t bytes) {
   if (!dst_ctx || !src_ctx || bytes < 0 || (bytes > 0 && (!dst || !src)))
     return wdc_fail(dst_ctx, WDC_ERR_INVALID, "wdc_peer_copy: bad argument");
-  wdc_note_write(dst_ctx, dst);
+  wdc_note_write(dst_ctx, dst, bytes);
   if (bytes == 0) return WDC_OK;
   // Order the copy after everything already enqueued on the source stream, run it on the
   // destination stream.

@@ -51,6 +51,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <vector>
 
 #include "common.cuh"
 
@@ -80,6 +81,13 @@ constexpr int SHIFT_TAB = 2048;        // per-column addends kept in shared memo
 constexpr int KTAB = 512;             // K blocks whose gather offsets are tabulated in shared memory
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
+// Development knock-out switches exist only in a build with -DWDC_TC_DEVELOP; the shipped kernel has none.
+#ifdef WDC_TC_DEVELOP
+#define TC_DBG(p, bit) (((p).dbg & (bit)) != 0)
+#else
+#define TC_DBG(p, bit) false
+#endif
+
 struct TcProblem {
   // implicit GEMM geometry
   int64_t M;          // batch * out_h * out_w
@@ -106,7 +114,10 @@ struct TcProblem {
   int64_t res_stride;
   float alpha, shift_mul, res_mul;
   int relu;
-  int dbg;  // development switches (WDC_TC_DEBUG): 1 = no A loads, 2 = no epilogue memory traffic, 4 = no MMAs
+  int single_pass;    // 1: precision tf32x1 (one MMA per multiply-add on the truncated operands; no low parts)
+#ifdef WDC_TC_DEVELOP
+  int dbg;  // development knock-outs (WDC_TC_DEBUG): 1 = no A loads, 2 = no epilogue memory traffic, 4 = no MMAs
+#endif
   int* status;
 };
 
@@ -467,7 +478,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
           }
         }
         tmem_st16(a_hi + (uint32_t)(h * 16), hi);
-        tmem_st16(a_hi + 32u + (uint32_t)(h * 16), lo);
+        if (!p.single_pass) tmem_st16(a_hi + 32u + (uint32_t)(h * 16), lo);
       }
       // the shared-memory tile has been read into registers: hand the slot back to the loader
       __syncwarp();
@@ -586,7 +597,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         e.nchunks = left < 8 ? left : 8;
       }
       const int iy = riy + e.dy;
-      const bool rowok = !(p.dbg & 1) && rsrc != nullptr && (unsigned)iy < (unsigned)p.in_h;
+      const bool rowok = !TC_DBG(p, 1) && rsrc != nullptr && (unsigned)iy < (unsigned)p.in_h;
       const float* src = rsrc + e.off;
       if (p.c4) {
         // one K block = one filter row: chunk j is tap kx = j (the 4 channels of one pixel)
@@ -640,7 +651,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
                 const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                 for (int t = 0; t < 4; t++) {
-                  if (p.dbg & 8) { hi[c * 4 + t] = e[t]; lo[c * 4 + t] = 0.f; continue; }
+                  if (p.single_pass) { hi[c * 4 + t] = e[t]; lo[c * 4 + t] = 0.f; continue; }
                   // hi = e rounded to TF32 (add half an ulp of the 10-bit mantissa, clear the low 13
                   // bits): two full-rate integer ops instead of a quarter-rate cvt.  lo = e - hi is
                   // exact in fp32; the tensor core ignores the low 13 bits of a tf32 operand, which
@@ -650,9 +661,9 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
                   lo[c * 4 + t] = e[t] - hh;
                 }
               }
-              if (p.dbg & 16) continue;
+              if (TC_DBG(p, 16)) continue;
               tmem_st16(a_hi + (uint32_t)(h * 16), hi);
-              tmem_st16(a_hi + 32u + (uint32_t)(h * 16), lo);
+              if (!p.single_pass) tmem_st16(a_hi + 32u + (uint32_t)(h * 16), lo);
             }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -669,7 +680,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
-      const uint32_t bytes = 2u * (uint32_t)p.tile_n * BLOCK_K * 4u;
+      const uint32_t bytes = (p.single_pass ? 1u : 2u) * (uint32_t)p.tile_n * BLOCK_K * 4u;
       bool ok = true;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         int tile, sp, kb0, kbn;
@@ -688,7 +699,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
             kx0 = tap * p.ch_in + (kr - tap * p.cblocks) * BLOCK_K;
           }
           tma_load_2d(w_hi_ptr(stage), &map_w_hi, &ss->full_bar[stage], kx0, n0);
-          tma_load_2d(w_lo_ptr(stage), &map_w_lo, &ss->full_bar[stage], kx0, n0);
+          if (!p.single_pass) tma_load_2d(w_lo_ptr(stage), &map_w_lo, &ss->full_bar[stage], kx0, n0);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -724,7 +735,11 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
           for (int k = 0; k < BLOCK_K / 8; k++) {
             const uint64_t adv = (uint64_t)(k * 2);  // 8 tf32 = 32 bytes = 2 x 16-byte units of W
             const uint32_t acol = (uint32_t)(k * 8); // 8 TMEM columns of A
-            if (p.dbg & 4) continue;
+            if (TC_DBG(p, 4)) continue;
+            if (p.single_pass) {
+              umma_tf32_ts(d_tmem, a_hi + acol, dw_hi + adv, idesc, (in_seg | k) ? 1u : 0u);
+              continue;
+            }
             umma_tf32_ts(d_tmem, a_lo + acol, dw_hi + adv, idesc, (in_seg | k) ? 1u : 0u);
             umma_tf32_ts(d_tmem, a_hi + acol, dw_lo + adv, idesc, 1u);
             umma_tf32_ts(d_tmem, a_hi + acol, dw_hi + adv, idesc, 1u);
@@ -761,7 +776,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       const uint32_t chunk_bytes = 32u * (uint32_t)cw * 4u;
       const uint32_t swz = cw == 32 ? (uint32_t)(lane & 7) : 0u;   // 128B swizzle only for 128-byte rows
       const uint32_t row_off = (uint32_t)lane * (uint32_t)cw * 4u;
-      const bool use_res = p.residual != nullptr && !(p.dbg & 2);
+      const bool use_res = p.residual != nullptr && !TC_DBG(p, 2);
       int64_t k = 0;                                    // chunks handled by this warp so far
       if (use_res && lane == 0 && (int)blockIdx.x < total_tiles) {
         const int t0 = blockIdx.x;
@@ -881,7 +896,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
               __syncwarp();
               if (lane == 0) {
                 const int col = nbase + c * 32;
-                if (!(p.dbg & 2) && mrow0 < p.M && col < p.N) tma_store_2d(&map_y, sbuf, col, (int)store_row);
+                if (!TC_DBG(p, 2) && mrow0 < p.M && col < p.N) tma_store_2d(&map_y, sbuf, col, (int)store_row);
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the other buffer's store has read it
                 if (use_res) {
@@ -924,7 +939,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         for (int i = 0; i < 4; i++) {
           const int64_t m = mrow0 + tr + 8 * i;
           float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (p.residual && !(p.dbg & 2) && m < p.M && col < p.N) {
+          if (p.residual && !TC_DBG(p, 2) && m < p.M && col < p.N) {
             const float* rp = p.residual + m * p.res_stride + col;
             if (vec) r = __ldg(reinterpret_cast<const float4*>(rp));
             else {
@@ -941,7 +956,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         const int buf = (int)(seg % NBUF);
         if (s == nseg - 1) {
           load_res(0, rcur);  // in flight while the last segment finishes
-          if (p.residual && !(p.dbg & 2)) {  // pull the rest of the residual tile towards L2
+          if (p.residual && !TC_DBG(p, 2)) {  // pull the rest of the residual tile towards L2
             for (int c = 1; c < nchunks; c++) {
               const int col = nbase + c * 16 + tc;
 #pragma unroll
@@ -982,7 +997,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
                 make_float4(acc[c * 16 + j], acc[c * 16 + j + 1], acc[c * 16 + j + 2], acc[c * 16 + j + 3]);
           __syncwarp();
           const int col = nbase + c * 16 + tc;
-          if (col < p.N && !(p.dbg & 2)) {
+          if (col < p.N && !TC_DBG(p, 2)) {
             float sc[4] = {p.alpha, p.alpha, p.alpha, p.alpha}, sh[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int e = 0; e < 4; e++) {
@@ -1198,6 +1213,7 @@ struct WeightEntry {
   float* lo = nullptr;
   int64_t rows = 0, k = 0;
   int64_t src_bytes = 0;  // size of the caller's weight buffer the split was made from
+  int64_t born = 0;       // creation number (wdc_context::split_seq), for the staleness of captured graphs
   // tensor maps of the split copies for tile heights of 32, 64 and 128 weight rows (index log2(n / 32)),
   // encoded when a launch first asks for that height
   CUtensorMap map_hi[3], map_lo[3];
@@ -1261,9 +1277,11 @@ int get_weight(wdc_context* ctx, const float* w, const float* scale, float alpha
                     "a weight operand was seen for the first time while capturing: run the sequence once before "
                     "wdc_capture_begin, so that the one-time split is not part of the recorded run");
   if (it != st->weights.end()) {
-    wdc_free(ctx, it->second.hi);
-    wdc_free(ctx, it->second.lo);
+    WeightEntry old = it->second;
     st->weights.erase(it);
+    wdc_graphs_note_evicted(ctx, old.born);
+    wdc_free(ctx, old.hi);
+    wdc_free(ctx, old.lo);
   }
   WeightEntry e;
   e.rows = rows;
@@ -1290,6 +1308,7 @@ int get_weight(wdc_context* ctx, const float* w, const float* scale, float alpha
     wdc_free(ctx, e.lo);
     return s;
   }
+  e.born = ++ctx->split_seq;
   auto ins = st->weights.emplace(key, e);
   *out = &ins.first->second;
   return WDC_OK;
@@ -1334,7 +1353,7 @@ bool tc_ready(wdc_context* ctx) {
 // pixel), traversal strides = the convolution's strides.  Returns false when the geometry does not
 // fit the map's fields; the caller then launches the gathering kernel.
 bool encode_a_map(TcState* st, const TcProblem& p, const float* x, CUtensorMap* map) {
-  if (!st->encode_im2col || (p.dbg & 32)) return false;
+  if (!st->encode_im2col || TC_DBG(p, 32)) return false;
   if (p.c4 && p.k_w > 8) return false;
   const int64_t hw = (int64_t)p.out_h * p.out_w;
   const int64_t images = (p.M + hw - 1) / hw;
@@ -1422,7 +1441,7 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
     // a split reduction needs the TMA paths on both sides (checked again below) and no first-layer mode
     const bool may_split = !p.c4 && p.N % 4 == 0 && p.M < (1ll << 27) && tc_state(ctx)->encode_im2col != nullptr &&
                            (((uintptr_t)p.shift | (uintptr_t)p.residual | (uintptr_t)y) & 15) == 0 &&
-                           (!p.residual || p.res_stride % 4 == 0) && !getenv("WDC_TC_NO_SPLITK");
+                           (!p.residual || p.res_stride % 4 == 0) && ctx->opt_split_k;
     choose_tiling(ctx, p.M, p.N, p.kblocks, may_split, &p.tile_n, &p.splits);
   }
   const int mi = p.tile_n == 128 ? 2 : p.tile_n == 64 ? 1 : 0;
@@ -1440,6 +1459,7 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
   p.tiles_m = (int)ceil_div64(p.M, TILE_M);
   p.tiles_n = (int)ceil_div64(p.N, p.tile_n);
   p.status = ctx->status_word;
+#ifdef WDC_TC_DEVELOP
   {
     static int dbg = -1;
     if (dbg < 0) {
@@ -1448,6 +1468,8 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
     }
     p.dbg = dbg;
   }
+#endif
+  p.single_pass = ctx->opt_precision == 1 ? 1 : 0;
   TcState* st = tc_state(ctx);
   p.m_pad = (int64_t)p.tiles_m * TILE_M;
   p.kbs = (p.kblocks + p.splits - 1) / p.splits;
@@ -1477,7 +1499,7 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
   CUtensorMap map_y = w_map_hi, map_res = w_map_hi;
   {
     const int ncols = p.tile_n / 2, cw = ncols < 32 ? ncols : 32;
-    bool can = (p.N % 4 == 0) && p.M < (1ll << 31) && !(p.dbg & 64) && (((uintptr_t)p.scale | (uintptr_t)p.shift) & 15) == 0;
+    bool can = (p.N % 4 == 0) && p.M < (1ll << 31) && !TC_DBG(p, 64) && (((uintptr_t)p.scale | (uintptr_t)p.shift) & 15) == 0;
     if (can) {
       if (p.splits > 1) can = encode_rows_map(st, &map_y, ws, (int64_t)p.splits * p.m_pad, p.N, p.N, cw) == 0;
       else can = encode_rows_map(st, &map_y, y, p.M, p.N, p.N, cw) == 0;
@@ -1514,24 +1536,35 @@ bool aligned16(const void* p) { return (((uintptr_t)p) & 15) == 0; }
 
 }  // namespace
 
-void wdc_tc_evict(wdc_context* ctx, const void* ptr) {
+void wdc_tc_evict(wdc_context* ctx, const void* ptr, int64_t bytes) {
   if (!ctx->tc_state) return;
   TcState* st = (TcState*)ctx->tc_state;
   if (st->weights.empty()) return;
-  // entries made from a buffer that contains ptr, as weights or as the per-channel scale
-  const char* q = (const char*)ptr;
+  // written extent: the byte range, widened to the arena allocation that contains its start
+  const char* lo = (const char*)ptr;
+  const char* hi = lo + (bytes > 0 ? bytes : 1);
+  const char *blo, *bhi;
+  if (wdc_arena_extent(ctx, ptr, &blo, &bhi)) {
+    if (blo < lo) lo = blo;
+    if (bhi > hi) hi = bhi;
+  }
+  // entries whose weight buffer or per-channel scale vector overlaps [lo, hi)
+  std::vector<WeightEntry> dropped;
   for (auto it = st->weights.begin(); it != st->weights.end();) {
     const char* w = (const char*)it->first.w;
     const char* sc = (const char*)it->first.scale;
-    const bool hit = (q >= w && q < w + it->second.src_bytes) || (sc && q >= sc && q < sc + it->second.rows * 4);
+    const bool hit = (w < hi && lo < w + it->second.src_bytes) || (sc && sc < hi && lo < sc + it->second.rows * 4);
     if (hit) {
-      WeightEntry e = it->second;
+      dropped.push_back(it->second);
       it = st->weights.erase(it);
-      wdc_free(ctx, e.hi);
-      wdc_free(ctx, e.lo);
     } else {
       ++it;
     }
+  }
+  for (const WeightEntry& e : dropped) {   // wdc_free re-enters this function: the map is already consistent
+    wdc_graphs_note_evicted(ctx, e.born);
+    wdc_free(ctx, e.hi);
+    wdc_free(ctx, e.lo);
   }
 }
 
@@ -1566,7 +1599,7 @@ int wdc_tc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, cons
   // 16-byte chunk is one pixel, and lay the filter out as 8 taps x 4 channels per filter row.
   float* x4 = nullptr;
   // stride-2 stems: pad the rows physically so that two taps are one 32-byte pixel pair
-  const bool pairs = d->stride_w == 2 && d->dil_w == 1 && tc_state(ctx)->encode_im2col != nullptr && !(getenv("WDC_TC_NO_PAIRS"));
+  const bool pairs = d->stride_w == 2 && d->dil_w == 1 && tc_state(ctx)->encode_im2col != nullptr;
   const int wp = pairs ? (int)(2 * d->out_w + 6) : (int)d->in_w;
   const int64_t pixels = d->batch * d->in_h * wp;
   int s = wdc_alloc(ctx, pixels * 16, (void**)&x4);

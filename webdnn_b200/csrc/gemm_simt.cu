@@ -16,6 +16,7 @@ struct SimtProblem {
   int64_t sab, sa0, sa1, sbb, sb0, sb1, sc0, sc1;
   float alpha, beta;
   int has_c;
+  int c_in_y;  // 1: the C operand IS the output (Y = alpha*A*B + beta*Y): read through Y with plain loads
   // conv addressing (x NHWC, w [ch_out][k_h][k_w][cig])
   int64_t in_h, in_w, ch_in, cig, cog, k_h, k_w, out_h, out_w, stride_h, stride_w, pad_t, pad_l,
       dil_h, dil_w, ch_out;
@@ -136,8 +137,11 @@ __global__ void __launch_bounds__(256) simt_contract_kernel(SimtProblem p, const
           if (residual) v += __ldg(residual + o);
         } else {
           v *= p.alpha;
-          if (p.has_c) v += __ldg(C + m * p.sc0 + n * p.sc1) * p.beta;
           o = (bz * p.M + m) * p.N + n;
+          // In-place accumulation reads the old value through the output pointer itself: the read-only
+          // data path (__ldg) and a second __restrict__ pointer must never see memory this kernel writes.
+          if (p.c_in_y) v += Y[o] * p.beta;
+          else if (p.has_c) v += __ldg(C + m * p.sc0 + n * p.sc1) * p.beta;
         }
         if (p.relu) v = v > 0.f ? v : (v == v ? 0.f : v);
         Y[o] = v;
@@ -158,6 +162,14 @@ static int launch_simt(wdc_context* ctx, const SimtProblem& p, const float* A, c
   return wdc_check_launch(ctx, "simt_contract_kernel");
 }
 
+// Makes the driver load this file's module on the current device (lazy module loading would otherwise do it
+// at the first launch).
+int wdc_simt_preload(wdc_context* ctx) {
+  cudaFuncAttributes fa;
+  WDC_CUDA(ctx, cudaFuncGetAttributes(&fa, simt_contract_kernel));
+  return WDC_OK;
+}
+
 int wdc_simt_gemm(wdc_context* ctx, const wdc_gemm_desc* d, const float* A, const float* B, const float* C,
                   float* Y) {
   SimtProblem p = {};
@@ -167,6 +179,14 @@ int wdc_simt_gemm(wdc_context* ctx, const wdc_gemm_desc* d, const float* A, cons
   p.sbb = d->sbb; p.sb0 = d->sb0; p.sb1 = d->sb1;
   p.sc0 = d->sc0; p.sc1 = d->sc1;
   p.alpha = d->alpha; p.beta = d->beta; p.has_c = C != nullptr; p.relu = d->relu;
+  if (C == Y && C != nullptr) {
+    // accumulate into Y: only the element-for-element case is meaningful (each output reads its own old value)
+    if (d->batch != 1 || d->sc0 != d->n || d->sc1 != 1)
+      return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_gemm: C may alias Y only as a dense [m, n] matrix of a single batch");
+    p.c_in_y = 1;
+    p.has_c = 0;
+    C = nullptr;
+  }
   return launch_simt(ctx, p, A, B, C, nullptr, nullptr, nullptr, Y);
 }
 
@@ -195,7 +215,8 @@ extern "C" int wdc_gemm(wdc_context* ctx, const wdc_gemm_desc* d, const float* A
   WDC_REQUIRE(ctx, Y && (d->k == 0 || (A && B)), "wdc_gemm: null buffer");
   DeviceGuard g(ctx->device);
   ProfScope prof(ctx, 2.0 * (double)d->batch * (double)d->m * (double)d->n * (double)d->k);
-  int s = wdc_tc_gemm(ctx, d, A, B, C, Y);
+  // Y = alpha*A*B + beta*Y (C aliasing the output) is served by the CUDA-core kernel's in-place mode only
+  int s = (C != nullptr && C == Y) ? WDC_ERR_UNSUPPORTED : wdc_tc_gemm(ctx, d, A, B, C, Y);
   if (s != WDC_ERR_UNSUPPORTED) return s;
   return wdc_simt_gemm(ctx, d, A, B, C, Y);
 }

@@ -10,8 +10,10 @@
 
 int wdc_simt_gemm(wdc_context* ctx, const wdc_gemm_desc* d, const float* A, const float* B, const float* C,
                   float* Y);
+int wdc_simt_preload(wdc_context* ctx);
 int wdc_lstm_persistent(wdc_context* ctx, const float* P, const float* R, const float* bias, const float* h0,
-                        const float* c0, float* Y, float* Yh, float* Yc, int64_t T, int64_t Bt, int64_t H);
+                        const float* c0, float* Y, float* Yh, float* Yc, int64_t T, int64_t Bt, int64_t H,
+                        int64_t selftest_wait_ns = 0);
 
 __device__ __forceinline__ float sigmoid_ref(float x) { return (tanhf(x * 0.5f) + 1.f) * 0.5f; }
 
@@ -100,6 +102,31 @@ extern "C" int wdc_lstm(wdc_context* ctx, const float* X, const float* W, const 
   return s;
 }
 
+// Self-test of the bounded device waits: runs the persistent recurrence kernel on a small zero-filled problem
+// (2 steps, batch 8, hidden 128: 32 CTAs) whose first step is told to wait for one arrival more than there are
+// CTAs, with `limit_ns` as the limit of every wait.  The wait runs out, the kernel records its status, raises its
+// abort word, every CTA returns, and the context stays usable: the next wdc_sync reports WDC_ERR_DEVICE_WAIT once.
+extern "C" int wdc_selftest_device_wait(wdc_context* ctx, int64_t limit_ns) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_selftest_device_wait: null context");
+  WDC_REQUIRE(ctx, limit_ns >= 1000 && limit_ns <= 1000000000ll,
+              "wdc_selftest_device_wait: limit of %lld ns is outside 1 us .. 1 s", (long long)limit_ns);
+  DeviceGuard g(ctx->device);
+  const int64_t T = 2, Bt = 8, H = 128;
+  const int64_t n_p = T * Bt * 4 * H, n_r = 4 * H * H, n_y = T * Bt * H, n_s = Bt * H;
+  float* buf = nullptr;
+  int s = wdc_alloc(ctx, (n_p + n_r + n_y + 2 * n_s) * 4, (void**)&buf);
+  if (s != WDC_OK) return s;
+  s = wdc_fill_u32(ctx, buf, 0u, n_p + n_r + n_y + 2 * n_s);
+  if (s == WDC_OK) {
+    float *P = buf, *R = P + n_p, *Y = R + n_r, *Yh = Y + n_y, *Yc = Yh + n_s;
+    s = wdc_lstm_persistent(ctx, P, R, nullptr, nullptr, nullptr, Y, Yh, Yc, T, Bt, H, limit_ns);
+    if (s == WDC_ERR_UNSUPPORTED)
+      s = wdc_fail(ctx, WDC_ERR_UNSUPPORTED, "wdc_selftest_device_wait: the persistent kernel cannot run on this device");
+  }
+  wdc_free(ctx, buf);   // stream-ordered
+  return s;
+}
+
 // ------------------------------------------------------------------------------------------------
 // wdc_lstm_static: the same LSTM for callers that must not allocate.
 //
@@ -115,15 +142,37 @@ extern "C" int wdc_lstm(wdc_context* ctx, const float* X, const float* W, const 
 // its weights in the arena).
 //
 // In host code the array's name is only a handle for the symbol, not a device address; the address
-// comes from cudaGetSymbolAddress, asked once per device with that device current.  That lookup
-// happens in the first call on each device, so make that first call outside any stream capture.
+// comes from cudaGetSymbolAddress, asked once per device with that device current.  wdc_create does
+// that lookup for its device (wdc_lstm_static_setup below), because the lookup is also the moment
+// the CUDA driver loads this file's module and sets the 4 MiB array aside: a context created at
+// start-up has therefore paid for the array before the first wdc_lstm_static call, and that call
+// touches no allocator at all, not even the driver's module loader.  Should the address of a device
+// still be unknown when wdc_lstm_static runs (it cannot be after a successful wdc_create), the call
+// looks it up itself; such a first call must come before any stream capture.
 // All calls on a device share the one array: it holds whatever the previous call left (nothing here
 // needs to start at zero: every step overwrites the block before reading it), and two calls that
 // overlap on the GPU (different streams or contexts of one device) would race on it.
 constexpr int64_t kLstmStaticFloats = 1 << 20;
 static __device__ __align__(256) float g_lstm_static_scratch[kLstmStaticFloats];
 
-static float* g_lstm_static_ptr[64] = {};  // per-device address of the array, filled on first use
+static float* g_lstm_static_ptr[64] = {};  // per-device address of the array, filled by wdc_lstm_static_setup
+
+// Resolves the array's device address for the context's device (which must be current).  Called by
+// wdc_create; the first lookup on a device makes the driver load this module and reserve the array.
+int wdc_lstm_static_setup(wdc_context* ctx) {
+  if (ctx->device < 0 || ctx->device >= 64) return WDC_OK;   // wdc_lstm_static refuses such a device itself
+  if (g_lstm_static_ptr[ctx->device]) return WDC_OK;
+  float* p = nullptr;
+  WDC_CUDA(ctx, cudaGetSymbolAddress((void**)&p, g_lstm_static_scratch));
+  // the kernels wdc_lstm_static launches live in three modules; with lazy module loading a module's code is
+  // placed in device memory at its first use, so touch them now as well
+  cudaFuncAttributes fa;
+  WDC_CUDA(ctx, cudaFuncGetAttributes(&fa, lstm_gate_kernel));
+  int s = wdc_simt_preload(ctx);
+  if (s != WDC_OK) return s;
+  g_lstm_static_ptr[ctx->device] = p;
+  return WDC_OK;
+}
 
 extern "C" int wdc_lstm_static(wdc_context* ctx, const float* X, const float* W, const float* R,
                                const float* bias, const float* h0, const float* c0, float* Y, float* Yh,
@@ -141,11 +190,11 @@ extern "C" int wdc_lstm_static(wdc_context* ctx, const float* X, const float* W,
                     (long long)(Bt * 4 * H), (long long)kLstmStaticFloats);
   WDC_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, "wdc_lstm_static: device index out of range");
   DeviceGuard g(ctx->device);
-  float* G = g_lstm_static_ptr[ctx->device];
-  if (!G) {
-    WDC_CUDA(ctx, cudaGetSymbolAddress((void**)&G, g_lstm_static_scratch));
-    g_lstm_static_ptr[ctx->device] = G;
+  {
+    int s0 = wdc_lstm_static_setup(ctx);   // a no-op after wdc_create
+    if (s0 != WDC_OK) return s0;
   }
+  float* G = g_lstm_static_ptr[ctx->device];
   int s;
   if (h0) s = wdc_copy(ctx, Yh, h0, Bt * H * 4);
   else s = wdc_fill_u32(ctx, Yh, 0u, Bt * H);
@@ -160,8 +209,8 @@ extern "C" int wdc_lstm_static(wdc_context* ctx, const float* X, const float* W,
     d.alpha = 1.f; d.beta = 0.f;
     s = wdc_simt_gemm(ctx, &d, X + t * Bt * I, W, nullptr, G);
     if (s != WDC_OK) break;
-    d.k = H; d.sa0 = H; d.sb1 = H;                // G = h * R^T + G (each element read then written by one thread)
-    d.sc0 = 4 * H; d.sc1 = 1; d.beta = 1.f;
+    d.k = H; d.sa0 = H; d.sb1 = H;                // G += h * R^T: C == Y selects the kernel's in-place mode, which
+    d.sc0 = 4 * H; d.sc1 = 1; d.beta = 1.f;       // reads the old value through the output pointer with a plain load
     s = wdc_simt_gemm(ctx, &d, Yh, R, G, G);
     if (s != WDC_OK) break;
     lstm_gate_kernel<<<grid_for(ctx, Bt * H, 256, 4), 256, 0, ctx->stream>>>(G, bias, Yc, Yh, Y + t * Bt * H, Bt, H);

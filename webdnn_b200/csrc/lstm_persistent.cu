@@ -42,6 +42,8 @@ struct LstmArgs {
   unsigned int* counters;  // [T + 1]: arrivals per step; last word = abort flag
   int* status;
   int T, B, H;
+  unsigned long long wait_ns;   // limit of every wait (WAIT_NS; the self-test passes about a millisecond)
+  unsigned int arrivals;        // arrivals that complete a step: the grid size (the self-test asks for one more)
 };
 
 __device__ __forceinline__ float sigmoid_ref(float x) { return (tanhf(x * 0.5f) + 1.f) * 0.5f; }
@@ -71,7 +73,7 @@ __device__ __forceinline__ unsigned long long global_ns() {
 
 // Waits until `*counter >= target`.  Returns false if the wait was abandoned.
 __device__ bool wait_counter(const unsigned int* counter, unsigned int target, unsigned int* abort_word, int* status,
-                             int code) {
+                             int code, unsigned long long limit_ns) {
   for (int i = 0; i < 4096; i++)
     if (ld_acquire(counter) >= target) return true;
   const unsigned long long t0 = global_ns();
@@ -79,7 +81,7 @@ __device__ bool wait_counter(const unsigned int* counter, unsigned int target, u
     for (int i = 0; i < 256; i++)
       if (ld_acquire(counter) >= target) return true;
     if (ld_acquire(abort_word) != 0) return false;
-    if (global_ns() - t0 > WAIT_NS) {
+    if (global_ns() - t0 > limit_ns) {
       atomicExch(abort_word, 1u);
       atomicCAS(status, 0, code);
       return false;
@@ -88,7 +90,8 @@ __device__ bool wait_counter(const unsigned int* counter, unsigned int target, u
 }
 
 // Bounded wait for the bulk copies of one step.  Returns false if the wait was abandoned.
-__device__ bool wait_copies(unsigned long long* bar, uint32_t parity, unsigned int* abort_word, int* status, int code) {
+__device__ bool wait_copies(unsigned long long* bar, uint32_t parity, unsigned int* abort_word, int* status, int code,
+                            unsigned long long limit_ns) {
   for (int i = 0; i < 4096; i++)
     if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
@@ -96,7 +99,7 @@ __device__ bool wait_copies(unsigned long long* bar, uint32_t parity, unsigned i
     for (int i = 0; i < 256; i++)
       if (mbar_try_wait(bar, parity)) return true;
     if (ld_acquire(abort_word) != 0) return false;
-    if (global_ns() - t0 > WAIT_NS) {
+    if (global_ns() - t0 > limit_ns) {
       atomicExch(abort_word, 1u);
       atomicCAS(status, 0, code);
       return false;
@@ -112,11 +115,10 @@ __global__ void __launch_bounds__(64 * U, 1) lstm_persistent_kernel(const LstmAr
   float* h_s = reinterpret_cast<float*>(smem_raw);       // [B][ld]
   float* r_s = h_s + (size_t)B * ld;                     // [4 * U][ld], row = gate * U + unit
   float4* part = reinterpret_cast<float4*>(r_s + (size_t)4 * U * ld);  // [KS][B * U] (4 gates each)
-  __shared__ int s_ok;
+  __shared__ int s_ok, s_ok_copies;   // verdicts of the two bounded waits of a step (thread 0 decides for the CTA)
   __shared__ __align__(8) unsigned long long h_bar;   // completion of the bulk copies of h_{t-1}
 
   const int tid = threadIdx.x;
-  const int G = gridDim.x;
   const int u0 = blockIdx.x * U;
   unsigned int* abort_word = a.counters + T;
 
@@ -165,7 +167,8 @@ __global__ void __launch_bounds__(64 * U, 1) lstm_persistent_kernel(const LstmAr
     }
     // h_{t-1}: h0 (or zero) for the first step, else Y[t-1] once every CTA has written its columns
     if (t > 0) {
-      if (tid == 0) s_ok = wait_counter(a.counters + (t - 1), (unsigned)G, abort_word, a.status, 61) ? 1 : 0;
+      if (tid == 0)
+        s_ok = wait_counter(a.counters + (t - 1), a.arrivals, abort_word, a.status, 61, a.wait_ns) ? 1 : 0;
       __syncthreads();
       if (!s_ok) return;
     }
@@ -188,7 +191,15 @@ __global__ void __launch_bounds__(64 * U, 1) lstm_persistent_kernel(const LstmAr
               "l"(hsrc + (size_t)b * H), "r"((uint32_t)(H * 4)), "r"(smem_addr(&h_bar))
               : "memory");
       }
-      if (!wait_copies(&h_bar, (uint32_t)(copies & 1), abort_word, a.status, 62)) return;
+      // One thread runs the bounded wait and the whole CTA follows its verdict, so that on expiry every thread
+      // leaves together (no thread is left behind at a later __syncthreads).  After the barrier each thread
+      // observes the completed phase itself, which is what orders its reads after the copies' writes; the
+      // phase cannot advance before the next step's expect_tx, so this returns at the first poll.
+      if (tid == 0)
+        s_ok_copies = wait_copies(&h_bar, (uint32_t)(copies & 1), abort_word, a.status, 62, a.wait_ns) ? 1 : 0;
+      __syncthreads();
+      if (!s_ok_copies) return;
+      for (int i = 0; i < (1 << 20) && !mbar_try_wait(&h_bar, (uint32_t)(copies & 1)); i++) {}
       copies++;
     } else {
       for (int i = tid; i < B * (H / 4); i += blockDim.x) {
@@ -288,7 +299,8 @@ int launch_persistent(wdc_context* ctx, LstmArgs& args, size_t smem) {
 // Runs the recurrence on the projected input P.  WDC_ERR_UNSUPPORTED: shape outside the kernel's range
 // (nothing has been written); any other non-zero status is an error.
 int wdc_lstm_persistent(wdc_context* ctx, const float* P, const float* R, const float* bias, const float* h0,
-                        const float* c0, float* Y, float* Yh, float* Yc, int64_t T, int64_t Bt, int64_t H) {
+                        const float* c0, float* Y, float* Yh, float* Yc, int64_t T, int64_t Bt, int64_t H,
+                        int64_t selftest_wait_ns) {
   if (Bt > 64 || H % 32 != 0 || T > (1 << 24) || T < 1) return WDC_ERR_UNSUPPORTED;
   if ((((uintptr_t)P | (uintptr_t)R | (uintptr_t)Y | (uintptr_t)h0) & 15) != 0) return WDC_ERR_UNSUPPORTED;
   int U = 0;
@@ -312,7 +324,12 @@ int wdc_lstm_persistent(wdc_context* ctx, const float* P, const float* R, const 
     wdc_free(ctx, counters);
     return wdc_check_cuda(ctx, e, "cudaMemsetAsync");
   }
-  LstmArgs args = {P, R, bias, h0, c0, Y, Yh, Yc, counters, ctx->status_word, (int)T, (int)Bt, (int)H};
+  LstmArgs args = {P, R, bias, h0, c0, Y, Yh, Yc, counters, ctx->status_word, (int)T, (int)Bt, (int)H,
+                   WAIT_NS, (unsigned)(H / U)};
+  if (selftest_wait_ns > 0) {   // wdc_selftest_device_wait: a step that can never complete, and a short limit
+    args.wait_ns = (unsigned long long)selftest_wait_ns;
+    args.arrivals = (unsigned)(H / U) + 1u;
+  }
   s = U == 4 ? launch_persistent<4>(ctx, args, smem) : launch_persistent<8>(ctx, args, smem);
   wdc_free(ctx, counters);  // stream-ordered arena: reused only by work queued after this launch
   return s;

@@ -120,6 +120,10 @@ SIGNATURES = {
     "wdc_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64]),
     "wdc_lstm": (c_int, [c_void_p] + [c_void_p] * 9 + [c_int64] * 4),
     "wdc_lstm_static": (c_int, [c_void_p] + [c_void_p] * 9 + [c_int64] * 4),
+    "wdc_selftest_device_wait": (c_int, [c_void_p, c_int64]),
+    "wdc_set_option": (c_int, [c_void_p, c_char_p, c_int64]),
+    "wdc_range_push": (c_int, [c_void_p, c_char_p]),
+    "wdc_range_pop": (c_int, [c_void_p]),
 }
 
 _lib = None

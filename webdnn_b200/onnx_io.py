@@ -436,6 +436,8 @@ def make_attr(name: str, value: Any) -> Attribute:
     if isinstance(value, Tensor):
         return Attribute(name, A_TENSOR, t=value)
     if isinstance(value, (list, tuple)):
+        if value and all(isinstance(v, (str, bytes)) for v in value):
+            return Attribute(name, A_STRINGS, strings=[v.encode("utf-8") if isinstance(v, str) else v for v in value])
         if all(isinstance(v, int) for v in value):
             return Attribute(name, A_INTS, ints=list(value))
         if all(isinstance(v, (int, float)) for v in value):

@@ -402,21 +402,37 @@ class CudaConv(base.Conv):
         # library anyway, so the separate NCHW -> NHWC conversion is skipped
         direct = (x.layout == "nchw" and s["group"] == 1 and s["ch_in"] <= 4 and s["kernel_shape"][1] <= 8
                   and s["ch_out"] % 4 == 0 and s["in_shape"][0] * s["in_shape"][1] > 1)
+        oh, ow = s["out_shape"]
+        # The epilogue reads residual[pixel, channel] for every output element, so the addend rides in it only
+        # when it is a float32 tensor of exactly the output's shape.  An Add that broadcasts ([1,C,H,W],
+        # [N,C,1,1], ... : binary7.ts broadcasts multidirectionally) keeps the reference's separate steps below.
+        unfused_res = None
+        if residual is not None and (list(residual.dims) != [s["batch"], s["ch_out"], oh, ow]
+                                     or residual.data_type != "float32"):
+            unfused_res, residual = residual, None
+        relu_here = self.relu and unfused_res is None
         xcl = x if direct else context.channels_last(x)
         rcl = context.channels_last(residual) if residual is not None else None
         wp = _packed_weight(context, w)
-        oh, ow = s["out_shape"]
         y = context.empty_tensor([s["batch"], s["ch_out"], oh, ow], "float32", layout="nhwc")
         d = ConvDesc(batch=s["batch"], ch_in=s["ch_in"], in_h=s["in_shape"][0], in_w=s["in_shape"][1],
                      ch_out=s["ch_out"], k_h=s["kernel_shape"][0], k_w=s["kernel_shape"][1], out_h=oh,
                      out_w=ow, stride_h=s["strides"][0], stride_w=s["strides"][1], pad_t=s["pads"][0],
                      pad_l=s["pads"][1], dil_h=s["dilations"][0], dil_w=s["dilations"][1],
-                     group=s["group"], relu=int(self.relu), x_nchw=int(direct))
+                     group=s["group"], relu=int(relu_here), x_nchw=int(direct))
         context.conv2d(d, xcl, wp, scale, shift, rcl, y)
         if xcl is not x:
             xcl.dispose()
         if rcl is not None and rcl is not residual:
             rcl.dispose()
+        if unfused_res is not None:
+            (t,) = CudaBinary7("Add").run(context, [y, unfused_res], 1)
+            y.dispose()
+            y = t
+            if self.relu:
+                (t,) = CudaUnary("Relu").run(context, [y], 1)
+                y.dispose()
+                y = t
         return [y]
 
 
@@ -1031,11 +1047,27 @@ class CudaLSTM(OperatorImpl):
             raise ValueError("LSTM: only direction=forward is supported")
         if get_attr_int(attribute, "input_forget", 0) != 0:
             raise ValueError("LSTM: input_forget is not supported")
+        # The kernels implement the operator's defaults only; anything else must fail here rather than
+        # return the default's numbers.
+        for a in attribute:
+            if a.name == "activations":
+                acts = [v.decode("utf-8") if isinstance(v, bytes) else str(v) for v in a.strings]
+                if [v.lower() for v in acts] != ["sigmoid", "tanh", "tanh"]:
+                    raise ValueError(f"LSTM: activations {acts} are not supported (only Sigmoid, Tanh, Tanh)")
+            elif a.name in ("activation_alpha", "activation_beta") and len(a.floats) > 0:
+                raise ValueError(f"LSTM: {a.name} is not supported")
+        if get_attr_float(attribute, "clip", 0.0) != 0.0 or any(a.name == "clip" for a in attribute):
+            raise ValueError("LSTM: clip is not supported")
+        if get_attr_int(attribute, "layout", 0) != 0:
+            raise ValueError("LSTM: layout=1 (batch-major) is not supported")
 
     def run(self, context, inputs, n_outputs):
         context.asserts_cuda_tensor_array(inputs)
         if len(inputs) == 5 or len(inputs) > 7:
             raise ValueError("LSTM: sequence_lens is not supported")
+        for t in inputs:
+            if t.data_type != "float32":
+                raise TypeError(f"LSTM: DataType {t.data_type} not supported")
         x, w, r = inputs[0], inputs[1], inputs[2]
         b = inputs[3] if len(inputs) > 3 else None
         h0 = inputs[5] if len(inputs) > 5 else None

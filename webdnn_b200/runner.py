@@ -262,7 +262,14 @@ class Runner:
                     raise RuntimeError(f"Input {input_name} not found")
             context = self.backend_contexts[operator.backend]
             logger.debug("Running %s(%s) on %s", node.name, op_type, operator.backend)
-            outputs = operator.run(context, operator_inputs, len(node.output))
+            ranged = getattr(context, "profile", False)
+            if ranged:
+                context.range_push(f"{node.name}({op_type})")
+            try:
+                outputs = operator.run(context, operator_inputs, len(node.output))
+            finally:
+                if ranged:
+                    context.range_pop()
             for j, output_name in enumerate(node.output):
                 tensors_for_backends[outputs[j].backend][output_name] = outputs[j]
             self.node_backends.append((node.name, op_type, operator.backend))
@@ -382,6 +389,11 @@ def load(source: Union[str, bytes, Model], backend_order: Optional[Sequence[str]
                 ctx = WebDNNCudaContext(cpu_context, device=opts.get("device", 0),
                                         arena_bytes=opts.get("arenaBytes", 0))
                 ctx.initialize()
+            if "precision" in opts:
+                ctx.set_precision(opts["precision"])
+            if "profile" in opts:
+                ctx.profile = bool(opts["profile"])
+                ctx.set_option("nvtx", int(ctx.profile))
             contexts["cuda"] = ctx
             _register("cuda")
             succeeded = "cuda"

@@ -98,9 +98,16 @@ struct TcProblem {
   int kblocks;        // ceil(K / 32)
   int cblocks;        // K blocks per filter tap = ceil(ch_in / 32)
   int tile_n;         // 32, 64 or 128
-  int splits;         // > 1: the reduction is cut into `splits` ranges of kbs K blocks; work unit = (tile, range);
-  int kbs;            //      each unit stores its raw partial sums at row range * m_pad + m of a workspace
-  int64_t m_pad;      //      (tiles_m * 128 rows per range); a second kernel adds the ranges and applies the epilogue
+  // Work units.  The first `full_tiles` tiles (a whole number of waves of the grid, possibly none) are computed
+  // by one unit each and leave through the fused epilogue.  Each of the remaining tiles (fewer than one wave) is
+  // cut into `splits` ranges of `kbs` K blocks that run as separate units, so that the last, partly filled wave
+  // becomes ceil(rest * splits / grid) rounds of 1 / splits of a tile instead of one whole tile per CTA.  A range's
+  // raw partial sums go to block (rest_index * splits + range) of a workspace of 128-row x tile_n blocks; a second
+  // kernel adds the ranges in ascending order and applies the epilogue.  splits == 1: every tile is a full tile.
+  int full_tiles;
+  int splits;
+  int kbs;
+  int early_consts;   // 1: the per-channel addends are constants of the model (may be read before the grid dependency resolves)
   int tma_epi;        // 1: residual tiles and output tiles move by TMA (map_res, map_y)
   int c4;             // 1: input has 4 channels per pixel, one K block per filter row, chunk j = tap kx;
                       // 2: the same with the row physically padded on the left and stride_w 2, so that taps
@@ -213,13 +220,28 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t pari
   return mbar_wait_timed(bar, parity, ss, status, code);
 }
 
-// Work unit u of a launch: tile u / splits, reduction range u % splits (K blocks kb0 .. kb0 + kbn - 1).
+// Work unit u of a launch: a full tile (sp = -1, all K blocks), or range sp of one of the remaining tiles
+// (K blocks kb0 .. kb0 + kbn - 1); `rest` is the tile's index among the remaining tiles.
 __device__ __forceinline__ void unit_of(const TcProblem& p, int u, int& tile, int& sp, int& kb0, int& kbn) {
-  tile = u / p.splits;
-  sp = u - tile * p.splits;
+  if (u < p.full_tiles) {
+    tile = u;
+    sp = -1;
+    kb0 = 0;
+    kbn = p.kblocks;
+    return;
+  }
+  const int r = u - p.full_tiles;
+  const int rest = r / p.splits;
+  tile = p.full_tiles + rest;
+  sp = r - rest * p.splits;
   kb0 = sp * p.kbs;
   kbn = p.kblocks - kb0 < p.kbs ? p.kblocks - kb0 : p.kbs;
 }
+
+// Programmatic dependent launch.  wait: everything the grids before this one wrote is visible afterwards (a no-op
+// for a launch without the attribute).  launch_dependents: the next grid of the stream may start its own set-up.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred;
@@ -340,12 +362,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x,
                 const __grid_constant__ CUtensorMap map_w_hi, const __grid_constant__ CUtensorMap map_w_lo,
                 const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_y,
-                const __grid_constant__ CUtensorMap map_res, float* __restrict__ y) {
+                const __grid_constant__ CUtensorMap map_res, const __grid_constant__ CUtensorMap map_ws,
+                float* __restrict__ y) {
   extern __shared__ unsigned char smem_raw[];
   SharedStorage* ss = reinterpret_cast<SharedStorage*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_tiles = p.tiles_m * p.tiles_n;
-  const int total_units = total_tiles * p.splits;   // = total_tiles unless the reduction is split
+  const int total_units = p.full_tiles + (total_tiles - p.full_tiles) * p.splits;
   // shared-memory stage addresses
   const bool narrow = p.tile_n <= 64;
   const uint32_t w_slot = narrow ? W_TILE_BYTES / 2 : W_TILE_BYTES;
@@ -395,18 +418,21 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     }
     ss->ktab[kb] = e;
   }
-  if (p.tma_epi && p.N <= SHIFT_TAB) {
+  auto fill_shift_tab = [&]() {
     // entries a warp can touch: its first column (< tiles_n * tile_n) plus 64
     const int used = p.tiles_n * p.tile_n + 64;
     for (int i = threadIdx.x; i < used; i += NUM_THREADS)
       ss->shift_tab[i] = (p.shift && i < p.N) ? p.shift_mul * __ldg(p.shift + i) : 0.f;
-  }
+  };
+  const bool use_shift_tab = p.tma_epi && p.N <= SHIFT_TAB;
+  if (use_shift_tab && p.early_consts) fill_shift_tab();
   if (threadIdx.x == 32) {
     // descriptor fetches of the first TMA operations overlap the rest of the set-up
     asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_w_hi) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_w_lo) : "memory");
     if (kTmaA) asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_a) : "memory");
     if (p.tma_epi) asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_y) : "memory");
+    if (p.splits > 1) asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_ws) : "memory");
   }
   if (kTmaA && p.c4) {
     // 4-channel mode: planes of taps past the filter width are never loaded; their weights are zero,
@@ -426,9 +452,20 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = ss->tmem_base;
-  // Each CTA walks the K blocks from a different starting point so that the CTAs, which all need the
-  // same weight tiles, do not ask the same L2 lines at the same moment.
-  const int rot = p.splits > 1 ? 0 : (int)(((int64_t)blockIdx.x * p.kblocks) / gridDim.x);
+  // Everything above touched only this CTA's own state, kernel parameters and constants of the model, so under
+  // programmatic dependent launch it overlaps the tail of the previous grid.  From here on the kernel reads what
+  // earlier grids wrote (activations, the residual) and writes memory they may still be reading (the arena reuses
+  // freed blocks in stream order): wait for them.  The next grid may begin its own set-up right away; its CTAs
+  // become resident as this grid's CTAs exit, and it waits for this grid's completion at the same point.
+  grid_dependency_wait();
+  grid_launch_dependents();
+  if (use_shift_tab && !p.early_consts) {
+    fill_shift_tab();
+    __syncthreads();
+  }
+  // Each CTA walks the K blocks of a full tile from a different starting point so that the CTAs, which all need
+  // the same weight tiles, do not ask the same L2 lines at the same moment (split ranges start at their first block).
+  const int rot_full = (int)(((int64_t)blockIdx.x * p.kblocks) / gridDim.x);
 
   if (kTmaA && warp < NUM_A_WARPS) {
     // ===================================================================== A producers (split only)
@@ -508,7 +545,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         const int oy = (int)(rem / (uint32_t)p.out_w), ox = (int)rem - oy * p.out_w;
         const int cw = p.c4 == 2 ? ox : ox * p.stride_w - p.pad_l, ch = oy * p.stride_h - p.pad_t;
         // first K block: this CTA's rotation, or the start of the unit's range (no rotation then)
-        const int kfirst = kb0 + rot;
+        const int kfirst = kb0 + (sp < 0 ? rot_full : 0);
         const int tap = kfirst / p.cblocks;
         int c0 = (kfirst - tap * p.cblocks) * BLOCK_K;
         int ky = tap / p.k_w, kx = tap - ky * p.k_w;
@@ -580,7 +617,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
           rsrc = nullptr;
         }
       }
-      int kb = ld_kb + rot;
+      int kb = ld_kb + rot_full;   // (this kernel never splits a tile)
       if (kb >= p.kblocks) kb -= p.kblocks;
       ld_kb++;
       KEntry e;
@@ -689,7 +726,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         for (int kb = 0; kb < kbn; kb++) {
           if (!mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 21)) { ok = false; break; }
           mbar_arrive_expect_tx(&ss->full_bar[stage], bytes);
-          int kr = kb0 + kb + rot;
+          int kr = kb0 + kb + (sp < 0 ? rot_full : 0);
           if (kr >= kb0 + kbn) kr -= kbn;
           // K offset of the block in a weight row: blocks are counted per filter tap, and when the channel
           // count is not a multiple of 32 a tap's last block is short (its tail columns meet zeros of A)
@@ -777,8 +814,10 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       const uint32_t swz = cw == 32 ? (uint32_t)(lane & 7) : 0u;   // 128B swizzle only for 128-byte rows
       const uint32_t row_off = (uint32_t)lane * (uint32_t)cw * 4u;
       const bool use_res = p.residual != nullptr && !TC_DBG(p, 2);
-      int64_t k = 0;                                    // chunks handled by this warp so far
-      if (use_res && lane == 0 && (int)blockIdx.x < total_tiles) {
+      // residual tiles exist for full tiles only; a CTA's full tiles all come before its split ranges
+      int64_t k = 0;                                    // residual chunks handled by this warp so far
+      int64_t ks = 0;                                   // staging buffers used so far (parity picks the buffer)
+      if (use_res && lane == 0 && (int)blockIdx.x < p.full_tiles) {
         const int t0 = blockIdx.x;
         mbar_arrive_expect_tx(&ss->res_bar[ew][0], chunk_bytes);
         tma_load_2d(ss->epi_buf[ew][0], &map_res, &ss->res_bar[ew][0], (int)(t0 % p.tiles_n) * p.tile_n + col0,
@@ -790,24 +829,30 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         int tile, sp, kb0, kbn;
         unit_of(p, u, tile, sp, kb0, kbn);
+        const bool direct = sp < 0;                     // full tile: fused epilogue; else raw partial sums
+        const bool res_u = use_res && direct;
         nseg = (kbn + SEG_KBLOCKS - 1) / SEG_KBLOCKS;
         // Short-K (memory-bound) launches: while this tile accumulates, L2 fetches the residual chunks of
         // the warp's next tile.  Each staging buffer holds one chunk, so without this every chunk waits
         // for a full trip to HBM.  Long-K launches hide that trip behind the MMAs and skip the extra requests.
-        if (use_res && lane == 0 && p.kblocks <= RES_L2_KBLOCKS && tile + (int)gridDim.x < total_tiles) {
+        if (res_u && lane == 0 && p.kblocks <= RES_L2_KBLOCKS && tile + (int)gridDim.x < p.full_tiles) {
           const int nt = tile + (int)gridDim.x;
           for (int c = 0; c < nch; c++)
             tma_prefetch_l2_2d(&map_res, (int)(nt % p.tiles_n) * p.tile_n + col0 + c * 32,
                                (int)((nt / p.tiles_n) * TILE_M + q * 32));
         }
         const int64_t mrow0 = (int64_t)(tile / p.tiles_n) * TILE_M + q * 32;   // first row of this warp
-        const int64_t store_row = mrow0 + sp * p.m_pad;   // split reductions: row block `sp` of the workspace
+        // split ranges: block (rest * splits + sp) of the workspace, 128 rows x tile_n columns each
+        const int64_t ws_row = ((int64_t)(tile - p.full_tiles) * p.splits + sp) * TILE_M + q * 32;
         const int nbase = (int)(tile % p.tiles_n) * p.tile_n + col0;
-        // The accumulators start at the per-column addend (bias / folded BatchNormalization shift); the
-        // per-column multiplier is already in the weights.  Warp-uniform 16-byte loads from the table in
-        // shared memory (from global memory when N exceeds the table).
+        // The accumulators of a full tile start at the per-column addend (bias / folded BatchNormalization
+        // shift); the per-column multiplier is already in the weights.  Warp-uniform 16-byte loads from the
+        // table in shared memory (from global memory when N exceeds the table).  Split ranges start at zero.
         float acc[64];
-        if (p.N <= SHIFT_TAB) {
+        if (!direct) {
+#pragma unroll
+          for (int j = 0; j < 64; j++) acc[j] = 0.f;
+        } else if (p.N <= SHIFT_TAB) {
           // branch-free: the table is zero past N, and 64 entries past any warp's first column exist
 #pragma unroll
           for (int j = 0; j < 64; j += 4) {
@@ -855,11 +900,11 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
 #pragma unroll
         for (int c = 0; c < 2; c++) {
           if (c < nch && ok) {
-            const int b = (int)(k & 1);
+            const int b = (int)(ks & 1);
             unsigned char* sbuf = ss->epi_buf[ew][b];
             // buffer b is free: with a residual, its load was issued after the store that last read
             // the buffer had finished; without, lane 0 has waited for that store before this point
-            if (use_res) ok = mbar_wait(&ss->res_bar[ew][b], (uint32_t)((k >> 1) & 1), ss, p.status, 43);
+            if (res_u) ok = mbar_wait(&ss->res_bar[ew][b], (uint32_t)((k >> 1) & 1), ss, p.status, 43);
             __syncwarp();
             if (ok) {
               // 4 cells (16 columns) at a time: residual reads first, then arithmetic and writes, so
@@ -868,7 +913,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
               for (int jb = 0; jb < 8; jb += 4) {
                 if (jb * 4 < cw) {
                   float4 r4[4];
-                  if (use_res) {
+                  if (res_u) {
 #pragma unroll
                     for (int j = 0; j < 4; j++)
                       r4[j] = *reinterpret_cast<const float4*>(sbuf + row_off + (((uint32_t)(jb + j) ^ swz) << 4));
@@ -877,13 +922,13 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
                   for (int j = 0; j < 4; j++) {
                     const float* av = &acc[c * 32 + (jb + j) * 4];
                     float o[4] = {av[0], av[1], av[2], av[3]};
-                    if (use_res) {
+                    if (res_u) {
                       o[0] = fmaf(p.res_mul, r4[j].x, o[0]);
                       o[1] = fmaf(p.res_mul, r4[j].y, o[1]);
                       o[2] = fmaf(p.res_mul, r4[j].z, o[2]);
                       o[3] = fmaf(p.res_mul, r4[j].w, o[3]);
                     }
-                    if (p.relu) {
+                    if (p.relu && direct) {
 #pragma unroll
                       for (int e = 0; e < 4; e++) o[e] = relu_nan(o[e]);
                     }
@@ -896,14 +941,17 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
               __syncwarp();
               if (lane == 0) {
                 const int col = nbase + c * 32;
-                if (!TC_DBG(p, 2) && mrow0 < p.M && col < p.N) tma_store_2d(&map_y, sbuf, col, (int)store_row);
+                if (!TC_DBG(p, 2) && mrow0 < p.M && col < p.N) {
+                  if (direct) tma_store_2d(&map_y, sbuf, col, (int)mrow0);
+                  else tma_store_2d(&map_ws, sbuf, col0 + c * 32, (int)ws_row);
+                }
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");   // the other buffer's store has read it
-                if (use_res) {
-                  int nt = tile;   // (a launch with a residual has splits == 1: unit == tile)
+                if (res_u) {
+                  int nt = tile;
                   int nc = c + 1;
                   if (nc == nch) { nc = 0; nt += gridDim.x; }
-                  if (nt < total_tiles) {
+                  if (nt < p.full_tiles) {
                     mbar_arrive_expect_tx(&ss->res_bar[ew][b ^ 1], chunk_bytes);
                     tma_load_2d(ss->epi_buf[ew][b ^ 1], &map_res, &ss->res_bar[ew][b ^ 1],
                                 (int)(nt % p.tiles_n) * p.tile_n + col0 + nc * 32,
@@ -911,7 +959,8 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
                   }
                 }
               }
-              k++;
+              if (res_u) k++;
+              ks++;
             }
           }
         }

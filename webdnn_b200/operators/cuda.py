@@ -1065,8 +1065,8 @@ class CudaLSTM(OperatorImpl):
         context.asserts_cuda_tensor_array(inputs)
         if len(inputs) == 5 or len(inputs) > 7:
             raise ValueError("LSTM: sequence_lens is not supported")
-        for t in inputs:
-            if t.data_type != "float32":
+        for j, t in enumerate(inputs):
+            if j != 4 and t.data_type != "float32":     # input 4 is sequence_lens (int32)
                 raise TypeError(f"LSTM: DataType {t.data_type} not supported")
         x, w, r = inputs[0], inputs[1], inputs[2]
         b = inputs[3] if len(inputs) > 3 else None

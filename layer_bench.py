@@ -1,9 +1,9 @@
 """Times wdc_conv2d on single convolution shapes (the ResNet-50 layers at a given batch), or
 wdc_attention on the attention shapes of the DETR-style configuration.
 
-    python -m webdnn_b200.layer_bench [--batch 256] [--only l4.c2,l1.c3] [--reps 5]
-    python -m webdnn_b200.layer_bench --attention [--batch 8] [--only enc] [--reps 5]
-    python -m webdnn_b200.layer_bench --streaming [--reps 20]     # HBM-bound operators, GB/s of algorithmic bytes
+    python layer_bench.py [--batch 256] [--only l4.c2,l1.c3] [--reps 5]
+    python layer_bench.py --attention [--batch 8] [--only enc] [--reps 5]
+    python layer_bench.py --streaming [--reps 20]     # HBM-bound operators, GB/s of algorithmic bytes
 
 Prints, per layer, the mean device time of the contraction launch (CUDA events recorded by the
 library around each launch), algorithmic TFLOP/s, the tensor-issue rate (3 MMAs per algorithmic
@@ -12,14 +12,21 @@ without running a whole network.
 """
 from __future__ import annotations
 
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
 import argparse
 
 import numpy as np
 
-from .backend import CPUTensor, WebDNNCudaContext
+from webdnn_b200.backend import CPUTensor, WebDNNCudaContext
 from ctypes import byref, c_void_p
 
-from .lib import AttentionDesc, ConvDesc
+from webdnn_b200.lib import AttentionDesc, ConvDesc
 
 # name, ch_in, ch_out, input size, kernel, stride, pad, residual, occurrences in ResNet-50 v1.5
 LAYERS = [
@@ -107,8 +114,8 @@ STREAMING = [
 def streaming_bench(ctx: WebDNNCudaContext, only, reps: int, hbm_peak: float) -> None:
     import time
 
-    from . import onnx_io
-    from .runner import load
+    from webdnn_b200 import onnx_io
+    from webdnn_b200.runner import load
     print("| operator | ms | GB/s of algorithmic bytes | of the measured HBM copy peak |")
     print("|---|---:|---:|---:|")
     for name, op, attrs, shapes, opset, factor in STREAMING:
@@ -145,25 +152,142 @@ def streaming_bench(ctx: WebDNNCudaContext, only, reps: int, hbm_peak: float) ->
         runner.dispose()
 
 
+# The operator shapes of the reference's own benchmark list (example/benchmark/make_models.py:142-162), batch 1
+# as there: name, op type, attributes, graph-input shapes, constant (initializer) shapes, opset, algorithmic FLOPs,
+# algorithmic bytes (every operand and the result once), bound.
+def _conv_ref(cin, cout, k, pad, hw):
+    return (f"conv-{cin}-{cout}-{k}-1-{pad} [1,{cin},{hw},{hw}]", "Conv",
+            dict(kernel_shape=[k, k], strides=[1, 1], pads=[pad] * 4), [(1, cin, hw, hw)], [(cout, cin, k, k)], 13,
+            2 * hw * hw * cout * cin * k * k, 4 * (cin * hw * hw + cout * hw * hw + cout * cin * k * k), "tensor")
+
+
+def _convt_ref(cin, cout, hw):
+    oh = (hw - 1) * 2 + 3
+    return (f"convtranspose-{cin}-{cout}-3-2-0 [1,{cin},{hw},{hw}]", "ConvTranspose",
+            dict(kernel_shape=[3, 3], strides=[2, 2], pads=[0, 0, 0, 0]), [(1, cin, hw, hw)], [(cin, cout, 3, 3)], 13,
+            2 * hw * hw * cin * cout * 9, 4 * (cin * hw * hw + cout * oh * oh + cin * cout * 9), "hbm")
+
+
+REFERENCE_SHAPES = [
+    _conv_ref(64, 64, 3, 1, 56), _conv_ref(256, 64, 1, 0, 56), _conv_ref(128, 128, 3, 1, 28),
+    _conv_ref(512, 128, 1, 0, 28), _conv_ref(256, 256, 3, 1, 14), _conv_ref(1024, 256, 1, 0, 14),
+    _convt_ref(512, 256, 64), _convt_ref(32, 16, 64),
+    ("gemm-1024-2048-4096", "Gemm", {"transB": 1}, [(1024, 4096)], [(2048, 4096), (2048,)], 13,
+     2 * 1024 * 2048 * 4096, 4 * (1024 * 4096 + 2048 * 4096 + 1024 * 2048), "tensor"),
+    ("gemm-1048576-32-288", "Gemm", {"transB": 1}, [(1048576, 288)], [(32, 288), (32,)], 13,
+     2 * 1048576 * 32 * 288, 4 * (1048576 * 288 + 32 * 288 + 1048576 * 32), "hbm"),
+    ("matmul-850x1x256-256x2048", "MatMul", {}, [(850, 1, 256), (256, 2048)], [], 13,
+     2 * 850 * 256 * 2048, 4 * (850 * 256 + 256 * 2048 + 850 * 2048), "hbm"),
+    ("matmul-850x1x2048-2048x256", "MatMul", {}, [(850, 1, 2048), (2048, 256)], [], 13,
+     2 * 850 * 256 * 2048, 4 * (850 * 2048 + 256 * 2048 + 850 * 256), "hbm"),
+    ("matmul-850x1x2048-c2048x256", "MatMul", {}, [(850, 1, 2048)], [(2048, 256)], 13,
+     2 * 850 * 256 * 2048, 4 * (850 * 2048 + 256 * 2048 + 850 * 256), "hbm"),
+    ("matmul-8x850x32-8x32x850", "MatMul", {}, [(8, 850, 32), (8, 32, 850)], [], 13,
+     2 * 8 * 850 * 850 * 32, 4 * (2 * 8 * 850 * 32 + 8 * 850 * 850), "hbm"),
+    ("matmul-8x850x850-8x850x32", "MatMul", {}, [(8, 850, 850), (8, 850, 32)], [], 13,
+     2 * 8 * 850 * 850 * 32, 4 * (8 * 850 * 850 + 2 * 8 * 850 * 32), "hbm"),
+    ("softmax-8-850-850", "Softmax", {"axis": 2}, [(8, 850, 850)], [], 13, 0, 8 * 8 * 850 * 850, "hbm"),
+    ("softmax-8-100-850", "Softmax", {"axis": 2}, [(8, 100, 850)], [], 13, 0, 8 * 8 * 100 * 850, "hbm"),
+    ("softmax-8-100-100", "Softmax", {"axis": 2}, [(8, 100, 100)], [], 13, 0, 8 * 8 * 100 * 100, "hbm"),
+]
+
+
+def reference_shapes_bench(ctx: WebDNNCudaContext, reps: int, tf32_peak: float, hbm_peak: float, only=()):
+    """Runs every entry of REFERENCE_SHAPES as a one-node model through the runner with resident inputs, node by
+    node and as a replayed graph (the better of the two is reported, like the reference's harness reports its
+    minimum), and returns one record per entry: microseconds, TFLOP/s, GB/s and the fraction of the bound's peak."""
+    import time
+
+    from webdnn_b200 import onnx_io
+    from webdnn_b200.runner import load
+    rng = np.random.default_rng(0)
+    out = []
+    for name, op, attrs, in_shapes, const_shapes, opset, flops, nbytes, bound in REFERENCE_SHAPES:
+        if only and not any(name.startswith(o) for o in only):
+            continue
+        in_names = [f"in{i}" for i in range(len(in_shapes))]
+        c_names = [f"c{i}" for i in range(len(const_shapes))]
+        node = onnx_io.make_node(op, in_names + c_names, ["out"], name=op, **attrs)
+        inits = [onnx_io.make_tensor(n, (rng.standard_normal(sh) * 0.05).astype(np.float32))
+                 for n, sh in zip(c_names, const_shapes)]
+        g = onnx_io.Graph("g", [node], inits, [onnx_io.ValueInfo(n, onnx_io.FLOAT, list(sh)) for n, sh in
+                                                zip(in_names, in_shapes)], [onnx_io.ValueInfo("out", onnx_io.FLOAT, [])])
+        runner = load(onnx_io.Model(g, opset_import=[("", opset)]), backend_order=["cuda", "cpu"],
+                      backend_options={"cuda": {"context": ctx}})
+        host = [CPUTensor.from_array(rng.standard_normal(sh).astype(np.float32)) for sh in in_shapes]
+        dev = [ctx.move_tensor(t) for t in host]
+
+        def step():
+            for o in runner.run(dev, outputs_on_device=True):
+                o.dispose()
+
+        def timed(fn):
+            for _ in range(3):
+                fn()
+            ctx.sync()
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                fn()
+            ctx.sync()
+            return (time.perf_counter() - t0) / reps * 1e6
+
+        us = timed(step)
+        mode = "node by node"
+        try:
+            cap = runner.capture(host)
+            us_g = timed(cap.launch)
+            cap.dispose()
+            if us_g < us:
+                us, mode = us_g, "graph replay"
+        except Exception:
+            pass
+        on_cuda = all(b == "cuda" for _, _, b in runner.node_backends)
+        for t in dev:
+            t.dispose()
+        runner.dispose()
+        tf = flops / us / 1e6
+        gbs = nbytes / us / 1e3
+        frac = tf / tf32_peak if bound == "tensor" else gbs / hbm_peak
+        out.append({"name": name, "us": us, "mode": mode, "tflops": tf, "gbs": gbs, "bound": bound, "frac_of_peak": frac,
+                    "on_cuda": on_cuda})
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--batch", type=int, default=0, help="default 256 (convolutions) or 8 (attention)")
     ap.add_argument("--attention", action="store_true")
     ap.add_argument("--streaming", action="store_true")
+    ap.add_argument("--reference-shapes", action="store_true",
+                    help="the operator shapes of the reference's benchmark list (example/benchmark/make_models.py)")
     ap.add_argument("--hbm-peak", type=float, default=6542.0, help="GB/s used for the fraction column of --streaming")
     ap.add_argument("--only", default="")
     ap.add_argument("--reps", type=int, default=5)
     ap.add_argument("--tf32-peak", type=float, default=752.0, help="TFLOP/s used for the issue-rate column")
+    ap.add_argument("--split-k", type=int, default=1, help="0: never cut a tile's reduction into ranges")
+    ap.add_argument("--pdl", type=int, default=1, help="0: plain stream order between contraction launches")
+    ap.add_argument("--precision", default="tf32x3", choices=["tf32x3", "tf32x1"])
     args = ap.parse_args()
     only = [s for s in args.only.split(",") if s]
     ctx = WebDNNCudaContext()
     ctx.initialize()
+    ctx.set_option("split_k", args.split_k)
+    ctx.set_option("pdl", args.pdl)
+    ctx.set_precision(args.precision)
     if args.attention:
         attention_bench(ctx, args.batch or 8, only, args.reps)
         ctx.close()
         return
     if args.streaming:
         streaming_bench(ctx, only, max(args.reps, 10), args.hbm_peak)
+        ctx.close()
+        return
+    if args.reference_shapes:
+        print("| shape | us | mode | TFLOP/s | GB/s | bound | of that peak |")
+        print("|---|---:|---|---:|---:|---|---:|")
+        for r in reference_shapes_bench(ctx, max(args.reps, 10), args.tf32_peak, args.hbm_peak, only):
+            print(f"| {r['name']} | {r['us']:.1f} | {r['mode']} | {r['tflops']:.2f} | {r['gbs']:.0f} | {r['bound']} | "
+                  f"{r['frac_of_peak'] * 100:.1f}% |")
         ctx.close()
         return
     B = args.batch or 256

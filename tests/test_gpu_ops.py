@@ -281,3 +281,36 @@ def test_conv_bn_add_with_a_broadcasting_addend(cuda_context, addend_shape, relu
     r.dispose()
     assert got.shape == want.shape == (3, 32, 9, 9)
     assert max_err_rel_linf(got, want) <= TOL
+
+
+@pytest.mark.parametrize("length", [1, 31, 33, 625, 1024, 1025, 2047, 2048, 4096, 4100, 8192, 8193, 9000])
+def test_softmax_and_layernorm_row_lengths(cuda_context, length):
+    """Every row kernel: one warp per row (up to 1024), one CTA with the row in registers (up to 8192), and the
+    re-reading CTA kernel beyond; ragged lengths on both sides of each boundary."""
+    rng = np.random.default_rng(length)
+    x = (rng.standard_normal((5, length)) * 3).astype(np.float32)
+    x[1] += 50.0                       # a row with a large common offset
+    model = single_op_model("Softmax", {"axis": -1}, [x])
+    (want,) = ref_runner.run_model(model, [x])
+    (got,) = run_cuda(model, [x], cuda_context)
+    assert max_err_rel_linf(got, want) <= TOL
+    assert np.allclose(got.sum(axis=-1), 1.0, atol=1e-4)
+    if length > 1:
+        gamma = rng.uniform(0.5, 1.5, length).astype(np.float32)
+        beta = (rng.standard_normal(length) * 0.1).astype(np.float32)
+        want_ln = ops.layernorm_chain(x, gamma, beta, 1e-5)
+        ln = single_op_model("LayerNormalization", {"axis": -1, "epsilon": 1e-5}, [x, gamma, beta], opset=17)
+        (got_ln,) = run_cuda(ln, [x, gamma, beta], cuda_context)
+        assert max_err_rel_linf(got_ln, want_ln) <= TOL
+
+
+@pytest.mark.parametrize("shape", [(3, 5, 7, 7), (2, 130, 1, 1), (4, 9, 5, 6), (2, 3, 8, 9), (1, 2, 11, 12), (2, 2, 40, 40)])
+def test_global_average_pool_on_nchw_maps_of_every_size(cuda_context, shape):
+    """NCHW input (a graph input, not a convolution's channels-last output): the grouped-lanes kernel for maps of at
+    most 128 pixels (4, 8 or 16 lanes per map) and the warp-per-map kernel above that."""
+    x = np.random.default_rng(sum(shape)).standard_normal(shape).astype(np.float32)
+    model = single_op_model("GlobalAveragePool", {}, [x])
+    (want,) = ref_runner.run_model(model, [x])
+    (got,) = run_cuda(model, [x], cuda_context)
+    assert got.shape == want.shape == shape[:2] + (1, 1)
+    assert max_err_rel_linf(got, want) <= 1e-6

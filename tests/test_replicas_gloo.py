@@ -71,3 +71,129 @@ def test_two_gloo_ranks_reproduce_the_full_batch(batch):
     assert sorted(r[0] for r in results) == [0, 1]
     assert all(ok for _, ok, _ in results), results
     assert all(shape == (batch, 10) for _, _, shape in results)
+
+
+# ---- one process, several replicas: stand-ins that compute with the CPU oracle, fail, or stall (no GPU involved) ----
+class _OracleReplica:
+    """Behaves like CudaReplica towards ReplicaGroup: start(shard) takes the slice, finish() returns host arrays."""
+
+    def __init__(self, model, fail=None, stall_s=0.0):
+        self.model, self.fail, self.stall_s = model, fail, stall_s
+        self.shard = None
+        self.closed = False
+
+    def start(self, shard):
+        if self.fail == "start":
+            from webdnn_b200.lib import CudaBackendError
+            raise CudaBackendError(3, "wdc_alloc: 1024 bytes would exceed the arena budget")   # what a full arena reports
+        self.shard = [np.asarray(a) for a in shard]
+
+    def finish(self):
+        import time
+        from oracle import ref_runner
+        if self.stall_s:
+            time.sleep(self.stall_s)
+        if self.fail == "finish":
+            from webdnn_b200.lib import CudaBackendError
+            raise CudaBackendError(5, "a bounded device-side wait expired (kernel status 61)")
+        return ref_runner.run_model(self.model, self.shard)
+
+    def close(self):
+        self.closed = True
+
+
+def test_replica_group_slices_and_gathers_like_one_run():
+    from oracle import ref_runner
+    from webdnn_b200 import zoo
+    from webdnn_b200.replicas import ReplicaGroup
+    model = zoo.mlp(7)
+    x = zoo.make_input((7, 784), "uniform")
+    (full,) = ref_runner.run_model(model, [x])
+    for n in (1, 2, 3):
+        group = ReplicaGroup(replicas=[_OracleReplica(model) for _ in range(n)])
+        (got,) = group.run([x], gather="host", deadline_s=60)
+        assert got.shape == full.shape and np.array_equal(got, full)      # uneven slices, offsets and order
+        group.close()
+        assert all(r.closed for r in group.replicas)
+    with pytest.raises(ValueError):
+        ReplicaGroup(replicas=[])
+
+
+def test_replica_group_names_the_replica_that_failed_or_stalled():
+    from webdnn_b200 import zoo
+    from webdnn_b200.lib import CudaBackendError
+    from webdnn_b200.replicas import ReplicaError, ReplicaGroup
+    model = zoo.mlp(6)
+    x = zoo.make_input((6, 784), "uniform")
+    # an error status while enqueueing (arena budget) on replica 1
+    group = ReplicaGroup(replicas=[_OracleReplica(model), _OracleReplica(model, fail="start"), _OracleReplica(model)])
+    with pytest.raises(ReplicaError) as e:
+        group.run([x])
+    assert list(e.value.failures) == [1] and isinstance(e.value.failures[1], CudaBackendError)
+    assert e.value.failures[1].status == 3
+    # an error status reported at the waiting call (a device wait that ran out) on replica 2
+    group = ReplicaGroup(replicas=[_OracleReplica(model), _OracleReplica(model), _OracleReplica(model, fail="finish")])
+    with pytest.raises(ReplicaError) as e:
+        group.run([x])
+    assert list(e.value.failures) == [2] and e.value.failures[2].status == 5
+    # a replica that does not answer before the host-side deadline
+    group = ReplicaGroup(replicas=[_OracleReplica(model, stall_s=5.0), _OracleReplica(model)])
+    with pytest.raises(ReplicaError) as e:
+        group.run([x], deadline_s=0.5)
+    assert list(e.value.failures) == [0] and isinstance(e.value.failures[0], TimeoutError)
+
+
+# ---- one process per replica over gloo: a rank whose step failed, and a rank that never arrives ----
+def _failing_worker(rank, world, port, mode, queue):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+    import torch.distributed as dist
+    from webdnn_b200.replicas import ReplicaError, check_all_ranks_ok
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    try:
+        dist.barrier()
+        if mode == "error":
+            # rank 1's step returned an error status; every rank must learn of it before the gather
+            err = RuntimeError("WDC_ERR_OOM: arena budget") if rank == 1 else None
+            try:
+                check_all_ranks_ok(err)
+                queue.put((rank, "no error seen"))
+            except ReplicaError as e:
+                queue.put((rank, sorted(e.failures)))
+        else:
+            # rank 1 leaves between steps and never joins the next collective: the others' collective ends with
+            # the process group's short timeout instead of waiting for ever
+            if rank == 1:
+                queue.put((rank, "left"))
+                return
+            try:
+                check_all_ranks_ok(None)
+                queue.put((rank, "no timeout"))
+            except ReplicaError:
+                queue.put((rank, "replica error"))
+            except Exception as e:       # gloo's timeout / connection-closed error
+                queue.put((rank, "collective failed"))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+@pytest.mark.parametrize("mode", ["error", "absent"])
+def test_gloo_ranks_learn_of_a_failed_or_absent_rank(mode):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, mode, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    if mode == "error":
+        assert results == {0: [1], 1: [1]}
+    else:
+        assert results[1] == "left" and results[0] == "collective failed"

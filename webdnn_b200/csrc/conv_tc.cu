@@ -107,7 +107,6 @@ struct TcProblem {
   int full_tiles;
   int splits;
   int kbs;
-  int early_consts;   // 1: the per-channel addends are constants of the model (may be read before the grid dependency resolves)
   int tma_epi;        // 1: residual tiles and output tiles move by TMA (map_res, map_y)
   int c4;             // 1: input has 4 channels per pixel, one K block per filter row, chunk j = tap kx;
                       // 2: the same with the row physically padded on the left and stride_w 2, so that taps
@@ -425,7 +424,6 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       ss->shift_tab[i] = (p.shift && i < p.N) ? p.shift_mul * __ldg(p.shift + i) : 0.f;
   };
   const bool use_shift_tab = p.tma_epi && p.N <= SHIFT_TAB;
-  if (use_shift_tab && p.early_consts) fill_shift_tab();
   if (threadIdx.x == 32) {
     // descriptor fetches of the first TMA operations overlap the rest of the set-up
     asm volatile("prefetch.tensormap [%0];" ::"l"((unsigned long long)&map_w_hi) : "memory");
@@ -459,7 +457,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
   // become resident as this grid's CTAs exit, and it waits for this grid's completion at the same point.
   grid_dependency_wait();
   grid_launch_dependents();
-  if (use_shift_tab && !p.early_consts) {
+  if (use_shift_tab) {   // the addends may have been produced by an earlier grid (a computed Gemm C row): after the wait
     fill_shift_tab();
     __syncthreads();
   }
@@ -1141,38 +1139,46 @@ __global__ void __launch_bounds__(256) split_tf32_transpose_kernel(const float* 
   }
 }
 
-// Second pass of a split reduction: y[m, n] = epilogue(sum over ranges of ws[range * m_pad + m, n]), ranges added in
-// ascending order (deterministic), then shift, residual and Relu as in the fused epilogue.  N % 4 == 0.
+// Second pass for the tiles whose reduction was cut into ranges: for tile `full_tiles + r`, block (r * splits + s)
+// of the workspace holds the raw partial sums of range s as 128 rows x tile_n columns.  The ranges are added in
+// ascending order (deterministic), then shift, residual and Relu are applied as in the fused epilogue.  N % 4 == 0.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ ws, float* __restrict__ y,
                                                             const float* __restrict__ shift, float shift_mul,
                                                             const float* __restrict__ residual, int64_t res_stride,
-                                                            float res_mul, int relu, int64_t M, int N, int64_t m_pad,
-                                                            int splits) {
-  const int nv = N / 4;
-  const int64_t total = M * nv;
+                                                            float res_mul, int relu, int64_t M, int N, int tile_n,
+                                                            int tiles_n, int full_tiles, int rest_tiles, int splits) {
+  grid_dependency_wait();   // launched as a programmatic dependent of the contraction kernel
+  const int tv = tile_n / 4;                       // float4 cells per tile row
+  const int64_t total = (int64_t)rest_tiles * TILE_M * tv;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t step = (int64_t)gridDim.x * blockDim.x;
   for (; i < total; i += step) {
-    const int64_t m = i / nv;
-    const int c = (int)(i - m * nv) * 4;
+    const int c4 = (int)(i % tv);
+    const int row = (int)((i / tv) % TILE_M);
+    const int r = (int)(i / ((int64_t)tv * TILE_M));
+    const int tile = full_tiles + r;
+    const int64_t m = (int64_t)(tile / tiles_n) * TILE_M + row;
+    const int n = (tile % tiles_n) * tile_n + c4 * 4;
+    if (m >= M || n >= N) continue;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (shift) {
-      const float4 b = __ldg(reinterpret_cast<const float4*>(shift + c));
+      const float4 b = __ldg(reinterpret_cast<const float4*>(shift + n));
       acc = make_float4(shift_mul * b.x, shift_mul * b.y, shift_mul * b.z, shift_mul * b.w);
     }
+    const float* src = ws + (((int64_t)r * splits) * TILE_M + row) * tile_n + c4 * 4;
     for (int s = 0; s < splits; s++) {
-      const float4 v = __ldg(reinterpret_cast<const float4*>(ws + (s * m_pad + m) * N + c));
+      const float4 v = *reinterpret_cast<const float4*>(src + (int64_t)s * TILE_M * tile_n);
       acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
     }
     if (residual) {
-      const float4 r = __ldg(reinterpret_cast<const float4*>(residual + m * res_stride + c));
-      acc.x = fmaf(res_mul, r.x, acc.x); acc.y = fmaf(res_mul, r.y, acc.y);
-      acc.z = fmaf(res_mul, r.z, acc.z); acc.w = fmaf(res_mul, r.w, acc.w);
+      const float4 rr = __ldg(reinterpret_cast<const float4*>(residual + m * res_stride + n));
+      acc.x = fmaf(res_mul, rr.x, acc.x); acc.y = fmaf(res_mul, rr.y, acc.y);
+      acc.z = fmaf(res_mul, rr.z, acc.z); acc.w = fmaf(res_mul, rr.w, acc.w);
     }
     if (relu) {
       acc.x = relu_nan(acc.x); acc.y = relu_nan(acc.y); acc.z = relu_nan(acc.z); acc.w = relu_nan(acc.w);
     }
-    *reinterpret_cast<float4*>(y + m * N + c) = acc;
+    *reinterpret_cast<float4*>(y + m * N + n) = acc;
   }
 }
 
@@ -1443,36 +1449,43 @@ bool encode_a_map(TcState* st, const TcProblem& p, const float* x, CUtensorMap* 
   return r == CUDA_SUCCESS;
 }
 
-// Tile width and reduction split for an [M, N] output with `kblocks` K blocks.  The widest tile is the
-// cheapest per column (a 64-column MMA costs about 0.65 of a 128-column one, a 32-column one about 0.45),
-// but a small problem cut into wide tiles leaves most SMs without work.  Such a problem can also cut its
-// reduction into ranges that run as separate work units (each at least 8 K blocks long, at most 8 ranges);
-// the ranges' partial sums then go through a workspace and a second, memory-bound pass, charged here as a
-// twentieth of a tile.  The estimate waves(units / SMs) x cost / splits picks both.
+// Tile width and the treatment of the last, partly filled wave for an [M, N] output with `kblocks` K blocks.
+// The widest tile is the cheapest per column (a 64-column MMA costs about 0.65 of a 128-column one, a 32-column
+// one about 0.45), but tiles are dealt to the SMs in waves, and the tiles of the last wave (`rest`, fewer than the
+// SMs) cost a whole tile time however few they are.  Those tiles can cut their reduction into `splits` ranges that
+// run as separate work units (each at least 4 K blocks long, at most 8 ranges): the last wave then takes
+// ceil(rest * splits / SMs) / splits of a tile time, plus a second, memory-bound pass over the rest tiles' partial
+// sums, charged here as a twentieth of a tile time per full wave of such tiles.  The estimate picks width and split.
 void choose_tiling(const wdc_context* ctx, int64_t m, int64_t n, int kblocks, bool may_split, int* tile_n,
-                   int* splits) {
+                   int* splits, int* full_tiles) {
   const int widest = pick_tile_n(n);
   const double cost[3] = {0.45, 0.65, 1.0};
+  const int sms = ctx->sm_count;
   double best_t = 1e300;
   *tile_n = widest;
   *splits = 1;
+  *full_tiles = 0;
   for (int t = widest, i = widest == 128 ? 2 : widest == 64 ? 1 : 0; t >= 32; t >>= 1, i--) {
     const int64_t tiles = ceil_div64(m, TILE_M) * ceil_div64(n, t);
-    int smax = 1;
-    if (may_split && tiles * 2 <= ctx->sm_count) {
-      smax = (int)(ctx->sm_count / tiles);
-      if (smax > 8) smax = 8;
-      if (smax > kblocks / 8) smax = kblocks / 8;
-      if (smax < 1) smax = 1;
+    if (tiles >= (1ll << 31) - 65536) continue;
+    const int64_t waves = tiles / sms, rest = tiles - waves * sms;
+    const double whole = (double)ceil_div64(tiles, sms) * cost[i];
+    if (whole < best_t - 1e-9) {
+      best_t = whole;
+      *tile_n = t;
+      *splits = 1;
+      *full_tiles = (int)tiles;
     }
-    for (int sp = 1; sp <= smax; sp++) {
+    if (!may_split || rest == 0) continue;
+    for (int sp = 2; sp <= 8 && kblocks / sp >= 4; sp++) {
       const int kbs = (kblocks + sp - 1) / sp;
       if ((sp - 1) * kbs >= kblocks) continue;   // an empty last range
-      const double est = (double)ceil_div64(tiles * sp, ctx->sm_count) * cost[i] * kbs / kblocks + (sp > 1 ? 0.05 : 0.0);
+      const double est = ((double)waves + (double)ceil_div64(rest * sp, sms) * kbs / kblocks + 0.05 * rest / sms) * cost[i];
       if (est < best_t - 1e-9) {
         best_t = est;
         *tile_n = t;
         *splits = sp;
+        *full_tiles = (int)(waves * sms);
       }
     }
   }
@@ -1491,7 +1504,7 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
     const bool may_split = !p.c4 && p.N % 4 == 0 && p.M < (1ll << 27) && tc_state(ctx)->encode_im2col != nullptr &&
                            (((uintptr_t)p.shift | (uintptr_t)p.residual | (uintptr_t)y) & 15) == 0 &&
                            (!p.residual || p.res_stride % 4 == 0) && ctx->opt_split_k;
-    choose_tiling(ctx, p.M, p.N, p.kblocks, may_split, &p.tile_n, &p.splits);
+    choose_tiling(ctx, p.M, p.N, p.kblocks, may_split, &p.tile_n, &p.splits, &p.full_tiles);
   }
   const int mi = p.tile_n == 128 ? 2 : p.tile_n == 64 ? 1 : 0;
   if (!we->has_map[mi]) {
@@ -1520,61 +1533,82 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
 #endif
   p.single_pass = ctx->opt_precision == 1 ? 1 : 0;
   TcState* st = tc_state(ctx);
-  p.m_pad = (int64_t)p.tiles_m * TILE_M;
-  p.kbs = (p.kblocks + p.splits - 1) / p.splits;
-  // the epilogue of a split reduction belongs to the second pass
-  const float* ep_shift = p.shift;
-  const float* ep_residual = p.residual;
-  const int ep_relu = p.relu;
-  const float ep_shift_mul = p.shift_mul, ep_res_mul = p.res_mul;
-  const int64_t ep_res_stride = p.res_stride;
+  const int total_tiles = p.tiles_m * p.tiles_n;
   float* ws = nullptr;
   CUtensorMap map_a;
   bool a_by_tma = encode_a_map(st, p, x, &map_a);
-  if (p.splits > 1 && !a_by_tma) {   // geometry outside the im2col map: one range, gathering producers
-    p.splits = 1;
-    p.kbs = p.kblocks;
-  }
-  if (p.splits > 1) {
-    s = wdc_alloc(ctx, (int64_t)p.splits * p.m_pad * p.N * 4, (void**)&ws);
-    if (s != WDC_OK) return s;
-    p.shift = nullptr;
-    p.residual = nullptr;
-    p.relu = 0;
-  }
-  const int64_t units = (int64_t)p.tiles_m * p.tiles_n * p.splits;
-  int grid = (int)(units < ctx->sm_count ? units : ctx->sm_count);
-  // output (or workspace) and residual as row-major matrices cut into 32-row x cw-column boxes for the epilogue warps
-  CUtensorMap map_y = w_map_hi, map_res = w_map_hi;
+  if (!a_by_tma) p.splits = 1;   // geometry outside the im2col map: gathering producers, whole tiles only
+  if (p.splits == 1) p.full_tiles = total_tiles;
+  p.kbs = (p.kblocks + p.splits - 1) / p.splits;
+  const int rest_tiles = total_tiles - p.full_tiles;
+  // output, residual and split-range workspace as row-major matrices cut into 32-row x cw-column boxes for the
+  // epilogue warps
+  CUtensorMap map_y = w_map_hi, map_res = w_map_hi, map_ws = w_map_hi;
   {
     const int ncols = p.tile_n / 2, cw = ncols < 32 ? ncols : 32;
     bool can = (p.N % 4 == 0) && p.M < (1ll << 31) && !TC_DBG(p, 64) && (((uintptr_t)p.scale | (uintptr_t)p.shift) & 15) == 0;
-    if (can) {
-      if (p.splits > 1) can = encode_rows_map(st, &map_y, ws, (int64_t)p.splits * p.m_pad, p.N, p.N, cw) == 0;
-      else can = encode_rows_map(st, &map_y, y, p.M, p.N, p.N, cw) == 0;
-    }
+    if (can) can = encode_rows_map(st, &map_y, y, p.M, p.N, p.N, cw) == 0;
     if (can && p.residual)
       can = p.res_stride % 4 == 0 && encode_rows_map(st, &map_res, p.residual, p.M, p.N, p.res_stride, cw) == 0;
     p.tma_epi = can ? 1 : 0;
+    if (!can && p.splits > 1) {   // split ranges leave through the TMA epilogue only
+      p.splits = 1;
+      p.full_tiles = total_tiles;
+      p.kbs = p.kblocks;
+    }
+    if (p.splits > 1) {
+      const int64_t ws_rows = (int64_t)rest_tiles * p.splits * TILE_M;
+      s = wdc_alloc(ctx, ws_rows * p.tile_n * 4, (void**)&ws);
+      if (s != WDC_OK) return s;
+      if (encode_rows_map(st, &map_ws, ws, ws_rows, p.tile_n, p.tile_n, cw) != 0) {
+        wdc_free(ctx, ws);
+        return wdc_fail(ctx, WDC_ERR_CUDA, "tensor map for the split-reduction workspace could not be encoded");
+      }
+    }
   }
-  if (p.splits > 1 && !p.tma_epi) {
-    wdc_free(ctx, ws);
-    return wdc_fail(ctx, WDC_ERR_CUDA, "tensor map for the split-reduction workspace could not be encoded");
-  }
+  const int64_t units = (int64_t)p.full_tiles + (int64_t)(total_tiles - p.full_tiles) * p.splits;
+  const int grid = (int)(units < ctx->sm_count ? units : ctx->sm_count);
   const size_t smem = sizeof(SharedStorage) + 1024;
-  if (!a_by_tma && p.c4 == 2) return WDC_ERR_UNSUPPORTED;  // the paired layout exists only for the TMA path
+  if (!a_by_tma && p.c4 == 2) {   // the paired layout exists only for the TMA path
+    if (ws) wdc_free(ctx, ws);
+    return WDC_ERR_UNSUPPORTED;
+  }
+  // Programmatic dependent launch: the grid may start while the previous grid of the stream drains; the kernel
+  // itself waits (griddepcontrol.wait) before it touches anything an earlier grid wrote or still reads.
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = ctx->stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx->opt_pdl ? 1 : 0;
+  const TcProblem& pc = p;
+  cudaError_t le;
   if (a_by_tma)
-    tc_igemm_kernel<true><<<grid, NUM_THREADS, smem, ctx->stream>>>(p, x, w_map_hi, w_map_lo, map_a, map_y, map_res, y);
+    le = cudaLaunchKernelEx(&cfg, tc_igemm_kernel<true>, pc, x, w_map_hi, w_map_lo, map_a, map_y, map_res, map_ws, y);
   else
-    tc_igemm_kernel<false><<<grid, NUM_THREADS, smem, ctx->stream>>>(p, x, w_map_hi, w_map_lo, w_map_hi, map_y,
-                                                                     map_res, y);
+    le = cudaLaunchKernelEx(&cfg, tc_igemm_kernel<false>, pc, x, w_map_hi, w_map_lo, w_map_hi, map_y, map_res, map_ws, y);
   ctx->n_tc_launch++;
-  s = wdc_check_launch(ctx, "tc_igemm_kernel");
+  ctx->n_launch++;
+  s = wdc_check_cuda(ctx, le, "tc_igemm_kernel");
+  if (s == WDC_OK) s = wdc_check_cuda(ctx, cudaGetLastError(), "tc_igemm_kernel");
   if (p.splits > 1) {
     if (s == WDC_OK) {
-      splitk_reduce_kernel<<<grid_for(ctx, p.M * (p.N / 4), 256, 8), 256, 0, ctx->stream>>>(
-          ws, y, ep_shift, ep_shift_mul, ep_residual, ep_res_stride, ep_res_mul, ep_relu, p.M, p.N, p.m_pad, p.splits);
-      s = wdc_check_launch(ctx, "splitk_reduce_kernel");
+      cudaLaunchConfig_t rc = {};
+      rc.gridDim = dim3((unsigned)grid_for(ctx, (int64_t)rest_tiles * TILE_M * (p.tile_n / 4), 256, 8));
+      rc.blockDim = dim3(256);
+      rc.stream = ctx->stream;
+      rc.attrs = attr;
+      rc.numAttrs = ctx->opt_pdl ? 1 : 0;
+      le = cudaLaunchKernelEx(&rc, splitk_reduce_kernel, (const float*)ws, y, p.shift, p.shift_mul, p.residual,
+                              p.res_stride, p.res_mul, p.relu, p.M, p.N, p.tile_n, p.tiles_n, p.full_tiles, rest_tiles,
+                              p.splits);
+      ctx->n_launch++;
+      s = wdc_check_cuda(ctx, le, "splitk_reduce_kernel");
+      if (s == WDC_OK) s = wdc_check_cuda(ctx, cudaGetLastError(), "splitk_reduce_kernel");
     }
     wdc_free(ctx, ws);   // stream-ordered: reused only by work queued after the reduction
   }

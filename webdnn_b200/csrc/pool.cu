@@ -195,6 +195,41 @@ __global__ void __launch_bounds__(256) gap_warp_kernel(const float* __restrict__
   }
 }
 
+// Short rows (a 7x7 map has 49 pixels): a whole warp per row leaves most lanes idle and one short load in flight,
+// so L lanes (4, 8 or 16) share a row and a warp works on 32 / L rows at once.  All of a row's loads are issued
+// before the first addition (up to 8 per lane), which is what keeps enough bytes in flight per SM.
+template <int L>
+__global__ void __launch_bounds__(256) gap_group_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                        int64_t rows, int64_t ch, int area, int64_t xs_n,
+                                                        int64_t xs_c, int64_t xs_p) {
+  const int gl = threadIdx.x % L;
+  const int64_t gid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / L;
+  const int64_t gstep = (int64_t)gridDim.x * blockDim.x / L;
+  const int64_t iters = (rows + gstep - 1) / gstep;      // the same for every lane: the shuffles need the whole warp
+  for (int64_t it = 0; it < iters; it++) {
+    const int64_t row = gid + it * gstep;
+    const bool valid = row < rows;
+    double s = 0;
+    if (valid) {
+      const int64_t b = row / ch, c = row - b * ch;
+      const float* p = x + b * xs_n + c * xs_c;
+      for (int a0 = gl; a0 < area; a0 += 8 * L) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          const int a = a0 + u * L;
+          v[u] = a < area ? __ldg(p + (int64_t)a * xs_p) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) s += (double)v[u];
+      }
+    }
+#pragma unroll
+    for (int o = L / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (valid && gl == 0) y[row] = (float)(s / (double)area);
+  }
+}
+
 extern "C" int wdc_global_avgpool(wdc_context* ctx, const float* x, float* y, int64_t batch, int64_t ch,
                                   int64_t area, int64_t xs_n, int64_t xs_c, int64_t xs_p) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_global_avgpool: null context");
@@ -206,6 +241,14 @@ extern "C" int wdc_global_avgpool(wdc_context* ctx, const float* x, float* y, in
   if (xs_c == 1) {
     gap_cl_kernel<<<grid_for(ctx, batch * ch, 256, 8), 256, 0, ctx->stream>>>(x, y, batch, ch, area, xs_n, xs_p);
     return wdc_check_launch(ctx, "gap_cl_kernel");
+  }
+  if (area <= 128) {
+    const int64_t rows = batch * ch;
+    const int a = (int)area;
+    if (area <= 32) gap_group_kernel<4><<<grid_for(ctx, rows * 4, 256, 8), 256, 0, ctx->stream>>>(x, y, rows, ch, a, xs_n, xs_c, xs_p);
+    else if (area <= 64) gap_group_kernel<8><<<grid_for(ctx, rows * 8, 256, 8), 256, 0, ctx->stream>>>(x, y, rows, ch, a, xs_n, xs_c, xs_p);
+    else gap_group_kernel<16><<<grid_for(ctx, rows * 16, 256, 8), 256, 0, ctx->stream>>>(x, y, rows, ch, a, xs_n, xs_c, xs_p);
+    return wdc_check_launch(ctx, "gap_group_kernel");
   }
   gap_warp_kernel<<<grid_for(ctx, batch * ch * 32, 256, 8), 256, 0, ctx->stream>>>(x, y, batch, ch, area,
                                                                                   xs_n, xs_c, xs_p);

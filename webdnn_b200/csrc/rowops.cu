@@ -102,6 +102,51 @@ __global__ void __launch_bounds__(512) softmax_block_kernel(const float* __restr
   }
 }
 
+// Rows of 1025 .. 256 * ITEMS elements: one CTA of 256 threads holds the row in registers (ITEMS per thread), so
+// the input is read from HBM once and the output written once, like the warp kernel does for short rows.
+__device__ __forceinline__ float block_reduce_f(float v, float* red, bool is_max) {
+  v = is_max ? warp_max(v) : warp_sum(v);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  __syncthreads();                 // red may still be read from the previous reduction
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = red[0];
+  for (int i = 1; i < (int)(blockDim.x >> 5); i++) t = is_max ? fmaxf(t, red[i]) : t + red[i];   // same order in every thread
+  return t;
+}
+template <int ITEMS>
+__global__ void __launch_bounds__(256) softmax_block_reg_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                                int64_t outer, int len) {
+  __shared__ float red[8];
+  for (int64_t row = blockIdx.x; row < outer; row += gridDim.x) {
+    const float* xr = x + row * len;
+    float v[ITEMS];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+      const int c = i * 256 + threadIdx.x;
+      v[i] = c < len ? xr[c] : -INFINITY;
+      mx = fmaxf(mx, v[i]);
+    }
+    mx = block_reduce_f(mx, red, true);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+      const int c = i * 256 + threadIdx.x;
+      v[i] = c < len ? expf(v[i] - mx) : 0.f;
+      s += v[i];
+    }
+    s = block_reduce_f(s, red, false);
+    const float inv = 1.f / s;
+    float* yr = y + row * len;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+      const int c = i * 256 + threadIdx.x;
+      if (c < len) yr[c] = v[i] * inv;
+    }
+  }
+}
+
 extern "C" int wdc_softmax(wdc_context* ctx, const float* x, float* y, int64_t outer, int64_t len) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_softmax: null context");
   wdc_note_write(ctx, y);
@@ -123,6 +168,15 @@ extern "C" int wdc_softmax(wdc_context* ctx, const float* x, float* y, int64_t o
     else SM(32);
 #undef SM
     return wdc_check_launch(ctx, "softmax_warp_kernel");
+  }
+  if (len <= 256 * 32) {
+    const int64_t cap = (int64_t)ctx->sm_count * 8;
+    const int grid = (int)(outer < cap ? outer : cap);
+    const int l = (int)len;
+    if (len <= 256 * 8) softmax_block_reg_kernel<8><<<grid, 256, 0, ctx->stream>>>(x, y, outer, l);
+    else if (len <= 256 * 16) softmax_block_reg_kernel<16><<<grid, 256, 0, ctx->stream>>>(x, y, outer, l);
+    else softmax_block_reg_kernel<32><<<grid, 256, 0, ctx->stream>>>(x, y, outer, l);
+    return wdc_check_launch(ctx, "softmax_block_reg_kernel");
   }
   int grid = (int)(outer < (int64_t)ctx->sm_count * 4 ? outer : (int64_t)ctx->sm_count * 4);
   softmax_block_kernel<<<grid, 512, 0, ctx->stream>>>(x, y, outer, len);
@@ -314,6 +368,49 @@ __global__ void __launch_bounds__(256) layernorm_block_kernel(const float* __res
   }
 }
 
+// Rows of 1025 .. 256 * ITEMS elements with the row held in the CTA's registers (one read of x).
+template <int ITEMS>
+__global__ void __launch_bounds__(256) layernorm_block_reg_kernel(const float* __restrict__ x,
+                                                                  const float* __restrict__ gamma,
+                                                                  const float* __restrict__ beta,
+                                                                  float* __restrict__ y, int64_t outer, int len,
+                                                                  float eps) {
+  __shared__ double scratch[8];
+  for (int64_t row = blockIdx.x; row < outer; row += gridDim.x) {
+    const float* xr = x + row * len;
+    float v[ITEMS];
+    double s = 0;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+      const int c = i * 256 + threadIdx.x;
+      v[i] = c < len ? xr[c] : 0.f;
+      s += (double)v[i];
+    }
+    const float mean = (float)(block_sum_d(s, scratch) / (double)len);
+    double q = 0;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+      const int c = i * 256 + threadIdx.x;
+      v[i] = v[i] - mean;                      // Sub
+      const float sq = v[i] * v[i];            // Mul / Pow 2
+      q += c < len ? (double)sq : 0.0;
+    }
+    const float var = (float)(block_sum_d(q, scratch) / (double)len);  // ReduceMean
+    const float rden = 1.f / sqrtf(var + eps);                            // Add, Sqrt; Div as a multiplication
+    float* yr = y + row * len;
+#pragma unroll
+    for (int i = 0; i < ITEMS; i++) {
+      const int c = i * 256 + threadIdx.x;
+      if (c < len) {
+        float r = v[i] * rden;                 // Div
+        if (gamma) r = r * gamma[c];           // Mul
+        if (beta) r = r + beta[c];             // Add
+        yr[c] = r;
+      }
+    }
+  }
+}
+
 extern "C" int wdc_layernorm(wdc_context* ctx, const float* x, const float* gamma, const float* beta,
                              float* y, int64_t outer, int64_t len, float eps) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_layernorm: null context");
@@ -322,6 +419,15 @@ extern "C" int wdc_layernorm(wdc_context* ctx, const float* x, const float* gamm
   if (outer == 0) return WDC_OK;
   WDC_REQUIRE(ctx, x && y, "wdc_layernorm: null buffer");
   DeviceGuard g(ctx->device);
+  if (len > 1024 && len <= 256 * 32) {
+    const int64_t cap = (int64_t)ctx->sm_count * 8;
+    const int grid = (int)(outer < cap ? outer : cap);
+    const int l = (int)len;
+    if (len <= 256 * 8) layernorm_block_reg_kernel<8><<<grid, 256, 0, ctx->stream>>>(x, gamma, beta, y, outer, l, eps);
+    else if (len <= 256 * 16) layernorm_block_reg_kernel<16><<<grid, 256, 0, ctx->stream>>>(x, gamma, beta, y, outer, l, eps);
+    else layernorm_block_reg_kernel<32><<<grid, 256, 0, ctx->stream>>>(x, gamma, beta, y, outer, l, eps);
+    return wdc_check_launch(ctx, "layernorm_block_reg_kernel");
+  }
   if (len > 1024) {
     const int64_t cap = (int64_t)ctx->sm_count * 8;
     layernorm_block_kernel<<<(int)(outer < cap ? outer : cap), 256, 0, ctx->stream>>>(x, gamma, beta, y, outer, len, eps);

@@ -8,8 +8,12 @@ Two deployment shapes:
 * one process per GPU (``torch.distributed.run``): ``shard_for_rank`` picks this rank's slice, the rank runs its own
   ``load(...)``-ed runner, ``gather_outputs`` concatenates the per-rank results on every rank (host-side
   all-gather; gloo on CPU tensors, so it also runs without GPUs);
-* one process, several contexts: ``ReplicaGroup`` owns one context + runner per device, enqueues all replicas
-  before it waits for any of them, and concatenates the outputs.
+* one process, several contexts: ``ReplicaGroup`` owns one ``CudaReplica`` (context + runner + pinned staging) per
+  device, enqueues all replicas from one host thread each before it waits for any of them, and concatenates the
+  outputs (through the host, or by peer copies into the first device).
+
+Failure handling is host-side: a replica that raises, returns an error status or misses a deadline is named in a
+``ReplicaError``; among processes ``check_all_ranks_ok`` makes every rank learn of a failed rank before the gather.
 """
 from __future__ import annotations
 
@@ -66,72 +70,203 @@ def _gather_uneven(parts, mine, group) -> None:
         dist.broadcast(p, src=dist.get_global_rank(group, r) if group is not None else r, group=group)
 
 
-class ReplicaGroup:
-    """N runners on N devices inside one process; batch slices run concurrently on their own streams."""
+class ReplicaError(RuntimeError):
+    """One or more replicas failed (an error status from the device library, an exception in an operator) or missed
+    the deadline.  ``failures`` maps the replica index to the exception (``TimeoutError`` for a missed deadline)."""
 
-    def __init__(self, source, devices: Sequence[int], batch_axis: int = 0, output_axes: Optional[Sequence[int]] = None):
+    def __init__(self, failures):
+        self.failures = dict(failures)
+        parts = [f"replica {i}: {type(e).__name__}: {e}" for i, e in sorted(self.failures.items())]
+        super().__init__("; ".join(parts))
+
+
+def check_all_ranks_ok(local_error: Optional[BaseException], group=None) -> None:
+    """One process per GPU: every rank reports whether its replica's step succeeded (host-side all-gather of one
+    integer) and every rank raises ``ReplicaError`` naming the failed ranks, so that no rank goes on to gather
+    slices that do not exist.  A rank that never arrives ends the collective with the process group's timeout,
+    which the caller sees as the backend's own exception."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    flags = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+    dist.all_gather(flags, torch.tensor([0 if local_error is None else 1], dtype=torch.int64), group=group)
+    failed = [r for r, f in enumerate(flags) if int(f.item()) != 0]
+    if failed:
+        me = dist.get_rank(group)
+        raise ReplicaError({r: (local_error if r == me else RuntimeError("reported a failed step")) for r in failed})
+
+
+class CudaReplica:
+    """One context + runner on one device.  ``start(shard)`` enqueues the replica's whole step without waiting for
+    the GPU: the shard is copied into pinned staging memory, moved on the context's copy stream
+    (wdc_upload_async) and run (as a replayed CUDA graph from the third step of a given shape on, when
+    ``graph_replay``); ``finish()`` waits and returns host arrays; ``finish_on_device()`` returns the device
+    tensors for a peer gather."""
+
+    def __init__(self, source, device: int, graph_replay: bool = True):
         from .backend import WebDNNCudaContext
         from .runner import load
-        self.batch_axis = batch_axis
-        self.output_axes = output_axes
-        self.contexts = []
-        self.runners = []
-        for d in devices:
-            ctx = WebDNNCudaContext(device=d)
-            ctx.initialize()
-            self.contexts.append(ctx)
-            self.runners.append(load(source, backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": ctx}}))
+        self.device = device
+        self.context = WebDNNCudaContext(device=device)
+        self.context.initialize()
+        self.runner = load(source, backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": self.context}})
+        self.graph_replay = graph_replay
+        self._pinned = {}       # (input index, shape, dtype) -> pinned staging array
+        self._captured = {}     # shape signature -> CapturedRun
+        self._seen = {}
+        self._pending = None
 
-    def run(self, inputs: Sequence[np.ndarray], gather: str = "host") -> List[np.ndarray]:
-        """``gather="host"``: every replica copies its output slice to the host.  ``gather="peer"``: the
-        slices are first collected on the first device by peer copies over NVLink (batch axis 0 only:
-        a replica's slice is then one contiguous range) and leave in one device-to-host transfer."""
+    def _stage(self, j: int, a: np.ndarray):
         from .backend import CPUTensor
-        if gather not in ("host", "peer"):
-            raise ValueError("gather must be 'host' or 'peer'")
-        n = len(self.runners)
-        pending = []
-        for i, runner in enumerate(self.runners):  # enqueue everything first: nothing here waits for a GPU
-            shard = shard_for_rank(inputs, i, n, self.batch_axis)
-            dev_in = [runner.backend_contexts["cuda"].move_tensor(CPUTensor.from_array(a)) for a in shard]
-            outs = runner.run(dev_in, outputs_on_device=True)
-            pending.append((dev_in, outs))
-        axes = self.output_axes or [self.batch_axis] * len(pending[0][1])
-        if gather == "peer":
-            if any(a != 0 for a in axes):
-                raise ValueError("gather='peer' needs outputs sharded along axis 0")
-            ctx0 = self.contexts[0]
-            results = []
-            for j in range(len(pending[0][1])):
-                parts = [ctx.canonical(outs[j]) for ctx, (_, outs) in zip(self.contexts, pending)]
-                dims = [sum(p.dims[0] for p in parts)] + list(parts[0].dims[1:])
-                whole = ctx0.empty_tensor(dims, parts[0].data_type)
-                off = 0
-                for ctx, p in zip(self.contexts, parts):
-                    ctx0.peer_copy_from(whole, off, ctx, p, p.length)
-                    off += p.length
-                results.append(whole.get_data().reshape(dims))
-                whole.dispose()
-                for p, (_, outs) in zip(parts, pending):
-                    if p is not outs[j]:
-                        p.dispose()
-            for dev_in, outs in pending:
-                for t in list(outs) + list(dev_in):
-                    t.dispose()
-            return results
-        per_output: List[List[np.ndarray]] = []
-        for dev_in, outs in pending:               # now drain, replica by replica
-            arrays = []
-            for o in outs:
-                arrays.append(o.get_data().reshape(o.dims))
-                o.dispose()
+        key = (j, a.shape, a.dtype.str)
+        buf = self._pinned.get(key)
+        if buf is None:
+            buf = self._pinned[key] = self.context.pinned_array(a.shape, a.dtype)
+        buf[...] = a
+        return CPUTensor(list(a.shape), "int32" if a.dtype == np.int32 else "float32", buf)
+
+    def start(self, shard: Sequence[np.ndarray]) -> None:
+        ctx = self.context
+        host = [self._stage(j, np.asarray(a)) for j, a in enumerate(shard)]
+        dev_in = [ctx.prefetch_tensor(t) for t in host]
+        sig = tuple((tuple(t.dims), t.data_type) for t in host)
+        cap = self._captured.get(sig)
+        if cap is None and self.graph_replay and self._seen.get(sig, 0) >= 1:
+            try:
+                cap = self._captured[sig] = self.runner.capture(dev_in)
+            except Exception:      # e.g. a node on the cpu backend: this replica keeps running node by node
+                self.graph_replay = False
+        self._seen[sig] = self._seen.get(sig, 0) + 1
+        if cap is not None:
+            for dst, src in zip(cap.inputs, dev_in):
+                ctx.wait_upload(src)
+                ctx._call("wdc_copy", _vp(dst.ptr), _vp(src.ptr), dst.length * 4)
+            cap.launch()
+            self._pending = (dev_in, list(cap.outputs), False)
+        else:
+            outs = self.runner.run(dev_in, outputs_on_device=True)
+            self._pending = (dev_in, outs, True)
+
+    def finish_on_device(self):
+        """(device tensors in canonical layout, release callback)."""
+        dev_in, outs, owned = self._pending
+        self._pending = None
+        canon = [self.context.canonical(o) for o in outs]
+
+        def release():
+            for c, o in zip(canon, outs):
+                if c is not o:
+                    c.dispose()
+                if owned:
+                    o.dispose()
             for t in dev_in:
                 t.dispose()
-            per_output.append(arrays)
-        return [np.concatenate([rep[j] for rep in per_output], axis=axes[j]) for j in range(len(per_output[0]))]
+        return canon, release
+
+    def finish(self) -> List[np.ndarray]:
+        canon, release = self.finish_on_device()
+        try:
+            return [c.get_data().reshape(c.dims) for c in canon]
+        finally:
+            release()
 
     def close(self) -> None:
-        for r in self.runners:
-            r.dispose()
-        for c in self.contexts:
-            c.close()
+        for cap in self._captured.values():
+            cap.dispose()
+        self._captured.clear()
+        self.runner.dispose()
+        self.context.close()
+
+
+def _vp(ptr: int):
+    from ctypes import c_void_p
+    return c_void_p(ptr)
+
+
+class ReplicaGroup:
+    """N replicas on N devices inside one process.  ``run`` slices the batch, lets one host thread per replica
+    enqueue that replica's step (so the per-node host work of the replicas overlaps; the device library releases the
+    interpreter lock inside its calls), then gathers.  ``replicas`` may be given instead of ``source``/``devices``:
+    any objects with ``start(shard)``, ``finish() -> [ndarray]`` and ``close()`` (the CPU tests pass stand-ins
+    that compute with the oracle, fail, or stall)."""
+
+    def __init__(self, source=None, devices: Sequence[int] = (), batch_axis: int = 0,
+                 output_axes: Optional[Sequence[int]] = None, replicas: Optional[Sequence[object]] = None,
+                 graph_replay: bool = True):
+        self.batch_axis = batch_axis
+        self.output_axes = output_axes
+        if replicas is not None:
+            self.replicas = list(replicas)
+        else:
+            self.replicas = [CudaReplica(source, d, graph_replay) for d in devices]
+        if not self.replicas:
+            raise ValueError("ReplicaGroup needs at least one replica")
+        self.contexts = [getattr(r, "context", None) for r in self.replicas]
+        self.runners = [getattr(r, "runner", None) for r in self.replicas]
+
+    def _on_threads(self, fn, deadline_s: Optional[float]):
+        """fn(i, replica) on one thread per replica; collects results, exceptions and missed deadlines."""
+        import threading
+        import time
+        n = len(self.replicas)
+        results, errors = [None] * n, {}
+
+        def work(i):
+            try:
+                results[i] = fn(i, self.replicas[i])
+            except BaseException as e:   # reported to the caller with the replica's index
+                errors[i] = e
+
+        threads = [threading.Thread(target=work, args=(i,), daemon=True) for i in range(n)]
+        t_end = None if deadline_s is None else time.monotonic() + deadline_s
+        for t in threads:
+            t.start()
+        for i, t in enumerate(threads):
+            t.join(None if t_end is None else max(t_end - time.monotonic(), 0.0))
+            if t.is_alive():
+                errors[i] = TimeoutError(f"no answer within {deadline_s} s")
+        if errors:
+            raise ReplicaError(errors)
+        return results
+
+    def run(self, inputs: Sequence[np.ndarray], gather: str = "host", deadline_s: Optional[float] = None) -> List[np.ndarray]:
+        """``gather="host"``: every replica copies its output slice to the host.  ``gather="peer"``: the slices are
+        first collected on the first device by peer copies over NVLink (batch axis 0 only: a replica's slice is
+        then one contiguous range) and leave in one device-to-host transfer.  ``deadline_s`` bounds each of the two
+        phases on the host; a replica that fails or stalls raises ``ReplicaError`` naming it (a stalled replica's
+        thread is abandoned, the group should then be closed)."""
+        if gather not in ("host", "peer"):
+            raise ValueError("gather must be 'host' or 'peer'")
+        n = len(self.replicas)
+        shards = [shard_for_rank(inputs, i, n, self.batch_axis) for i in range(n)]
+        self._on_threads(lambda i, r: r.start(shards[i]), deadline_s)      # enqueue everything first
+        if gather == "host":
+            per_replica = self._on_threads(lambda i, r: r.finish(), deadline_s)
+            axes = self.output_axes or [self.batch_axis] * len(per_replica[0])
+            return [np.concatenate([rep[j] for rep in per_replica], axis=axes[j]) for j in range(len(per_replica[0]))]
+        pending = [r.finish_on_device() for r in self.replicas]
+        n_out = len(pending[0][0])
+        axes = self.output_axes or [self.batch_axis] * n_out
+        if any(a != 0 for a in axes):
+            for _, release in pending:
+                release()
+            raise ValueError("gather='peer' needs outputs sharded along axis 0")
+        ctx0 = self.contexts[0]
+        results = []
+        for j in range(n_out):
+            parts = [canon[j] for canon, _ in pending]
+            dims = [sum(p.dims[0] for p in parts)] + list(parts[0].dims[1:])
+            whole = ctx0.empty_tensor(dims, parts[0].data_type)
+            off = 0
+            for ctx, p in zip(self.contexts, parts):
+                ctx0.peer_copy_from(whole, off, ctx, p, p.length)
+                off += p.length
+            results.append(whole.get_data().reshape(dims))
+            whole.dispose()
+        for _, release in pending:
+            release()
+        return results
+
+    def close(self) -> None:
+        for r in self.replicas:
+            r.close()

@@ -17,6 +17,7 @@ assert that nothing ran on the host except shape bookkeeping.
 """
 from __future__ import annotations
 
+import ctypes
 import json
 import logging
 import os
@@ -148,7 +149,15 @@ class Runner:
         ctx = self.backend_contexts.get("cuda")
         if ctx is None:
             raise RuntimeError("capture needs the cuda backend")
-        dev_in = [ctx.move_tensor(t) for t in inputs]
+        dev_in = []
+        for t in inputs:
+            if t.backend == "cpu":
+                dev_in.append(ctx.move_tensor(t))
+            else:   # a device tensor (e.g. a prefetched batch): the recorded run gets its own input buffer
+                ctx.wait_upload(t)
+                own = ctx.empty_tensor(t.dims, t.data_type)
+                ctx._call("wdc_copy", ctypes.c_void_p(own.ptr), ctypes.c_void_p(t.ptr), own.length * 4)
+                dev_in.append(own)
         for o in self.run(dev_in, outputs_on_device=True):
             o.dispose()
         if self.nodes_on("cpu"):
@@ -186,7 +195,9 @@ class Runner:
         if self.model is None or not self.loaded:
             raise RuntimeError("not initialized")
         if (self.graph_replay and not measure_performance and not outputs_on_device
-                and len(inputs) == len(self.inputs_without_initializer) and all(t.backend == "cpu" for t in inputs)):
+                and len(inputs) == len(self.inputs_without_initializer)
+                and all(t.backend == "cpu" or (t.backend == "cuda" and getattr(t, "layout", "nchw") == "nchw")
+                        for t in inputs)):
             sig = tuple((tuple(t.dims), t.data_type) for t in inputs)
             cap = self._captured.get(sig)
             if cap is None and not self._uncapturable and self._seen.get(sig, 0) >= 1 \
@@ -349,7 +360,13 @@ class CapturedRun:
         for dst, src in zip(self.inputs, inputs):
             if list(src.dims) != list(dst.dims) or src.data_type != dst.data_type:
                 raise ValueError("CapturedRun.run: input shape or dtype differs from the captured one")
-            dst.set_data(src.get_data())
+            if src.backend == "cpu":
+                dst.set_data(src.get_data())
+            else:
+                # a batch already on the device (moved there by prefetch_tensor while the previous run computed):
+                # order after its transfer, then a device-to-device copy into the recorded input buffer
+                self.context.wait_upload(src)
+                self.context._call("wdc_copy", ctypes.c_void_p(dst.ptr), ctypes.c_void_p(src.ptr), dst.length * 4)
         self.launch()
         return [self.context.cpu_context.empty_tensor(o.dims, o.data_type, o.get_data()) for o in self.outputs]
 

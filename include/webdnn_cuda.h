@@ -254,7 +254,10 @@ int wdc_instance_norm(wdc_context* ctx, const float* x, const float* scale, cons
  * score matrix kept on chip (one pass over the keys with a running row maximum and sum).  Not an operator of
  * the reference: it replaces the chain MatMul -> Mul -> Softmax -> MatMul that its graphs contain
  * (operators/cpu/operators/standard/matmul.ts:11-111, binary7.ts:16-68, softmax.ts:15-59) and is checked
- * against that chain.  Element (b, h, t, c) of q sits at q[b * q_sb + h * q_sh + t * q_st + c] (likewise k, v
+ * against that chain.  Both contractions run on the tensor cores (tcgen05, 3xTF32: scores and the running
+ * output live in tensor memory, K and V^T tiles arrive by TMA from a split copy made by a pre-pass in arena
+ * scratch); a CUDA-core kernel takes over when the tensor-map entry point or the scratch is unavailable.
+ * Element (b, h, t, c) of q sits at q[b * q_sb + h * q_sh + t * q_st + c] (likewise k, v
  * with tk rows and y with tq rows): head-split views of [batch, tokens, heads * dh] tensors need no transpose.
  * dh is 32 or 64 (else WDC_ERR_UNSUPPORTED); strides are multiples of 4 floats, buffers 16-byte aligned. */
 typedef struct wdc_attention_desc {

@@ -1,4 +1,7 @@
-"""Regenerates tests/golden/wdn2_golden.json from the reference checkout (needs /root/reference).
+"""Regenerates tests/golden/wdn2_golden.json from a checkout of the reference:
+
+    python tests/golden/make_wdn2_golden.py <path to the mil-tokyo/webdnn checkout>
+
 
 What is taken from the reference itself:
   * the 128 decode levels, parsed out of core/tensorDecoder/decodeTensorEightbit.ts;
@@ -15,14 +18,17 @@ import json
 import os
 import re
 import struct
+import sys
 
 import numpy as np
 
-REF = "/root/reference"
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def main():
+    if len(sys.argv) != 2 or not os.path.isdir(sys.argv[1]):
+        raise SystemExit(__doc__)
+    REF = sys.argv[1]
     ts = open(os.path.join(REF, "src/descriptor_runner/core/tensorDecoder/decodeTensorEightbit.ts")).read()
     body = ts[ts.index("const decodeTable = ["):ts.index("];")]
     table = [float(x) for x in re.findall(r"[0-9]+\.[0-9]+(?:e-?[0-9]+)?", body)]

@@ -30,7 +30,8 @@ def _device(ctx, a):
 
 
 @pytest.mark.parametrize("bh,tq,tk,dh", [(3, 70, 130, 32), (2, 64, 64, 32), (5, 1, 7, 32), (2, 100, 625, 32),
-                                         (3, 65, 129, 64), (1, 128, 200, 64)])
+                                         (3, 65, 129, 64), (1, 128, 200, 64), (2, 129, 1, 32), (1, 300, 63, 64),
+                                         (4, 257, 65, 32), (1, 5, 1000, 64)])
 def test_contiguous_heads_match_the_operator_chain(cuda_context, bh, tq, tk, dh):
     rng = np.random.default_rng(bh * 1000 + tq + tk + dh)
     q, k, v = (rng.standard_normal((bh, t, dh)).astype(np.float32) for t in (tq, tk, tk))
@@ -41,7 +42,9 @@ def test_contiguous_heads_match_the_operator_chain(cuda_context, bh, tq, tk, dh)
     y = ctx.empty_tensor([bh, tq, dh], "float32")
     d = AttentionDesc(batch=bh, heads=1, tq=tq, tk=tk, dh=dh, q_sb=tq * dh, q_sh=0, q_st=dh, k_sb=tk * dh, k_sh=0,
                       k_st=dh, v_sb=tk * dh, v_sh=0, v_st=dh, y_sb=tq * dh, y_sh=0, y_st=dh, scale=scale)
+    before = ctx.stats()["tensor_core_launches"]
     ctx._call("wdc_attention", byref(d), *(c_void_p(t.ptr) for t in (dq, dk, dv, y)))
+    assert ctx.stats()["tensor_core_launches"] == before + 1      # the tcgen05 kernel ran, not the CUDA-core one
     got = y.get_data().reshape(bh, tq, dh)
     assert max_err_rel_linf(got, want) <= TOL
     for t in (dq, dk, dv, y):

@@ -202,6 +202,9 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 }  // namespace
 
+int wdc_attention_tc(wdc_context* ctx, const wdc_attention_desc* d, const float* q, const float* k, const float* v,
+                     float* y);
+
 extern "C" int wdc_attention(wdc_context* ctx, const wdc_attention_desc* d, const float* q, const float* k,
                              const float* v, float* y) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_attention: null context");
@@ -230,6 +233,12 @@ extern "C" int wdc_attention(wdc_context* ctx, const wdc_attention_desc* d, cons
   p.scale = d->scale;
   dim3 grid((unsigned)((d->tq + ATT_BQ - 1) / ATT_BQ), (unsigned)(d->batch * d->heads));
   ProfScope prof(ctx, 4.0 * (double)d->batch * d->heads * d->tq * d->tk * d->dh);
+  {
+    // the tensor-core kernel (attention_tc.cu) takes every shape it can; the CUDA-core kernel below is what runs
+    // when the tensor-map entry point or the scratch memory is not to be had
+    const int s = wdc_attention_tc(ctx, d, q, k, v, y);
+    if (s != WDC_ERR_UNSUPPORTED) return s;
+  }
   if (d->dh == 32) {
     attention_kernel<32><<<grid, ATT_THREADS, attention_smem<32>(), ctx->stream>>>(p);   // 38 KB: no opt-in needed
   } else {

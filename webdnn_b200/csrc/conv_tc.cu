@@ -378,25 +378,29 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     return st < A_STAGES ? ss->a_raw[st] : ss->w_region + 2 * STAGES * (W_TILE_BYTES / 2) + (st - A_STAGES) * A_TILE_BYTES;
   };
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; s++) {
-      mbar_init(&ss->full_bar[s], NUM_A_WARPS + 1);
-      mbar_init(&ss->empty_bar[s], 1);
+  {
+    // one barrier per thread (38 of them): a single thread initialising them all costs half a microsecond per launch
+    const int t = threadIdx.x;
+    unsigned long long* bar = nullptr;
+    int count = 1;
+    if (t < STAGES) { bar = &ss->full_bar[t]; count = NUM_A_WARPS + 1; }
+    else if (t < 2 * STAGES) { bar = &ss->empty_bar[t - STAGES]; }
+    else if (t < 2 * STAGES + A_STAGES_MAX) { bar = &ss->a_full_bar[t - 2 * STAGES]; }
+    else if (t < 2 * STAGES + 2 * A_STAGES_MAX) { bar = &ss->a_empty_bar[t - 2 * STAGES - A_STAGES_MAX]; count = NUM_A_WARPS; }
+    else if (t < 2 * STAGES + 2 * A_STAGES_MAX + 2 * NUM_EPI_WARPS) {
+      const int i = t - 2 * STAGES - 2 * A_STAGES_MAX;
+      bar = &ss->res_bar[i >> 1][i & 1];
+    } else if (t < 2 * STAGES + 2 * A_STAGES_MAX + 2 * NUM_EPI_WARPS + NBUF) {
+      bar = &ss->seg_full_bar[t - 2 * STAGES - 2 * A_STAGES_MAX - 2 * NUM_EPI_WARPS];
+    } else if (t < 2 * STAGES + 2 * A_STAGES_MAX + 2 * NUM_EPI_WARPS + 2 * NBUF) {
+      bar = &ss->seg_empty_bar[t - 2 * STAGES - 2 * A_STAGES_MAX - 2 * NUM_EPI_WARPS - NBUF];
+      count = NUM_EPI_WARPS;
     }
-    for (int s = 0; s < A_STAGES_MAX; s++) {
-      mbar_init(&ss->a_full_bar[s], 1);
-      mbar_init(&ss->a_empty_bar[s], NUM_A_WARPS);
+    if (bar) {
+      mbar_init(bar, count);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    for (int w = 0; w < NUM_EPI_WARPS; w++) {
-      mbar_init(&ss->res_bar[w][0], 1);
-      mbar_init(&ss->res_bar[w][1], 1);
-    }
-    for (int b = 0; b < NBUF; b++) {
-      mbar_init(&ss->seg_full_bar[b], 1);
-      mbar_init(&ss->seg_empty_bar[b], NUM_EPI_WARPS);
-    }
-    ss->abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (t == 0) ss->abort_flag = 0;
   }
   for (int kb = threadIdx.x; !kTmaA && kb < p.kblocks && kb < KTAB; kb += NUM_THREADS) {
     KEntry e;
@@ -417,12 +421,6 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     }
     ss->ktab[kb] = e;
   }
-  auto fill_shift_tab = [&]() {
-    // entries a warp can touch: its first column (< tiles_n * tile_n) plus 64
-    const int used = p.tiles_n * p.tile_n + 64;
-    for (int i = threadIdx.x; i < used; i += NUM_THREADS)
-      ss->shift_tab[i] = (p.shift && i < p.N) ? p.shift_mul * __ldg(p.shift + i) : 0.f;
-  };
   const bool use_shift_tab = p.tma_epi && p.N <= SHIFT_TAB;
   if (threadIdx.x == 32) {
     // descriptor fetches of the first TMA operations overlap the rest of the set-up
@@ -457,10 +455,8 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
   // become resident as this grid's CTAs exit, and it waits for this grid's completion at the same point.
   grid_dependency_wait();
   grid_launch_dependents();
-  if (use_shift_tab) {   // the addends may have been produced by an earlier grid (a computed Gemm C row): after the wait
-    fill_shift_tab();
-    __syncthreads();
-  }
+  // (the table of per-column addends is filled by the epilogue warps themselves, after this wait: the addends may
+  // have been produced by an earlier grid, and the producer warps need not wait for the table)
   // Each CTA walks the K blocks of a full tile from a different starting point so that the CTAs, which all need
   // the same weight tiles, do not ask the same L2 lines at the same moment (split ranges start at their first block).
   const int rot_full = (int)(((int64_t)blockIdx.x * p.kblocks) / gridDim.x);
@@ -798,6 +794,14 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     int nseg = (p.kblocks + SEG_KBLOCKS - 1) / SEG_KBLOCKS;
     int64_t seg = 0;
     bool ok = true;
+    if (use_shift_tab) {
+      // entries a warp can touch: its first column (< tiles_n * tile_n) plus 64; the eight epilogue warps fill the
+      // table and meet at a barrier of their own (id 1, 256 threads), so the producers are not held up
+      const int used = p.tiles_n * p.tile_n + 64;
+      for (int i = threadIdx.x - EPI_WARP0 * 32; i < used; i += NUM_EPI_WARPS * 32)
+        ss->shift_tab[i] = (p.shift && i < p.N) ? p.shift_mul * __ldg(p.shift + i) : 0.f;
+      asm volatile("bar.sync 1, %0;" ::"n"(NUM_EPI_WARPS * 32) : "memory");
+    }
     if (p.tma_epi) {
       // ------------------------------------------------------------------ epilogue through TMA
       // The warp's 32 rows x ncols columns leave in chunks of 32 rows x cw columns.  Per chunk: the
@@ -963,7 +967,9 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
           }
         }
       }
-      if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      // the staging buffers must have been read before the CTA's shared memory goes away; the stores' arrival in
+      // global memory is covered by the grid's completion
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     } else {
       // ------------------------------------------------------------------ plain epilogue
     const int nchunks = ncols >> 4;

@@ -305,17 +305,23 @@ class ReplicaBench:
 
     def e2e_steps(self, n: int):
         """n end-to-end steps through the public API: every step's batch goes host -> device (ctx.prefetch_tensor,
-        from pinned memory, on the copy stream) and its result device -> host (runner.run returns CPU tensors).
-        The transfer of batch i+1 is queued before the kernels of batch i, so the two overlap; nothing is reused
-        between steps."""
+        from pinned memory, on the copy stream) and its result device -> host (runner.run(..., wait=False) queues the
+        kernels and the transfer of the outputs; PendingRun.result() waits for them).  The loop is the one a server
+        runs: batch i+1 is on its way and step i+1 is queued before the host reads the result of step i, so neither
+        the copies nor the host's enqueueing leave the GPU idle.  Every step's result is read inside the region."""
         ctx = self.ctx
         out = None
+        pending = None
         nxt = ctx.prefetch_tensor(self.x_host)
         for i in range(n):
             cur = nxt
             nxt = ctx.prefetch_tensor(self.x_host) if i + 1 < n else None
-            out = self.runner.run([cur])
+            p = self.runner.run([cur], wait=False)
             cur.dispose()
+            if pending is not None:
+                out = pending.result()
+            pending = p
+        out = pending.result()
         return out
 
     def launches_per_step(self) -> int:
@@ -341,10 +347,13 @@ def one_process_replicas(world: int, batch: int, steps: int, warmup: int) -> dic
     from webdnn_b200 import zoo
     from webdnn_b200.replicas import ReplicaGroup
     model = zoo.resnet50(batch // world)
-    x = zoo.make_input((batch, 3, 224, 224), seed=1)
     t_load = time.perf_counter()
     group = ReplicaGroup(model, devices=list(range(world)), graph_replay=batch // world <= GRAPH_MAX_BATCH)
     t_load = time.perf_counter() - t_load
+    # the batch sits in page-locked host memory, as in the other end-to-end figure: each replica transfers its
+    # slice straight from it (a pageable array would first be copied into the replica's staging buffer)
+    x = group.contexts[0].pinned_array((batch, 3, 224, 224), np.float32)
+    x[...] = zoo.make_input((batch, 3, 224, 224), seed=1)
     try:
         ref = None
         res = {}

@@ -71,6 +71,14 @@ int wdc_graph_launch(wdc_context* ctx, wdc_graph* graph);
 int wdc_graph_destroy(wdc_context* ctx, wdc_graph* graph);
 int wdc_upload_async(wdc_context* ctx, void* dst, const void* host, int64_t bytes, int64_t* ticket);
 int wdc_wait_upload(wdc_context* ctx, int64_t ticket);
+/* Device-to-host transfer on a third stream, for callers that queue the next run before they read the result of
+ * this one (the reference's getData, webgpuTensorImpl.ts:31-53, maps a staging buffer and awaits it; its runner
+ * has one run in flight).  The transfer starts after the work queued so far on the compute stream and does not
+ * hold up work queued later; wdc_wait_download blocks the host until that transfer has arrived (and reports an
+ * expired device wait like wdc_download).  `host` should be pinned; `src` must not be freed or overwritten before
+ * wdc_wait_download has returned. */
+int wdc_download_async(wdc_context* ctx, void* host, const void* src, int64_t bytes, int64_t* ticket);
+int wdc_wait_download(wdc_context* ctx, int64_t ticket);
 int wdc_copy(wdc_context* ctx, void* dst, const void* src, int64_t bytes);
 int wdc_fill_u32(wdc_context* ctx, void* dst, uint32_t value, int64_t count);
 int wdc_sync(wdc_context* ctx);

@@ -314,3 +314,39 @@ def test_global_average_pool_on_nchw_maps_of_every_size(cuda_context, shape):
     (got,) = run_cuda(model, [x], cuda_context)
     assert got.shape == want.shape == shape[:2] + (1, 1)
     assert max_err_rel_linf(got, want) <= 1e-6
+
+
+@pytest.mark.parametrize("shape", [(3, 64, 96), (2, 100, 36), (1, 132, 260), (2, 33, 64), (1, 1024, 68)])
+def test_batched_transpose_tiles_are_bit_exact(cuda_context, shape):
+    """[b, r, c] -> [b, c, r] through the 64x64 tile kernel with 16-byte accesses (both sizes multiples of 4 and at
+    least 32) and through the 32x32 kernel (33 rows): ragged tile edges on both axes."""
+    x = np.random.default_rng(sum(shape)).standard_normal(shape).astype(np.float32)
+    model = single_op_model("Transpose", {"perm": [0, 2, 1]}, [x])
+    (want,) = ref_runner.run_model(model, [x])
+    (got,) = run_cuda(model, [x], cuda_context)
+    assert got.shape == want.shape and np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("cin,cout,k,stride,pad,dil,outpad,bias,size", [
+    (32, 16, 3, 2, 0, 1, 0, False, (12, 12)),     # the reference benchmark's form (3x3, stride 2, no padding), small
+    (64, 40, 3, 2, 1, 1, 1, True, (9, 15)),       # padding, output_padding, bias, channel tile edge (40 of 64)
+    (32, 8, 4, 2, 1, 1, 0, True, (8, 16)),        # even kernel
+    (48, 33, 2, 1, 0, 1, 0, False, (12, 11)),     # stride 1; 33 output channels (N = 132, a multiple of 4)
+    (32, 12, 3, 3, 2, 2, 0, True, (10, 13)),      # stride 3 with dilation 2
+])
+def test_conv_transpose_through_matmul_and_col2im(cuda_context, cin, cout, k, stride, pad, dil, outpad, bias, size):
+    """ConvTranspose shapes large enough for the tensor-core route (convtranspose.ts:139-240 as one GEMM over the
+    input pixels and a col2im pass) against the oracle; two images, so the batch offset of col2im is covered."""
+    rng = np.random.default_rng(cin + cout + k)
+    x = rng.standard_normal((2, cin) + size).astype(np.float32)
+    w = (rng.standard_normal((cin, cout, k, k)) * 0.1).astype(np.float32)
+    ins = [x, w] + ([rng.uniform(-0.5, 0.5, cout).astype(np.float32)] if bias else [])
+    attrs = dict(kernel_shape=[k, k], strides=[stride, stride], pads=[pad] * 4, dilations=[dil, dil],
+                 output_padding=[outpad, outpad])
+    model = single_op_model("ConvTranspose", attrs, ins, n_graph_inputs=1)
+    (want,) = ref_runner.run_model(model, [x])
+    before = cuda_context.stats()["tensor_core_launches"]
+    (got,) = run_cuda(model, [x], cuda_context)
+    assert cuda_context.stats()["tensor_core_launches"] == before + 1
+    assert got.shape == want.shape
+    assert max_err_rel_linf(got, want) <= TOL

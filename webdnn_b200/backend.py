@@ -222,6 +222,22 @@ class WebDNNCPUContext:
                 raise TypeError("tensor is not CPUTensor")
 
 
+class PendingDownload:
+    """A device-to-host transfer in flight (WebDNNCudaContext.download_async)."""
+
+    def __init__(self, context, tensor, source, host, ticket):
+        self.context, self.tensor, self.source, self.host, self.ticket = context, tensor, source, host, ticket
+
+    def result(self) -> np.ndarray:
+        """Waits for the transfer and returns a copy of the data (the staging buffer is reused by later transfers)."""
+        self.context._call("wdc_wait_download", self.ticket)
+        out = np.array(self.host[:self.tensor.length], copy=True)
+        if self.source is not self.tensor:
+            self.source.dispose()
+        self.source = None
+        return out
+
+
 class WebDNNCudaContext:
     """Owns one device context (stream + arena) of libwebdnn_cuda.so."""
 
@@ -417,6 +433,28 @@ class WebDNNCudaContext:
                                        c_void_p(src.ptr), 4 * n_elements)
         if st != 0:
             self._L.check(self.handle, st)
+
+    def download_async(self, t: CudaTensor) -> "PendingDownload":
+        """Starts the device-to-host transfer of a tensor's (canonical) contents on the download stream and returns at
+        once; ``PendingDownload.result()`` waits for it.  Work queued on the context after this call does not delay
+        the transfer and is not delayed by it."""
+        src = self.canonical(t)
+        n = max(t.length, 1)
+        host = self._download_buffer(n, t.data_type)
+        ticket = ctypes.c_int64()
+        self._call("wdc_download_async", host.ctypes.data_as(c_void_p), c_void_p(src.ptr), t.length * 4, byref(ticket))
+        return PendingDownload(self, t, src, host, ticket.value)
+
+    def _download_buffer(self, n: int, data_type: str) -> np.ndarray:
+        """A pinned staging array of at least n elements, reused round-robin (pinned allocations are slow)."""
+        pool = self.__dict__.setdefault("_dl_pool", {})
+        key = (n, data_type)
+        ring = pool.setdefault(key, {"bufs": [], "next": 0})
+        if len(ring["bufs"]) < 4:
+            ring["bufs"].append(self.pinned_array((n,), NP_DTYPE[data_type]))
+            return ring["bufs"][-1]
+        ring["next"] = (ring["next"] + 1) % len(ring["bufs"])
+        return ring["bufs"][ring["next"]]
 
     def wait_upload(self, t: CudaTensor) -> None:
         """Compute stream waits (on the device, not the host) for the tensor's pending transfer."""

@@ -59,6 +59,12 @@ struct wdc_context {
   static const int kUploadTickets = 16;
   cudaEvent_t upload_done[kUploadTickets] = {};  // recorded on `copy_stream` after each transfer
   int64_t upload_seq = 0;
+  // third stream for device-to-host transfers that the host waits for while later work is already queued
+  cudaStream_t d2h_stream = nullptr;
+  cudaEvent_t d2h_fence = nullptr;               // recorded on `stream`, waited by `d2h_stream`
+  static const int kDownloadTickets = 32;
+  cudaEvent_t download_done[kDownloadTickets] = {};
+  int64_t download_seq = 0;
   // optional per-launch timing of the contraction kernels
   struct ProfRec {
     cudaEvent_t start, stop;

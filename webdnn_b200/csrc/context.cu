@@ -113,6 +113,13 @@ extern "C" int wdc_destroy(wdc_context* ctx) {
   }
   cudaFree(ctx->status_word);
   cudaFreeHost(ctx->status_word_host);
+  if (ctx->d2h_stream) {
+    cudaStreamSynchronize(ctx->d2h_stream);
+    cudaStreamDestroy(ctx->d2h_stream);
+    cudaEventDestroy(ctx->d2h_fence);
+    for (auto& ev : ctx->download_done)
+      if (ev) cudaEventDestroy(ev);
+  }
   if (ctx->copy_stream) {
     cudaStreamSynchronize(ctx->copy_stream);
     cudaStreamDestroy(ctx->copy_stream);
@@ -449,6 +456,48 @@ extern "C" int wdc_download(wdc_context* ctx, void* host, const void* src, int64
     ctx->d2h_bytes += bytes;
   }
   return wdc_sync(ctx);
+}
+
+extern "C" int wdc_download_async(wdc_context* ctx, void* host, const void* src, int64_t bytes, int64_t* ticket) {
+  if (!ctx || !ticket || bytes < 0 || (bytes > 0 && (!host || !src)))
+    return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_download_async: bad argument");
+  DeviceGuard g(ctx->device);
+  if (!ctx->d2h_stream) {
+    WDC_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->d2h_stream, cudaStreamNonBlocking));
+    WDC_CUDA(ctx, cudaEventCreateWithFlags(&ctx->d2h_fence, cudaEventDisableTiming));
+    for (auto& ev : ctx->download_done) WDC_CUDA(ctx, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+  }
+  if (ctx->download_seq - wdc_context::kDownloadTickets >= 0) {
+    // the event slot about to be reused belongs to a transfer issued kDownloadTickets calls ago: make sure it ran
+    WDC_CUDA(ctx, cudaEventSynchronize(ctx->download_done[ctx->download_seq % wdc_context::kDownloadTickets]));
+  }
+  // the transfer reads what the work queued so far on the compute stream produces, and nothing queued later
+  WDC_CUDA(ctx, cudaEventRecord(ctx->d2h_fence, ctx->stream));
+  WDC_CUDA(ctx, cudaStreamWaitEvent(ctx->d2h_stream, ctx->d2h_fence, 0));
+  if (bytes > 0)
+    WDC_CUDA(ctx, cudaMemcpyAsync(host, src, (size_t)bytes, cudaMemcpyDeviceToHost, ctx->d2h_stream));
+  // the device status word travels with it, so that wdc_wait_download can report an expired device wait
+  WDC_CUDA(ctx, cudaMemcpyAsync(ctx->status_word_host, ctx->status_word, sizeof(int), cudaMemcpyDeviceToHost,
+                                ctx->d2h_stream));
+  const int64_t t = ctx->download_seq++;
+  WDC_CUDA(ctx, cudaEventRecord(ctx->download_done[t % wdc_context::kDownloadTickets], ctx->d2h_stream));
+  ctx->d2h_bytes += bytes;
+  *ticket = t;
+  return WDC_OK;
+}
+
+extern "C" int wdc_wait_download(wdc_context* ctx, int64_t ticket) {
+  if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_wait_download: null context");
+  if (ticket < 0 || ticket >= ctx->download_seq)
+    return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_wait_download: unknown ticket %lld", (long long)ticket);
+  DeviceGuard g(ctx->device);
+  // a reused slot marks a later transfer of the same in-order stream, which implies this one
+  int64_t slot = ticket;
+  if (ctx->download_seq - ticket > wdc_context::kDownloadTickets) slot = ctx->download_seq - 1;
+  WDC_CUDA(ctx, cudaEventSynchronize(ctx->download_done[slot % wdc_context::kDownloadTickets]));
+  // a bounded device wait that expired before this point is reported here, like wdc_download does
+  if (*(volatile int*)ctx->status_word_host != 0) return report_device_status(ctx);
+  return WDC_OK;
 }
 
 extern "C" int wdc_copy(wdc_context* ctx, void* dst, const void* src, int64_t bytes) {

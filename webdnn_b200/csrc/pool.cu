@@ -202,31 +202,44 @@ template <int L>
 __global__ void __launch_bounds__(256) gap_group_kernel(const float* __restrict__ x, float* __restrict__ y,
                                                         int64_t rows, int64_t ch, int area, int64_t xs_n,
                                                         int64_t xs_c, int64_t xs_p) {
+  constexpr int R = 2;                                   // rows per lane group and iteration: twice the loads in flight
   const int gl = threadIdx.x % L;
   const int64_t gid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) / L;
   const int64_t gstep = (int64_t)gridDim.x * blockDim.x / L;
-  const int64_t iters = (rows + gstep - 1) / gstep;      // the same for every lane: the shuffles need the whole warp
+  const int64_t iters = (rows + R * gstep - 1) / (R * gstep);   // the same for every lane: the shuffles need the whole warp
+  const double inv_area = 1.0 / (double)area;
   for (int64_t it = 0; it < iters; it++) {
-    const int64_t row = gid + it * gstep;
-    const bool valid = row < rows;
-    double s = 0;
-    if (valid) {
-      const int64_t b = row / ch, c = row - b * ch;
-      const float* p = x + b * xs_n + c * xs_c;
-      for (int a0 = gl; a0 < area; a0 += 8 * L) {
-        float v[8];
+    float v[R][8];
+    int64_t row[R];
 #pragma unroll
-        for (int u = 0; u < 8; u++) {
-          const int a = a0 + u * L;
-          v[u] = a < area ? __ldg(p + (int64_t)a * xs_p) : 0.f;
+    for (int r = 0; r < R; r++) {
+      row[r] = gid + (it * R + r) * gstep;
+      const bool valid = row[r] < rows;
+      // rows of consecutive channels and images are equally spaced in a dense tensor (xs_n == ch * xs_c): no
+      // division then, and a 32-bit one otherwise (a 64-bit division costs more than the row's seven loads)
+      const float* p = x;
+      if (valid) {
+        if (xs_n == ch * xs_c) p = x + row[r] * xs_c;
+        else {
+          const uint32_t b = (uint32_t)row[r] / (uint32_t)ch, c = (uint32_t)row[r] - b * (uint32_t)ch;
+          p = x + (int64_t)b * xs_n + (int64_t)c * xs_c;
         }
+      }
 #pragma unroll
-        for (int u = 0; u < 8; u++) s += (double)v[u];
+      for (int u = 0; u < 8; u++) {
+        const int a = gl + u * L;
+        v[r][u] = (valid && a < area) ? __ldg(p + (int64_t)a * xs_p) : 0.f;
       }
     }
 #pragma unroll
-    for (int o = L / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (valid && gl == 0) y[row] = (float)(s / (double)area);
+    for (int r = 0; r < R; r++) {
+      double s = 0;
+#pragma unroll
+      for (int u = 0; u < 8; u++) s += (double)v[r][u];
+#pragma unroll
+      for (int o = L / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      if (row[r] < rows && gl == 0) y[row[r]] = (float)(s * inv_area);
+    }
   }
 }
 
@@ -242,7 +255,7 @@ extern "C" int wdc_global_avgpool(wdc_context* ctx, const float* x, float* y, in
     gap_cl_kernel<<<grid_for(ctx, batch * ch, 256, 8), 256, 0, ctx->stream>>>(x, y, batch, ch, area, xs_n, xs_p);
     return wdc_check_launch(ctx, "gap_cl_kernel");
   }
-  if (area <= 128) {
+  if (area <= 128 && batch * ch < (1ll << 31) && ch < (1ll << 31)) {
     const int64_t rows = batch * ch;
     const int a = (int)area;
     if (area <= 32) gap_group_kernel<4><<<grid_for(ctx, rows * 4, 256, 8), 256, 0, ctx->stream>>>(x, y, rows, ch, a, xs_n, xs_c, xs_p);

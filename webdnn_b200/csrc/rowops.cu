@@ -283,45 +283,60 @@ extern "C" int wdc_reduce_axis(wdc_context* ctx, int kind, int final, const floa
 // --------------------------------------------------------------------------- layer norm
 // Equals the reference's decomposed chain ReduceMean -> Sub -> Mul(x,x) -> ReduceMean -> Add(eps)
 // -> Sqrt -> Div -> Mul(gamma) -> Add(beta) with a float rounding after each node.
+// Per-lane partial sums (at most 32 addends) are taken in fp32 and only the lanes' partials are added in double:
+// converting every element to double made the conversion unit the limiter (63% of the HBM roofline for rows of
+// 256); the result differs from the all-double sum by a few 1e-7 relative.  Two rows per warp iteration keep
+// twice the loads in flight.
 template <int ITEMS>
 __global__ void __launch_bounds__(256) layernorm_warp_kernel(const float* __restrict__ x,
                                                              const float* __restrict__ gamma,
                                                              const float* __restrict__ beta,
                                                              float* __restrict__ y, int64_t outer,
                                                              int len, float eps) {
+  constexpr int R = ITEMS <= 8 ? 2 : 1;   // rows per warp iteration
+  const double inv_len = 1.0 / (double)len;   // a double division per row costs more than the rest of the row
   int lane = threadIdx.x & 31;
-  int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  int64_t rstep = (int64_t)gridDim.x * (blockDim.x >> 5);
-  for (; row < outer; row += rstep) {
-    const float* xr = x + row * len;
-    float v[ITEMS];
-    double s = 0;
+  int64_t row0 = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * R;
+  int64_t rstep = (int64_t)gridDim.x * (blockDim.x >> 5) * R;
+  for (; row0 < outer; row0 += rstep) {
+    float v[R][ITEMS];
+    float s[R];
 #pragma unroll
-    for (int i = 0; i < ITEMS; i++) {
-      int c = i * 32 + lane;
-      v[i] = c < len ? xr[c] : 0.f;
-      s += (double)v[i];
+    for (int r = 0; r < R; r++) {
+      const bool live = row0 + r < outer;
+      const float* xr = x + (row0 + r) * len;
+      s[r] = 0.f;
+#pragma unroll
+      for (int i = 0; i < ITEMS; i++) {
+        int c = i * 32 + lane;
+        v[r][i] = (live && c < len) ? xr[c] : 0.f;
+        s[r] += v[r][i];
+      }
     }
-    float mean = (float)(warp_sum_d(s) / (double)len);
-    double q = 0;
 #pragma unroll
-    for (int i = 0; i < ITEMS; i++) {
-      int c = i * 32 + lane;
-      v[i] = v[i] - mean;                      // Sub
-      float sq = v[i] * v[i];                  // Mul / Pow 2
-      q += c < len ? (double)sq : 0.0;
-    }
-    float var = (float)(warp_sum_d(q) / (double)len);  // ReduceMean
-    float rden = 1.f / sqrtf(var + eps);                // Add, Sqrt; the Div as a multiplication (within an ulp)
-    float* yr = y + row * len;
+    for (int r = 0; r < R; r++) {
+      if (row0 + r >= outer) continue;   // warp-uniform
+      float mean = (float)(warp_sum_d((double)s[r]) * inv_len);
+      float q = 0.f;
 #pragma unroll
-    for (int i = 0; i < ITEMS; i++) {
-      int c = i * 32 + lane;
-      if (c < len) {
-        float r = v[i] * rden;                 // Div
-        if (gamma) r = r * gamma[c];           // Mul
-        if (beta) r = r + beta[c];             // Add
-        yr[c] = r;
+      for (int i = 0; i < ITEMS; i++) {
+        int c = i * 32 + lane;
+        v[r][i] = v[r][i] - mean;                // Sub
+        float sq = v[r][i] * v[r][i];            // Mul / Pow 2
+        q += c < len ? sq : 0.f;
+      }
+      float var = (float)(warp_sum_d((double)q) * inv_len);  // ReduceMean
+      float rden = 1.f / sqrtf(var + eps);                // Add, Sqrt; the Div as a multiplication (within an ulp)
+      float* yr = y + (row0 + r) * len;
+#pragma unroll
+      for (int i = 0; i < ITEMS; i++) {
+        int c = i * 32 + lane;
+        if (c < len) {
+          float o = v[r][i] * rden;              // Div
+          if (gamma) o = o * gamma[c];           // Mul
+          if (beta) o = o + beta[c];             // Add
+          yr[c] = o;
+        }
       }
     }
   }
@@ -376,26 +391,27 @@ __global__ void __launch_bounds__(256) layernorm_block_reg_kernel(const float* _
                                                                   float* __restrict__ y, int64_t outer, int len,
                                                                   float eps) {
   __shared__ double scratch[8];
+  const double inv_len = 1.0 / (double)len;
   for (int64_t row = blockIdx.x; row < outer; row += gridDim.x) {
     const float* xr = x + row * len;
     float v[ITEMS];
-    double s = 0;
+    float s = 0.f;                             // per-thread partial (at most 32 addends) in fp32, then double
 #pragma unroll
     for (int i = 0; i < ITEMS; i++) {
       const int c = i * 256 + threadIdx.x;
       v[i] = c < len ? xr[c] : 0.f;
-      s += (double)v[i];
+      s += v[i];
     }
-    const float mean = (float)(block_sum_d(s, scratch) / (double)len);
-    double q = 0;
+    const float mean = (float)(block_sum_d((double)s, scratch) * inv_len);
+    float q = 0.f;
 #pragma unroll
     for (int i = 0; i < ITEMS; i++) {
       const int c = i * 256 + threadIdx.x;
       v[i] = v[i] - mean;                      // Sub
       const float sq = v[i] * v[i];            // Mul / Pow 2
-      q += c < len ? (double)sq : 0.0;
+      q += c < len ? sq : 0.f;
     }
-    const float var = (float)(block_sum_d(q, scratch) / (double)len);  // ReduceMean
+    const float var = (float)(block_sum_d((double)q, scratch) * inv_len);  // ReduceMean
     const float rden = 1.f / sqrtf(var + eps);                            // Add, Sqrt; Div as a multiplication
     float* yr = y + row * len;
 #pragma unroll

@@ -37,7 +37,10 @@ def shard_for_rank(inputs: Sequence[np.ndarray], rank: int, world: int, axis: in
         lo, hi = slice_bounds(a.shape[axis], world, rank)
         idx = [slice(None)] * a.ndim
         idx[axis] = slice(lo, hi)
-        out.append(np.ascontiguousarray(a[tuple(idx)]))
+        part = a[tuple(idx)]
+        # a slice along the leading axis is contiguous already: keep the view (and with it the page-locked
+        # property of an array that came from WebDNNCudaContext.pinned_array)
+        out.append(part if part.flags["C_CONTIGUOUS"] else np.ascontiguousarray(part))
     return out
 
 
@@ -118,6 +121,9 @@ class CudaReplica:
 
     def _stage(self, j: int, a: np.ndarray):
         from .backend import CPUTensor
+        if getattr(a, "_wdc_pinned", False) and a.flags["C_CONTIGUOUS"]:
+            # the caller's array is page-locked already (WebDNNCudaContext.pinned_array): transfer straight from it
+            return CPUTensor(list(a.shape), "int32" if a.dtype == np.int32 else "float32", a)
         key = (j, a.shape, a.dtype.str)
         buf = self._pinned.get(key)
         if buf is None:
@@ -127,7 +133,7 @@ class CudaReplica:
 
     def start(self, shard: Sequence[np.ndarray]) -> None:
         ctx = self.context
-        host = [self._stage(j, np.asarray(a)) for j, a in enumerate(shard)]
+        host = [self._stage(j, a if isinstance(a, np.ndarray) else np.asarray(a)) for j, a in enumerate(shard)]
         dev_in = [ctx.prefetch_tensor(t) for t in host]
         sig = tuple((tuple(t.dims), t.data_type) for t in host)
         cap = self._captured.get(sig)

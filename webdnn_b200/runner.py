@@ -187,13 +187,18 @@ class Runner:
 
     # ---- runnerImpl.ts:315-596
     def run(self, inputs: Sequence[CPUTensor], measure_performance: bool = False,
-            outputs_on_device: bool = False) -> List[CPUTensor]:
+            outputs_on_device: bool = False, wait: bool = True):
         """``inputs`` are CPUTensors as in the reference; a tensor that already lives on a device
         backend is filed under that backend instead (used to time the device path with resident
         inputs).  ``outputs_on_device`` skips the final move to the cpu and returns the device
-        tensors, which the caller must dispose."""
+        tensors, which the caller must dispose.  ``wait=False`` returns a ``PendingRun`` at once: the
+        kernels and the device-to-host transfer of the outputs are queued, ``PendingRun.result()`` waits for
+        them and returns the CPU tensors, so a caller can queue the next run before it reads this one
+        (the reference's run() is a promise the caller awaits: the counterpart of awaiting it later)."""
         if self.model is None or not self.loaded:
             raise RuntimeError("not initialized")
+        if not wait:
+            return self._run_pending(inputs)
         if (self.graph_replay and not measure_performance and not outputs_on_device
                 and len(inputs) == len(self.inputs_without_initializer)
                 and all(t.backend == "cpu" or (t.backend == "cuda" and getattr(t, "layout", "nchw") == "nchw")
@@ -328,6 +333,34 @@ class Runner:
                     t.dispose()
         return results
 
+    def _run_pending(self, inputs) -> "PendingRun":
+        ctx = self.backend_contexts.get("cuda")
+        if ctx is None:
+            return PendingRun(None, [], [], ready=self.run(inputs))
+        cap = None
+        if self.graph_replay and len(inputs) == len(self.inputs_without_initializer):
+            cap = self._captured.get(tuple((tuple(t.dims), t.data_type) for t in inputs))
+        if cap is not None:
+            self.graph_replays += 1
+            cap.load_inputs(inputs)
+            cap.launch()
+            # the recorded output buffers are overwritten by the next replay: the transfer reads a private copy
+            outs = []
+            for o in cap.outputs:
+                c = ctx.empty_tensor(o.dims, o.data_type)
+                src = ctx.canonical(o)
+                ctx._call("wdc_copy", ctypes.c_void_p(c.ptr), ctypes.c_void_p(src.ptr), o.length * 4)
+                if src is not o:
+                    src.dispose()
+                outs.append(c)
+        else:
+            if self.graph_replay:   # the ordinary path records the graph on its second use of a signature
+                first = self.run(inputs)
+                return PendingRun(None, [], [], ready=first)
+            outs = self.run(inputs, outputs_on_device=True)
+        downloads = [ctx.download_async(o) if getattr(o, "backend", "cpu") == "cuda" else None for o in outs]
+        return PendingRun(ctx, outs, downloads)
+
     def nodes_on(self, backend: str) -> List[tuple]:
         return [n for n in self.node_backends if n[2] == backend]
 
@@ -339,6 +372,27 @@ class Runner:
             for t in kv.values():
                 t.dispose()
             kv.clear()
+
+
+class PendingRun:
+    """Outputs of a ``Runner.run(..., wait=False)`` whose kernels and device-to-host transfers are queued."""
+
+    def __init__(self, context, device_outputs, downloads, ready=None):
+        self.context, self.device_outputs, self.downloads, self.ready = context, device_outputs, downloads, ready
+
+    def result(self) -> List[CPUTensor]:
+        if self.ready is not None:
+            return self.ready
+        outs = []
+        for t, d in zip(self.device_outputs, self.downloads):
+            if d is None:
+                outs.append(t)            # an output that was produced on the cpu backend
+                continue
+            outs.append(self.context.cpu_context.empty_tensor(t.dims, t.data_type, d.result()))
+            t.dispose()
+        self.ready = outs
+        self.device_outputs, self.downloads = [], []
+        return outs
 
 
 class CapturedRun:
@@ -357,6 +411,13 @@ class CapturedRun:
     def run(self, inputs: Sequence[CPUTensor]) -> List[CPUTensor]:
         if len(inputs) != len(self.inputs):
             raise ValueError("length of inputs mismatch")
+        self.load_inputs(inputs)
+        self.launch()
+        return [self.context.cpu_context.empty_tensor(o.dims, o.data_type, o.get_data()) for o in self.outputs]
+
+    def load_inputs(self, inputs: Sequence[CPUTensor]) -> None:
+        if len(inputs) != len(self.inputs):
+            raise ValueError("length of inputs mismatch")
         for dst, src in zip(self.inputs, inputs):
             if list(src.dims) != list(dst.dims) or src.data_type != dst.data_type:
                 raise ValueError("CapturedRun.run: input shape or dtype differs from the captured one")
@@ -367,8 +428,6 @@ class CapturedRun:
                 # order after its transfer, then a device-to-device copy into the recorded input buffer
                 self.context.wait_upload(src)
                 self.context._call("wdc_copy", ctypes.c_void_p(dst.ptr), ctypes.c_void_p(src.ptr), dst.length * 4)
-        self.launch()
-        return [self.context.cpu_context.empty_tensor(o.dims, o.data_type, o.get_data()) for o in self.outputs]
 
     def dispose(self) -> None:
         if self.graph is None:

@@ -243,12 +243,17 @@ int wdc_gather(wdc_context* ctx, const void* data, const int32_t* idx, void* out
 /* ConvTranspose, 2-D, NCHW (operators/cpu/operators/standard/convtranspose.ts:30-263, shape rule
  * base/convtranspose.ts:34-104): x [batch, ch_in, in_h, in_w], w [ch_in, ch_out_per_group, k_h, k_w],
  * bias [group * ch_out_per_group] or NULL, y [batch, group * ch_out_per_group, out_h, out_w].  Rounding
- * points as in the reference: channel contraction per tap in double -> float32, taps summed in
- * double -> float32, bias added in float32. */
+ * points as in the reference: channel contraction per tap -> float32, taps summed in
+ * double -> float32, bias added in float32.  Large enough group-1 shapes run as the reference's own two steps on
+ * the device: one tensor-core GEMM over the input pixels (3xTF32) into arena scratch, then col2im. */
 typedef struct wdc_convt_desc {
   int64_t batch, ch_in, in_h, in_w;
   int64_t ch_out_per_group, group, k_h, k_w, out_h, out_w;
   int64_t stride_h, stride_w, pad_t, pad_l, dil_h, dil_w;
+  int64_t w_layout; /* 0: w as in ONNX, [ch_in, ch_out_per_group, k_h, k_w].  1: w re-laid out once by the caller as
+                     * [ch_in, k_h, k_w, ch_out_per_group] (a wdc_strided_copy), which the tensor-core route (group 1,
+                     * ch_in a multiple of 4 and at least 32, ch_out_per_group * k_h * k_w a multiple of 4, at least 128
+                     * input pixels) multiplies by directly; WDC_ERR_INVALID where that route does not apply. */
 } wdc_convt_desc;
 int wdc_conv_transpose2d(wdc_context* ctx, const wdc_convt_desc* d, const float* x, const float* w,
                          const float* bias, float* y);

@@ -49,5 +49,5 @@ def test_struct_layouts_match_header_field_counts():
     assert len(lib.GemmDesc._fields_) == 15 and ctypes.sizeof(lib.GemmDesc) == 12 * 8 + 3 * 4 + 4
     assert len(lib.ConvDesc._fields_) == 18 and ctypes.sizeof(lib.ConvDesc) == 16 * 8 + 8
     assert len(lib.PoolDesc._fields_) == 23 and ctypes.sizeof(lib.PoolDesc) == 22 * 8 + 8
-    assert len(lib.ConvTransposeDesc._fields_) == 16 and ctypes.sizeof(lib.ConvTransposeDesc) == 16 * 8
+    assert len(lib.ConvTransposeDesc._fields_) == 17 and ctypes.sizeof(lib.ConvTransposeDesc) == 17 * 8
     assert len(lib.AttentionDesc._fields_) == 18 and ctypes.sizeof(lib.AttentionDesc) == 17 * 8 + 8

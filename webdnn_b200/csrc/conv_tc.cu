@@ -1172,9 +1172,15 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
       acc = make_float4(shift_mul * b.x, shift_mul * b.y, shift_mul * b.z, shift_mul * b.w);
     }
     const float* src = ws + (((int64_t)r * splits) * TILE_M + row) * tile_n + c4 * 4;
-    for (int s = 0; s < splits; s++) {
-      const float4 v = *reinterpret_cast<const float4*>(src + (int64_t)s * TILE_M * tile_n);
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    // all ranges' loads first (at most 8 in flight per thread), then the additions in ascending order
+    float4 v[8];
+#pragma unroll
+    for (int s = 0; s < 8; s++)
+      v[s] = s < splits ? __ldcg(reinterpret_cast<const float4*>(src + (int64_t)s * TILE_M * tile_n))
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < 8; s++) {
+      if (s < splits) { acc.x += v[s].x; acc.y += v[s].y; acc.z += v[s].z; acc.w += v[s].w; }
     }
     if (residual) {
       const float4 rr = __ldg(reinterpret_cast<const float4*>(residual + m * res_stride + n));
@@ -1461,7 +1467,8 @@ bool encode_a_map(TcState* st, const TcProblem& p, const float* x, CUtensorMap* 
 // SMs) cost a whole tile time however few they are.  Those tiles can cut their reduction into `splits` ranges that
 // run as separate work units (each at least 4 K blocks long, at most 8 ranges): the last wave then takes
 // ceil(rest * splits / SMs) / splits of a tile time, plus a second, memory-bound pass over the rest tiles' partial
-// sums, charged here as a twentieth of a tile time per full wave of such tiles.  The estimate picks width and split.
+// sums, charged as a fixed 5 us (measured on ResNet-50's layers at batch 32: shorter reductions than about 20 K
+// blocks lose more to that launch than the split wins).  The estimate picks width and split.
 void choose_tiling(const wdc_context* ctx, int64_t m, int64_t n, int kblocks, bool may_split, int* tile_n,
                    int* splits, int* full_tiles) {
   const int widest = pick_tile_n(n);
@@ -1486,7 +1493,9 @@ void choose_tiling(const wdc_context* ctx, int64_t m, int64_t n, int kblocks, bo
     for (int sp = 2; sp <= 8 && kblocks / sp >= 4; sp++) {
       const int kbs = (kblocks + sp - 1) / sp;
       if ((sp - 1) * kbs >= kblocks) continue;   // an empty last range
-      const double est = ((double)waves + (double)ceil_div64(rest * sp, sms) * kbs / kblocks + 0.05 * rest / sms) * cost[i];
+      // the second pass is a launch of its own: about 5 us, i.e. 12 / kblocks of a 128-column tile's time (a K block
+      // of such a tile takes ~0.42 us), whatever the tile width
+      const double est = ((double)waves + (double)ceil_div64(rest * sp, sms) * kbs / kblocks) * cost[i] + 12.0 / kblocks;
       if (est < best_t - 1e-9) {
         best_t = est;
         *tile_n = t;

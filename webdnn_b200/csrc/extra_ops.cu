@@ -115,10 +115,11 @@ static int conv_transpose_by_gemm(wdc_context* ctx, const wdc_convt_desc* d, con
     const int64_t dims[3] = {d->batch, pix, cin}, ss[3] = {cin * pix, 1, pix}, ds[3] = {pix * cin, cin, 1};
     s = wdc_strided_copy(ctx, x, xt, 3, dims, ss, 0, ds, 0);
   }
-  if (s == WDC_OK) {   // w [cin, cog, taps] -> wp [cin, taps, cog]
+  if (s == WDC_OK && d->w_layout == 0) {   // w [cin, cog, taps] -> wp [cin, taps, cog]
     const int64_t dims[3] = {cin, taps, cog}, ss[3] = {cog * taps, 1, taps}, ds[3] = {taps * cog, cog, 1};
     s = wdc_strided_copy(ctx, w, wp, 3, dims, ss, 0, ds, 0);
   }
+  if (d->w_layout == 1) wp = const_cast<float*>(w);   // the caller's own re-laid-out copy: its split stays cached
   if (s == WDC_OK) {
     wdc_gemm_desc g = {};
     g.batch = 1; g.m = M; g.n = N; g.k = cin;
@@ -143,7 +144,8 @@ extern "C" int wdc_conv_transpose2d(wdc_context* ctx, const wdc_convt_desc* d, c
   WDC_REQUIRE(ctx, d != nullptr, "wdc_conv_transpose2d: null descriptor");
   WDC_REQUIRE(ctx, d->batch >= 0 && d->ch_in > 0 && d->group > 0 && d->ch_out_per_group > 0 && d->in_h > 0 &&
                        d->in_w > 0 && d->k_h > 0 && d->k_w > 0 && d->out_h >= 0 && d->out_w >= 0 && d->stride_h > 0 &&
-                       d->stride_w > 0 && d->dil_h > 0 && d->dil_w > 0 && d->ch_in % d->group == 0,
+                       d->stride_w > 0 && d->dil_h > 0 && d->dil_w > 0 && d->ch_in % d->group == 0 &&
+                       (d->w_layout == 0 || d->w_layout == 1),
               "wdc_conv_transpose2d: bad shape");
   const int64_t n = d->batch * d->group * d->ch_out_per_group * d->out_h * d->out_w;
   if (n == 0) return WDC_OK;
@@ -155,6 +157,7 @@ extern "C" int wdc_conv_transpose2d(wdc_context* ctx, const wdc_convt_desc* d, c
   if (d->group == 1 && d->ch_in % 4 == 0 && d->ch_in >= 32 && N % 4 == 0 && M >= 128 &&
       M * N < (1ll << 40) && d->out_w < (1ll << 30) && d->out_h < (1ll << 30))
     return conv_transpose_by_gemm(ctx, d, x, w, bias, y);
+  WDC_REQUIRE(ctx, d->w_layout == 0, "wdc_conv_transpose2d: w_layout 1 is only taken by the tensor-core route");
   conv_transpose2d_kernel<<<grid_for(ctx, n, 256, 8), 256, 0, ctx->stream>>>(*d, x, w, bias, y);
   return wdc_check_launch(ctx, "conv_transpose2d_kernel");
 }

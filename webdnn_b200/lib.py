@@ -53,7 +53,8 @@ class ConvDesc(Structure):
 
 class ConvTransposeDesc(Structure):
     _fields_ = [(n, c_int64) for n in ("batch", "ch_in", "in_h", "in_w", "ch_out_per_group", "group", "k_h", "k_w",
-                                       "out_h", "out_w", "stride_h", "stride_w", "pad_t", "pad_l", "dil_h", "dil_w")]
+                                       "out_h", "out_w", "stride_h", "stride_w", "pad_t", "pad_l", "dil_h", "dil_w",
+                                       "w_layout")]
 
 
 class AttentionDesc(Structure):

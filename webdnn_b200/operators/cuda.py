@@ -885,11 +885,26 @@ class CudaConvTranspose(OperatorImpl):
         out_h = st[0] * (in_h - 1) + op[0] + (ks[0] - 1) * dil[0] + 1 - pads[0] - pads[2]
         out_w = st[1] * (in_w - 1) + op[1] + (ks[1] - 1) * dil[1] + 1 - pads[1] - pads[3]
         cog = w.dims[1]
+        # Shapes the library runs as one tensor-core GEMM over the input pixels + col2im take the weight re-laid out
+        # as [ch_in, k_h, k_w, ch_out] (made once, kept with the persistent weight tensor like a Conv's packed
+        # weight), so that its hi/lo split stays cached and the run can be recorded as a graph.
+        wk = w
+        w_layout = 0
+        n_cols = cog * ks[0] * ks[1]
+        if (self.group == 1 and ch_in % 4 == 0 and ch_in >= 32 and n_cols % 4 == 0 and batch * in_h * in_w >= 128
+                and w is inputs[1]):
+            wk = inputs[1].aux.get("ckkc")
+            if wk is None:
+                taps = ks[0] * ks[1]
+                wk = context.empty_tensor([ch_in, ks[0], ks[1], cog], "float32")
+                context.strided_copy(w, wk, [ch_in, taps, cog], [cog * taps, 1, taps], 0, [taps * cog, cog, 1], 0)
+                inputs[1].aux["ckkc"] = wk
+            w_layout = 1
         d = ConvTransposeDesc(batch=batch, ch_in=ch_in, in_h=in_h, in_w=in_w, ch_out_per_group=cog, group=self.group,
                               k_h=ks[0], k_w=ks[1], out_h=out_h, out_w=out_w, stride_h=st[0], stride_w=st[1],
-                              pad_t=pads[0], pad_l=pads[1], dil_h=dil[0], dil_w=dil[1])
+                              pad_t=pads[0], pad_l=pads[1], dil_h=dil[0], dil_w=dil[1], w_layout=w_layout)
         y = context.empty_tensor([batch, cog * self.group, out_h, out_w], "float32")
-        context._call("wdc_conv_transpose2d", byref(d), _p(x), _p(w), _p(bias) if bias is not None else None, _p(y))
+        context._call("wdc_conv_transpose2d", byref(d), _p(x), _p(wk), _p(bias) if bias is not None else None, _p(y))
         for t, o in ((x, inputs[0]), (w, inputs[1])):
             if t is not o:
                 t.dispose()

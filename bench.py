@@ -276,7 +276,7 @@ class ReplicaBench:
         self.runner = load(self.model, backend_order=["cuda", "cpu"],
                            backend_options={"cuda": {"context": ctx, "graphReplay": graph}})
         self.plain = self.runner if not graph else load(
-            self.model, backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": ctx}})
+            self.model, backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": ctx, "graphReplay": False}})
         x_pinned = ctx.pinned_array((batch, 3, 224, 224), np.float32)
         x_pinned[...] = zoo.make_input((batch, 3, 224, 224), seed=seed)
         self.x_host = CPUTensor([batch, 3, 224, 224], "float32", x_pinned)
@@ -323,6 +323,19 @@ class ReplicaBench:
             pending = p
         out = pending.result()
         return out
+
+    def h2d_only_ms(self, n: int) -> float:
+        """Milliseconds per step of the input transfer alone (pinned host -> device, nothing computing): what the
+        host link gives this rank while every rank transfers at once."""
+        ctx = self.ctx
+        ctx.sync()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            t = ctx.prefetch_tensor(self.x_host)
+            ctx.wait_upload(t)
+            t.dispose()
+        ctx.sync()
+        return (time.perf_counter() - t0) * 1e3 / n
 
     def launches_per_step(self) -> int:
         self.ctx.sync()
@@ -474,6 +487,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     dev_ms, e2e_ms, st, out = timed_pair(rb)
     clocks = sampler.stop()
     checksum = float(out[0].numpy().sum())
+    barrier()
+    h2d_ms = rb.h2d_only_ms(args.steps)      # every rank at once: the share of the host link a rank really gets
 
     # ---- the contraction launches one by one (CUDA events around every wdc_conv2d / wdc_gemm launch), node by node,
     # over the same number of steps: the roofline's `achieved`
@@ -484,7 +499,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     k_ms, k_launches, k_flops = ctx.profile_read()
     ctx.profile_enable(False)
     barrier()
-    dev_ms, e2e_ms = max_over_ranks(dev_ms, e2e_ms)
+    dev_ms, e2e_ms, h2d_ms = max_over_ranks(dev_ms, e2e_ms, h2d_ms)
     # the roofline's denominators, measured AFTER the timed regions: seconds of back-to-back cuBLAS GEMMs pull the
     # clock down under the power cap, and a step timed right behind them would pay for it
     tf32_peak = tf32_sustained = None
@@ -492,7 +507,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         tf32_peak, tf32_sustained = measure_tf32_peak(local_rank, sustained_s=4.0 if world == 1 else 0.0)
     barrier()
 
-    # ---- weak scaling beside it (N > 1): the whole batch on every GPU, as the earlier rounds reported
+    # ---- weak scaling beside it (N > 1): the whole batch on every GPU, (the figure of a replica per GPU with a full batch each)
     weak = None
     if world > 1 and not args.no_weak:
         rb.close()
@@ -535,7 +550,11 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                        "l2": "no flush: a step streams > 1 GB of weights and activations through the 126 MB L2"},
             "e2e": {"value": e2e_value, "unit": "images/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": world * (st["h2d_bytes"] // args.steps),
-                    "d2h_bytes_per_step": world * (st["d2h_bytes"] // args.steps)},
+                    "d2h_bytes_per_step": world * (st["d2h_bytes"] // args.steps),
+                    "h2d_only_ms_per_step": h2d_ms,
+                    "h2d_only_gb_per_s": world * (st["h2d_bytes"] // args.steps) / (h2d_ms * 1e-3) / 1e9,
+                    "h2d_note": "the input transfer alone, all ranks at once (max over ranks): where this is close to "
+                                "e2e.ms_per_step the end-to-end figure is bound by the host link, not by the GPUs"},
             "gpu_launches": int(launches_per_step * args.steps * 2),
             "gpu_launches_note": f"{launches_per_step} kernel launches per step and rank (counted on a node-by-node "
                                  "step); two timed regions of `steps` steps each; a replayed graph issues the same kernels",
@@ -559,6 +578,19 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                                         "back to back for 4 s (peak_sustained, N = 1 only)"},
             "output_checksum": checksum,
         }
+        if world > 1:
+            # what stops the split batch from scaling linearly, in the line's own numbers: the step is the same 54
+            # contraction launches (plus split passes) whatever the share, and each launch has a floor
+            step_ms = dev_ms / args.steps
+            n_contr = int(k_launches) // max(args.steps, 1)
+            line["strong_scaling_limit"] = {
+                "images_per_gpu": B, "ms_per_step": step_ms, "kernel_launches_per_step": launches_per_step,
+                "contraction_launches_per_step": n_contr,
+                "us_per_contraction_launch": 1e3 * step_ms / max(n_contr, 1),
+                "note": "per contraction launch a persistent 148-CTA grid has a fixed cost (launch, pipeline fill, the last "
+                        "tile's epilogue: about 10 us) and, at this share, 1-3 waves of tiles per launch, so the cost is not "
+                        "amortised as it is at 256 images per GPU; a 218 KB / 512-TMEM-column CTA cannot share its SM with "
+                        "the next launch's CTA, so programmatic dependent launch hides the launch latency only"}
         if weak is not None:
             line["weak"] = weak
         if one_proc is not None:

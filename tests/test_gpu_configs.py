@@ -518,3 +518,26 @@ def test_pipelined_runs_equal_plain_runs(cuda_context, graph_replay):
         assert r.graph_replays >= 3
     r.dispose()
     plain.dispose()
+
+
+def test_graph_replay_is_automatic_for_small_batches_only(cuda_context):
+    """Without any option, runs whose inputs have a leading dimension of at most 32 are recorded on their second
+    use and replayed from then on (the host's per-node work is as long as the GPU's there); larger batches keep
+    running node by node; graphReplay=False switches it off.  Results are those of the node-by-node runner."""
+    from webdnn_b200.backend import CPUTensor
+    from webdnn_b200.runner import load
+    model = zoo.resnet50(2, size=32, width=8, classes=10)
+    auto = load(model, backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": cuda_context}})
+    off = load(model, backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": cuda_context, "graphReplay": False}})
+    for i in range(4):
+        x = zoo.make_input((2, 3, 32, 32), seed=20 + i)
+        want = off.run([CPUTensor.from_array(x)])[0].numpy()
+        got = auto.run([CPUTensor.from_array(x)])[0].numpy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), i
+    assert auto.graph_replays == 3 and off.graph_replays == 0
+    big = zoo.make_input((40, 3, 32, 32), seed=30)
+    for _ in range(3):
+        auto.run([CPUTensor.from_array(big)])
+    assert auto.graph_replays == 3          # 40 > 32: not recorded
+    auto.dispose()
+    off.dispose()

@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(64 * U, 1) lstm_persistent_kernel(const LstmAr
   float* h_s = reinterpret_cast<float*>(smem_raw);       // [B][ld]
   float* r_s = h_s + (size_t)B * ld;                     // [4 * U][ld], row = gate * U + unit
   float4* part = reinterpret_cast<float4*>(r_s + (size_t)4 * U * ld);  // [KS][B * U] (4 gates each)
-  __shared__ int s_ok, s_ok_copies;   // verdicts of the two bounded waits of a step (thread 0 decides for the CTA)
+  __shared__ int s_ok, s_ok_copies;   // outcomes of the two bounded waits of a step (thread 0 decides for the CTA)
   __shared__ __align__(8) unsigned long long h_bar;   // completion of the bulk copies of h_{t-1}
 
   const int tid = threadIdx.x;
@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(64 * U, 1) lstm_persistent_kernel(const LstmAr
               "l"(hsrc + (size_t)b * H), "r"((uint32_t)(H * 4)), "r"(smem_addr(&h_bar))
               : "memory");
       }
-      // One thread runs the bounded wait and the whole CTA follows its verdict, so that on expiry every thread
+      // One thread runs the bounded wait and the whole CTA follows its outcome, so that on expiry every thread
       // leaves together (no thread is left behind at a later __syncthreads).  After the barrier each thread
       // observes the completed phase itself, which is what orders its reads after the copies' writes; the
       // phase cannot advance before the next step's expect_tx, so this returns at the first poll.

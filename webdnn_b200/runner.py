@@ -69,11 +69,21 @@ class Runner:
         # backendOptions.cuda.graphReplay: the second run() with host inputs of a given signature (shapes and
         # dtypes) is recorded as a CUDA graph, and every later run() with that signature replays it
         self.graph_replay = False
+        # backendOptions.cuda.graphReplay = "auto" (the default): replay only runs whose inputs all have a leading
+        # dimension of at most GRAPH_REPLAY_AUTO_BATCH, where the host's per-node work is as long as the GPU's
+        self.graph_replay_auto = False
         self.graph_replays = 0                    # run() calls served by a replay
         self._captured: Dict[tuple, "CapturedRun"] = {}
         self._seen: Dict[tuple, int] = {}
         self._uncapturable = False
     MAX_CAPTURED_SIGNATURES = 4                   # each recorded run keeps its own activation memory
+    GRAPH_REPLAY_AUTO_BATCH = 32
+
+    def _replay_wanted(self, inputs) -> bool:
+        if self.graph_replay:
+            return True
+        return self.graph_replay_auto and all(len(t.dims) > 0 and t.dims[0] <= self.GRAPH_REPLAY_AUTO_BATCH
+                                              for t in inputs)
 
     # ---- runnerImpl.ts:88-134
     DEVICE_DECODE_MIN_ELEMENTS = 4096  # 8-bit initializers at least this large are decoded on the device
@@ -199,7 +209,7 @@ class Runner:
             raise RuntimeError("not initialized")
         if not wait:
             return self._run_pending(inputs)
-        if (self.graph_replay and not measure_performance and not outputs_on_device
+        if (self._replay_wanted(inputs) and not measure_performance and not outputs_on_device
                 and len(inputs) == len(self.inputs_without_initializer)
                 and all(t.backend == "cpu" or (t.backend == "cuda" and getattr(t, "layout", "nchw") == "nchw")
                         for t in inputs)):
@@ -338,7 +348,8 @@ class Runner:
         if ctx is None:
             return PendingRun(None, [], [], ready=self.run(inputs))
         cap = None
-        if self.graph_replay and len(inputs) == len(self.inputs_without_initializer):
+        replay = self._replay_wanted(inputs)
+        if replay and len(inputs) == len(self.inputs_without_initializer):
             cap = self._captured.get(tuple((tuple(t.dims), t.data_type) for t in inputs))
         if cap is not None:
             self.graph_replays += 1
@@ -354,7 +365,7 @@ class Runner:
                     src.dispose()
                 outs.append(c)
         else:
-            if self.graph_replay:   # the ordinary path records the graph on its second use of a signature
+            if replay and not self._uncapturable:   # the ordinary path records the graph on its second use of a signature
                 first = self.run(inputs)
                 return PendingRun(None, [], [], ready=first)
             outs = self.run(inputs, outputs_on_device=True)
@@ -481,6 +492,8 @@ def load(source: Union[str, bytes, Model], backend_order: Optional[Sequence[str]
         raise RuntimeError("No backend available: " + "; ".join(errors))
     order = [succeeded] if succeeded == "cpu" else [succeeded, "cpu"]
     runner = Runner(order, contexts)
-    runner.graph_replay = succeeded == "cuda" and bool(backend_options.get("cuda", {}).get("graphReplay", False))
+    gr = backend_options.get("cuda", {}).get("graphReplay", "auto")
+    runner.graph_replay = succeeded == "cuda" and gr is True
+    runner.graph_replay_auto = succeeded == "cuda" and gr == "auto"
     runner.load_model(source, onnx_basename)
     return runner

@@ -39,7 +39,7 @@ if ROOT not in sys.path:
 METRIC = "resnet50_fp32_inference_images_per_sec"
 # dram__bytes_read.sum + dram__bytes_write.sum of the contraction launches of one batch-256 step, per launch, from one
 # ncu capture of this workload (the algorithmic bytes of the same launches are 28.06 GB per step).
-CONTRACTION_DRAM_BYTES_PER_STEP_B256 = 25.166e9
+CONTRACTION_DRAM_BYTES_PER_STEP_B256 = 25.38e9
 GRAPH_MAX_BATCH = 32     # a rank whose share of the batch is at most this runs its step as a replayed CUDA graph
 
 

@@ -350,3 +350,22 @@ def test_conv_transpose_through_matmul_and_col2im(cuda_context, cin, cout, k, st
     assert cuda_context.stats()["tensor_core_launches"] == before + 1
     assert got.shape == want.shape
     assert max_err_rel_linf(got, want) <= TOL
+
+
+def test_conv_add_that_broadcasts_the_conv_output_up(cuda_context):
+    """The Add's other operand is larger than the convolution's output ([1,C,H,W] + [3,C,H,W]): the fused node must
+    return the broadcast shape, like binary7.ts does, not the convolution's."""
+    from webdnn_b200 import zoo
+    b = zoo._Builder(6)
+    h = b.conv("input", 16, 32, 3, 1, 1, bias=True)
+    h = b.node("Relu", [b.node("Add", ["addend", h])[0]])[0]
+    model = b.model([("input", [1, 16, 9, 9]), ("addend", [3, 32, 9, 9])], [(h, [3, 32, 9, 9])])
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((1, 16, 9, 9)).astype(np.float32)
+    a = rng.standard_normal((3, 32, 9, 9)).astype(np.float32)
+    (want,) = ref_runner.run_model(model, [x, a])
+    (got,), r = run_cuda(model, [x, a], cuda_context, return_runner=True)
+    assert [t for _, t, _ in r.node_backends] == ["CudaConvFused"]
+    r.dispose()
+    assert got.shape == want.shape == (3, 32, 9, 9)
+    assert max_err_rel_linf(got, want) <= TOL

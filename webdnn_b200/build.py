@@ -11,6 +11,8 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_PATH = os.path.join(HERE, "libwebdnn_cuda.so")
 SOURCES = ["context.cu", "pointwise.cu", "rowops.cu", "pool.cu", "layout.cu", "gemm_simt.cu",
            "conv_tc.cu", "lstm.cu", "lstm_persistent.cu", "extra_ops.cu", "attention.cu", "attention_tc.cu"]
+# WDC_BUILD_DEVELOP=1 in the environment adds -DWDC_TC_DEVELOP: the contraction kernel then carries its development
+# knock-out switches (read from WDC_TC_DEBUG); the shipped build has none.
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-Wall"] + (["-DWDC_TC_DEVELOP"] if os.environ.get("WDC_BUILD_DEVELOP") else [])
 

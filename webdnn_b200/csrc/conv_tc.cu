@@ -48,6 +48,7 @@
 // and returns.
 #include <cuda.h>
 
+#include <cstddef>
 #include <cstdlib>
 #include <cstring>
 #include <map>
@@ -62,6 +63,7 @@ constexpr int BLOCK_K = 32;           // fp32 elements per K block = one 128-byt
 constexpr int STAGES = 3;             // W tiles in shared memory and A (hi, lo) column groups in TMEM
 constexpr int A_STAGES = 3;           // raw A tiles in shared memory (kTmaA)
 constexpr int A_STAGES_MAX = 6;       // tiles of at most 64 columns leave half of the W region free: 3 more A stages
+constexpr int DUO_MIN_KBLOCKS = 4;    // shortest reduction that runs with two splitter groups (see duo_mode)
 constexpr int NUM_A_WARPS = 4;
 constexpr int TMA_WARP = 4;
 constexpr int MMA_WARP = 5;
@@ -121,7 +123,9 @@ struct TcProblem {
   float alpha, shift_mul, res_mul;
   int relu;
   int single_pass;    // 1: precision tf32x1 (one MMA per multiply-add on the truncated operands; no low parts)
+  uint32_t nap_ns;    // sleep between failed barrier polls (0: spin)
 #ifdef WDC_TC_DEVELOP
+  long long* prof;    // [grid][16] cycle counters of the warp roles (WDC_TC_PROF), or null
   int dbg;  // development knock-outs (WDC_TC_DEBUG): 1 = no A loads, 2 = no epilogue memory traffic, 4 = no MMAs
 #endif
   int* status;
@@ -160,6 +164,9 @@ struct __align__(1024) SharedStorage {
   volatile int abort_flag;
 };
 
+static_assert(offsetof(SharedStorage, a_raw) == offsetof(SharedStorage, w_region) + 2 * STAGES * W_TILE_BYTES,
+              "the raw A tiles follow the W region without a gap");
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
@@ -179,6 +186,18 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t 
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Non-blocking probe of a phase (try_wait may suspend the thread; this never does).
+__device__ __forceinline__ bool mbar_test(unsigned long long* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.b32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
@@ -208,15 +227,36 @@ __device__ __noinline__ bool mbar_wait_timed(unsigned long long* bar, uint32_t p
   }
 }
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, uint32_t parity, SharedStorage* ss,
-                                          int* status, int code) {
+                                          int* status, int code, uint32_t nap_ns = 100) {
   // Hot path: plain polling, no timer read.  After two failed polls the thread sleeps ~100 ns between
   // polls: under a sustained load the GPU runs at its power cap, and warps that spin at full issue rate
   // cost clock frequency for the tensor pipe (measured: 0.7% of a ResNet-50 step).
   for (int i = 0; i < 4096; i++) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (i >= 2) __nanosleep(100);
+    if (i >= 2 && nap_ns) __nanosleep(nap_ns);
   }
   return mbar_wait_timed(bar, parity, ss, status, code);
+}
+
+#ifdef WDC_TC_DEVELOP
+#define PROF_DECL(n) long long prof_acc[n] = {}; long long prof_t = clock64(); const long long prof_t0 = prof_t
+#define PROF_ADD(slot) do { const long long n_ = clock64(); prof_acc[slot] += n_ - prof_t; prof_t = n_; } while (0)
+#define PROF_OUT(base, n) do { if (p.prof) { for (int i_ = 0; i_ < (n); i_++) p.prof[blockIdx.x * 16 + (base) + i_] = prof_acc[i_]; \
+                                 p.prof[blockIdx.x * 16 + (base) + (n)] = clock64() - prof_t0; } } while (0)
+#define PROF_CNT(slot, cond) do { if (p.prof && (cond)) p.prof[blockIdx.x * 16 + (slot)] += 1; } while (0)
+#define PROF_EV(type, g) do { if (p.prof && blockIdx.x == 0 && (g) < 64) p.prof[2368 + (type) * 64 + (int)(g)] = clock64(); } while (0)
+#else
+#define PROF_EV(type, g)
+#define PROF_CNT(slot, cond)
+#define PROF_DECL(n)
+#define PROF_ADD(slot)
+#define PROF_OUT(base, n)
+#endif
+
+// Narrow tiles with a reduction long enough for the operand split to matter run with two splitter groups and four
+// epilogue warps; short reductions are bound by the epilogue's memory traffic and keep all eight epilogue warps.
+__host__ __device__ __forceinline__ bool duo_mode(const TcProblem& p, bool a_by_tma) {
+  return a_by_tma && p.tile_n <= 64 && p.kblocks >= DUO_MIN_KBLOCKS && !TC_DBG(p, 8192);
 }
 
 // Work unit u of a launch: a full tile (sp = -1, all K blocks), or range sp of one of the remaining tiles
@@ -370,10 +410,17 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
   const int total_units = p.full_tiles + (total_tiles - p.full_tiles) * p.splits;
   // shared-memory stage addresses
   const bool narrow = p.tile_n <= 64;
+  // Narrow tiles: the operand split, not the tensor pipe, is the serial path (a barrier or shared-memory round trip
+  // costs about 150 cycles, and a K block needs several).  Their epilogue is light (at most 64 columns), so four
+  // warps do it instead of eight and the other four become a second group of splitters: the groups take alternate
+  // K blocks.
+  const bool duo = duo_mode(p, kTmaA);
+  const int n_epi = duo ? NUM_EPI_WARPS / 2 : NUM_EPI_WARPS;
   const uint32_t w_slot = narrow ? W_TILE_BYTES / 2 : W_TILE_BYTES;
   const int a_stages = (kTmaA && narrow) ? A_STAGES_MAX : A_STAGES;
   auto w_hi_ptr = [&](int st) { return ss->w_region + (uint32_t)st * w_slot; };
   auto w_lo_ptr = [&](int st) { return ss->w_region + (uint32_t)(STAGES + st) * w_slot; };
+  // (the upper half of the W region and the raw A tiles behind it are one contiguous block of 96 KB)
   auto a_ptr = [&](int st) {
     return st < A_STAGES ? ss->a_raw[st] : ss->w_region + 2 * STAGES * (W_TILE_BYTES / 2) + (st - A_STAGES) * A_TILE_BYTES;
   };
@@ -394,7 +441,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       bar = &ss->seg_full_bar[t - 2 * STAGES - 2 * A_STAGES_MAX - 2 * NUM_EPI_WARPS];
     } else if (t < 2 * STAGES + 2 * A_STAGES_MAX + 2 * NUM_EPI_WARPS + 2 * NBUF) {
       bar = &ss->seg_empty_bar[t - 2 * STAGES - 2 * A_STAGES_MAX - 2 * NUM_EPI_WARPS - NBUF];
-      count = NUM_EPI_WARPS;
+      count = n_epi;
     }
     if (bar) {
       mbar_init(bar, count);
@@ -461,29 +508,40 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
   // the same weight tiles, do not ask the same L2 lines at the same moment (split ranges start at their first block).
   const int rot_full = (int)(((int64_t)blockIdx.x * p.kblocks) / gridDim.x);
 
-  if (kTmaA && warp < NUM_A_WARPS) {
+  if (kTmaA && (warp < NUM_A_WARPS || (duo && warp >= EPI_WARP0 + NUM_EPI_WARPS / 2))) {
     // ===================================================================== A producers (split only)
     // Thread (w, l) owns row 32w+l of the tile = TMEM lane.  Per K block: read the row's 32 raw
     // values from the swizzled shared-memory tile, write them unchanged as the high operand (the
     // tensor core ignores the low 13 bits of a tf32 operand, i.e. it truncates) and
     // lo = x - truncate(x), exact in fp32, as the low operand.
-    const int row = threadIdx.x;
+    const int q4 = warp & 3;                       // TMEM lane quadrant of this warp
+    const int row = q4 * 32 + lane;
+    const int group = warp < NUM_A_WARPS ? 0 : 1;  // second group: narrow tiles only
+    const int ngroups = duo ? 2 : 1;
+    const bool t0 = threadIdx.x == 0;
     int64_t items = 0;   // K blocks of all work units of this CTA
     for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
       int tile, sp, kb0, kbn;
       unit_of(p, u, tile, sp, kb0, kbn);
       items += kbn;
     }
-    const uint32_t lane_base = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)TMEM_A_COL0;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)TMEM_A_COL0;
     // normal mode: 128-byte rows, 16-byte chunks XOR-swizzled by the row; 4-channel mode: 8 planes
     // (one per filter tap of the row) of 128 rows x 16 bytes, or 4 planes (one per tap pair) of 128
     // rows x 32 bytes with the 32B swizzle (chunk ^= bit 2 of the row)
     const uint32_t row_off = (uint32_t)row * (p.c4 == 1 ? 16u : p.c4 == 2 ? 32u : 128u);
     const uint32_t sw = (uint32_t)(row & 7);
-    int stage = 0, as = 0;
+    // ring positions of K block g: TMEM / W stage g % STAGES, raw tile g % a_stages
+    int stage = group % STAGES, as = group % a_stages;
     uint32_t phase = 0, aphase = 0;
-    for (int64_t g = 0; g < items; g++) {
-      if (!mbar_wait(&ss->a_full_bar[as], aphase, ss, p.status, 11)) break;
+    bool a_tok = false;   // answer of the probe made one iteration earlier
+    PROF_DECL(5);
+    for (int64_t g = group; g < items; g += ngroups) {
+      PROF_ADD(4);
+      if (t0) PROF_CNT(10, !a_tok);
+      if (!a_tok && !mbar_wait(&ss->a_full_bar[as], aphase, ss, p.status, 11, p.nap_ns)) break;
+      PROF_ADD(0);
+      if (t0) PROF_EV(0, g);
       float4 v[8];
       const unsigned char* tile = a_ptr(as) + row_off;
 #pragma unroll
@@ -492,7 +550,23 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
             tile + (p.c4 == 1   ? (uint32_t)j * (TILE_M * 16u)
                     : p.c4 == 2 ? (uint32_t)(j >> 1) * (TILE_M * 32u) + ((((uint32_t)j & 1u) ^ ((uint32_t)(row >> 2) & 1u)) << 4)
                                 : (((uint32_t)j ^ sw) << 4)));
-      if (!mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 12)) break;
+      // A barrier operation takes about 150 cycles to answer even when the phase is long over.  So both barriers
+      // are probed without blocking while the shared-memory loads above are in flight: this K block's TMEM stage,
+      // and the raw tile of the group's NEXT K block (looked at one iteration later).  A probe that came too early
+      // falls back to the blocking wait.
+      int as_n = as + ngroups, stage_n = stage + ngroups;
+      uint32_t aphase_n = aphase, phase_n = phase;
+      if (as_n >= a_stages) { as_n -= a_stages; aphase_n ^= 1; }
+      if (stage_n >= STAGES) { stage_n -= STAGES; phase_n ^= 1; }
+      bool a_tok_n = false, e_tok = false;
+      if (!TC_DBG(p, 4096)) {
+        e_tok = mbar_test(&ss->empty_bar[stage], phase ^ 1);
+        if (g + ngroups < items) a_tok_n = mbar_test(&ss->a_full_bar[as_n], aphase_n);
+      }
+      if (t0) PROF_CNT(11, !e_tok);
+      if (!e_tok && !mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 12, p.nap_ns)) break;
+      PROF_ADD(1);
+      if (t0) PROF_EV(1, g);
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t a_hi = lane_base + (uint32_t)(stage * 64);
 #pragma unroll
@@ -514,13 +588,18 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       // the shared-memory tile has been read into registers: hand the slot back to the loader
       __syncwarp();
       if (lane == 0) mbar_arrive(&ss->a_empty_bar[as]);
+      PROF_ADD(2);
       asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      PROF_ADD(3);
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&ss->full_bar[stage]);
-      if (++stage == STAGES) { stage = 0; phase ^= 1; }
-      if (++as == a_stages) { as = 0; aphase ^= 1; }
+      if (t0) PROF_EV(2, g);
+      stage = stage_n; phase = phase_n;
+      as = as_n; aphase = aphase_n;
+      a_tok = a_tok_n;
     }
+    if (t0) PROF_OUT(0, 5);
   } else if (kTmaA && warp == ATMA_WARP) {
     // ===================================================================== A loader (im2col TMA)
     // One lane issues the loads; in 4-channel mode lane j issues the load of tap j of the filter row.
@@ -545,7 +624,12 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         int ky = tap / p.k_w, kx = tap - ky * p.k_w;
         if (p.c4) ky = kfirst;
         for (int kb = 0; kb < kbn; kb++) {
-          if (!mbar_wait(&ss->a_empty_bar[stage], phase ^ 1, ss, p.status, 22)) { ok = false; break; }
+          if (!mbar_wait(&ss->a_empty_bar[stage], phase ^ 1, ss, p.status, 22, p.nap_ns)) { ok = false; break; }
+          if (TC_DBG(p, 256)) {   // no A loads
+            if (lane == 0) mbar_arrive(&ss->a_full_bar[stage]);
+            if (++stage == a_stages) { stage = 0; phase ^= 1; }
+            continue;
+          }
           if (p.c4) {
             // K block = filter row ky; one load of 128 pixels x 4 channels per tap of the row, or of 128
             // pixel pairs x 8 channels per tap pair
@@ -669,7 +753,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       for (int j = 0; j < PREFETCH; j++) {
         const int64_t g = g0 + j;
         if (ok && g < items) {
-          ok = mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 12);
+          ok = mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 12, p.nap_ns);
           if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t a_hi = lane_base + (uint32_t)(stage * 64);
@@ -718,7 +802,12 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         unit_of(p, u, tile, sp, kb0, kbn);
         const int n0 = (int)(tile % p.tiles_n) * p.tile_n;
         for (int kb = 0; kb < kbn; kb++) {
-          if (!mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 21)) { ok = false; break; }
+          if (!mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 21, p.nap_ns)) { ok = false; break; }
+          if (TC_DBG(p, 128)) {   // no W loads: the MMAs read whatever the stage holds
+            mbar_arrive(&ss->full_bar[stage]);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            continue;
+          }
           mbar_arrive_expect_tx(&ss->full_bar[stage], bytes);
           int kr = kb0 + kb + (sp < 0 ? rot_full : 0);
           if (kr >= kb0 + kbn) kr -= kbn;
@@ -743,6 +832,10 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       const uint32_t idesc = make_idesc(p.tile_n);
       int64_t seg = 0;  // segments issued by this CTA so far
       bool ok = true;
+      bool f_tok = false;   // answer of the probe made one K block earlier
+      bool s_tok = false;   // the same for the next segment's accumulator
+      PROF_DECL(3);
+      int gk = 0;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         int tile, sp, kb0, kbn;
         unit_of(p, u, tile, sp, kb0, kbn);
@@ -750,13 +843,27 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         int buf = 0;
         for (int kb = 0; kb < kbn; kb++) {
           const int in_seg = kb % SEG_KBLOCKS;
+          PROF_ADD(2);
           if (in_seg == 0) {
             buf = (int)(seg % NBUF);
-            if (!mbar_wait(&ss->seg_empty_bar[buf], (uint32_t)((seg / NBUF) & 1) ^ 1, ss, p.status, 31)) { ok = false; break; }
+            if (!s_tok && !mbar_wait(&ss->seg_empty_bar[buf], (uint32_t)((seg / NBUF) & 1) ^ 1, ss, p.status, 31, p.nap_ns)) { ok = false; break; }
+            s_tok = false;
+            PROF_ADD(0);
+            PROF_EV(5, gk);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             d_tmem = tmem_base + (uint32_t)(buf * 128);
           }
-          if (!mbar_wait(&ss->full_bar[stage], phase, ss, p.status, 32)) { ok = false; break; }
+          PROF_CNT(12, !f_tok);
+          if (!f_tok && !mbar_wait(&ss->full_bar[stage], phase, ss, p.status, 32, p.nap_ns)) { ok = false; break; }
+          PROF_ADD(1);
+          PROF_EV(3, gk);
+          // probe the next stage's barrier before issuing this stage's MMAs (see the operand splitters)
+          const int stage_n = stage + 1 == STAGES ? 0 : stage + 1;
+          const uint32_t phase_n = stage_n ? phase : phase ^ 1;
+          f_tok = !TC_DBG(p, 4096) && mbar_test(&ss->full_bar[stage_n], phase_n);
+          // ... and, on a segment's last K block, the accumulator the next segment will use
+          if ((in_seg == SEG_KBLOCKS - 1 || kb == kbn - 1) && !TC_DBG(p, 4096))
+            s_tok = mbar_test(&ss->seg_empty_bar[(int)((seg + 1) % NBUF)], (uint32_t)(((seg + 1) / NBUF) & 1) ^ 1);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_hi = tmem_base + (uint32_t)(TMEM_A_COL0 + stage * 64);
           const uint32_t a_lo = a_hi + 32u;
@@ -776,31 +883,34 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
             umma_tf32_ts(d_tmem, a_hi + acol, dw_hi + adv, idesc, 1u);
           }
           umma_commit(&ss->empty_bar[stage]);  // stage reusable once these MMAs have read it
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          PROF_EV(4, gk);
+          gk++;
+          stage = stage_n; phase = phase_n;
           if (in_seg == SEG_KBLOCKS - 1 || kb == kbn - 1) {
             umma_commit(&ss->seg_full_bar[buf]);  // partial sum of this segment is complete
             seg++;
           }
         }
       }
+      PROF_OUT(6, 3);
     }
   } else if (warp >= EPI_WARP0) {
     // ===================================================================== accumulate + epilogue warps
     const int ew = warp - EPI_WARP0;
     const int q = warp & 3;                       // TMEM lane quadrant this warp may read
-    const int half = ew >> 2;                     // which half of the tile's columns
-    const int ncols = p.tile_n >> 1;              // 16, 32 or 64 columns per warp
+    const int half = ew >> 2;                     // which half of the tile's columns (eight warps)
+    const int ncols = duo ? p.tile_n : p.tile_n >> 1;   // 16, 32 or 64 columns per warp
     const int col0 = half * ncols;
     int nseg = (p.kblocks + SEG_KBLOCKS - 1) / SEG_KBLOCKS;
     int64_t seg = 0;
     bool ok = true;
     if (use_shift_tab) {
-      // entries a warp can touch: its first column (< tiles_n * tile_n) plus 64; the eight epilogue warps fill the
+      // entries a warp can touch: its first column (< tiles_n * tile_n) plus 64; the epilogue warps fill the
       // table and meet at a barrier of their own (id 1, 256 threads), so the producers are not held up
       const int used = p.tiles_n * p.tile_n + 64;
-      for (int i = threadIdx.x - EPI_WARP0 * 32; i < used; i += NUM_EPI_WARPS * 32)
+      for (int i = threadIdx.x - EPI_WARP0 * 32; i < used; i += n_epi * 32)
         ss->shift_tab[i] = (p.shift && i < p.N) ? p.shift_mul * __ldg(p.shift + i) : 0.f;
-      asm volatile("bar.sync 1, %0;" ::"n"(NUM_EPI_WARPS * 32) : "memory");
+      asm volatile("bar.sync 1, %0;" ::"r"(n_epi * 32) : "memory");
     }
     if (p.tma_epi) {
       // ------------------------------------------------------------------ epilogue through TMA
@@ -880,7 +990,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         }
         for (int s = 0; s < nseg && ok; s++, seg++) {
           const int buf = (int)(seg % NBUF);
-          ok = mbar_wait(&ss->seg_full_bar[buf], (uint32_t)((seg / NBUF) & 1), ss, p.status, 42);
+          ok = mbar_wait(&ss->seg_full_bar[buf], (uint32_t)((seg / NBUF) & 1), ss, p.status, 42, p.nap_ns);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 128 + col0);
@@ -906,7 +1016,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
             unsigned char* sbuf = ss->epi_buf[ew][b];
             // buffer b is free: with a residual, its load was issued after the store that last read
             // the buffer had finished; without, lane 0 has waited for that store before this point
-            if (res_u) ok = mbar_wait(&ss->res_bar[ew][b], (uint32_t)((k >> 1) & 1), ss, p.status, 43);
+            if (res_u) ok = mbar_wait(&ss->res_bar[ew][b], (uint32_t)((k >> 1) & 1), ss, p.status, 43, p.nap_ns);
             __syncwarp();
             if (ok) {
               // 4 cells (16 columns) at a time: residual reads first, then arithmetic and writes, so
@@ -1021,7 +1131,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
             }
           }
         }
-        ok = mbar_wait(&ss->seg_full_bar[buf], (uint32_t)((seg / NBUF) & 1), ss, p.status, 42);
+        ok = mbar_wait(&ss->seg_full_bar[buf], (uint32_t)((seg / NBUF) & 1), ss, p.status, 42, p.nap_ns);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * 128 + col0);
@@ -1213,20 +1323,23 @@ __global__ void pad_channels4_kernel(const float* __restrict__ x, float* __restr
 }
 // Same with every image row shifted right by pad_l pixels into a zero-filled row of wp pixels: pixel pair
 // (2j, 2j+1) of the padded row is then the pair of taps (2j, 2j+1) of output column j for stride 2.
-__global__ void pad_channels4_rows_kernel(const float* __restrict__ x, float* __restrict__ x4, int64_t rows, int w,
-                                          int wp, int pad_l, int cin, int h_nchw) {
-  int64_t total = rows * wp;
+// With hp > h the images are padded vertically too: pad_t zero rows above, hp - pad_t - h below.
+__global__ void pad_channels4_rows_kernel(const float* __restrict__ x, float* __restrict__ x4, int64_t images, int h,
+                                          int hp, int pad_t, int w, int wp, int pad_l, int cin, int nchw) {
+  int64_t total = images * hp * wp;
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t step = (int64_t)gridDim.x * blockDim.x;
   for (; i < total; i += step) {
-    const int64_t r = i / wp;
-    const int px = (int)(i - r * wp) - pad_l;
+    const int64_t rp = i / wp;
+    const int px = (int)(i - rp * wp) - pad_l;
+    const int64_t img = rp / hp;
+    const int yy = (int)(rp - img * hp) - pad_t;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (px >= 0 && px < w) {
-      // h_nchw = 0: NHWC rows; > 0: NCHW with h_nchw rows per image (row r = image * h + y)
-      const int64_t plane = (int64_t)h_nchw * w;
-      const float* s = h_nchw ? x + (r / h_nchw) * plane * cin + (r % h_nchw) * w + px : x + (r * w + px) * cin;
-      const int64_t cs = h_nchw ? plane : 1;
+    if (px >= 0 && px < w && yy >= 0 && yy < h) {
+      // NHWC rows, or NCHW planes of h x w
+      const int64_t plane = (int64_t)h * w;
+      const float* s = nchw ? x + img * plane * cin + (int64_t)yy * w + px : x + ((img * h + yy) * w + px) * cin;
+      const int64_t cs = nchw ? plane : 1;
       v.x = s[0];
       if (cin > 1) v.y = s[cs];
       if (cin > 2) v.z = s[2 * cs];
@@ -1536,6 +1649,7 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
   p.tiles_m = (int)ceil_div64(p.M, TILE_M);
   p.tiles_n = (int)ceil_div64(p.N, p.tile_n);
   p.status = ctx->status_word;
+  p.nap_ns = 100;
 #ifdef WDC_TC_DEVELOP
   {
     static int dbg = -1;
@@ -1544,6 +1658,20 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
       dbg = e ? atoi(e) : 0;
     }
     p.dbg = dbg;
+    static int nap = -2;
+    if (nap == -2) {
+      const char* e = getenv("WDC_TC_NAP");
+      nap = e ? atoi(e) : -1;
+    }
+    if (nap >= 0) p.nap_ns = (uint32_t)nap;
+  }
+  static long long* prof_buf = nullptr;
+  static int prof_on = -1;
+  if (prof_on < 0) prof_on = getenv("WDC_TC_PROF") ? 1 : 0;
+  if (prof_on) {
+    if (!prof_buf) cudaMalloc(&prof_buf, 256 * 16 * sizeof(long long));
+    cudaMemsetAsync(prof_buf, 0, 256 * 16 * sizeof(long long), ctx->stream);
+    p.prof = prof_buf;
   }
 #endif
   p.single_pass = ctx->opt_precision == 1 ? 1 : 0;
@@ -1560,7 +1688,8 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
   // epilogue warps
   CUtensorMap map_y = w_map_hi, map_res = w_map_hi, map_ws = w_map_hi;
   {
-    const int ncols = p.tile_n / 2, cw = ncols < 32 ? ncols : 32;
+    // (narrow tiles fed by TMA have four epilogue warps of tile_n columns each, all others eight of tile_n / 2)
+    const int ncols = duo_mode(p, a_by_tma) ? p.tile_n : p.tile_n / 2, cw = ncols < 32 ? ncols : 32;
     bool can = (p.N % 4 == 0) && p.M < (1ll << 31) && !TC_DBG(p, 64) && (((uintptr_t)p.scale | (uintptr_t)p.shift) & 15) == 0;
     if (can) can = encode_rows_map(st, &map_y, y, p.M, p.N, p.N, cw) == 0;
     if (can && p.residual)
@@ -1610,6 +1739,30 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
   ctx->n_launch++;
   s = wdc_check_cuda(ctx, le, "tc_igemm_kernel");
   if (s == WDC_OK) s = wdc_check_cuda(ctx, cudaGetLastError(), "tc_igemm_kernel");
+#ifdef WDC_TC_DEVELOP
+  if (p.prof) {
+    static long long host[256 * 16];
+    cudaStreamSynchronize(ctx->stream);
+    cudaMemcpy(host, p.prof, sizeof(host), cudaMemcpyDeviceToHost);
+    double acc[16] = {};
+    for (int b = 0; b < grid; b++)
+      for (int i = 0; i < 16; i++) acc[i] += (double)host[b * 16 + i] / grid;
+    const double steps = (double)units * p.kbs / grid;   // K blocks per CTA (about)
+    if (getenv("WDC_TC_TIMELINE")) {
+      const long long* ev = host + 2368;
+      const long long t0 = ev[0 * 64 + 8];
+      fprintf(stderr, "timeline CTA 0 (cycles from K block 8): g | split a_full, empty, arrived | mma seg_empty, full, issued\n");
+      for (int g = 8; g < 40; g++)
+        fprintf(stderr, "  %2d | %6lld %6lld %6lld | %6lld %6lld %6lld\n", g, ev[g] - t0, ev[64 + g] - t0, ev[128 + g] - t0,
+                ev[5 * 64 + g] ? ev[5 * 64 + g] - t0 : -1, ev[3 * 64 + g] - t0, ev[4 * 64 + g] - t0);
+    }
+    fprintf(stderr, "prof M=%lld N=%d kb=%d tile_n=%d c4=%d | per K block, cycles: split[a_full %.0f empty %.0f ld+st %.0f wait_st %.0f "
+            "loop %.0f total %.0f] mma[seg_empty %.0f full %.0f issue %.0f total %.0f]\n", (long long)p.M, p.N, p.kblocks, p.tile_n,
+            p.c4, acc[0] / steps, acc[1] / steps, acc[2] / steps, acc[3] / steps, acc[4] / steps, acc[5] / steps, acc[6] / steps,
+            acc[7] / steps, acc[8] / steps, acc[9] / steps);
+    fprintf(stderr, "   blocking waits per K block: a_full %.2f empty %.2f full %.2f\n", acc[10] / steps, acc[11] / steps, acc[12] / steps);
+  }
+#endif
   if (p.splits > 1) {
     if (s == WDC_OK) {
       cudaLaunchConfig_t rc = {};
@@ -1699,12 +1852,14 @@ int wdc_tc_conv2d(wdc_context* ctx, const wdc_conv_desc* d, const float* x, cons
   // stride-2 stems: pad the rows physically so that two taps are one 32-byte pixel pair
   const bool pairs = d->stride_w == 2 && d->dil_w == 1 && tc_state(ctx)->encode_im2col != nullptr;
   const int wp = pairs ? (int)(2 * d->out_w + 6) : (int)d->in_w;
-  const int64_t pixels = d->batch * d->in_h * wp;
+  const int hp = (int)d->in_h;
+  const int64_t pixels = d->batch * hp * wp;
   int s = wdc_alloc(ctx, pixels * 16, (void**)&x4);
   if (s != WDC_OK) return s;
   if (pairs)
     pad_channels4_rows_kernel<<<grid_for(ctx, pixels, 256, 8), 256, 0, ctx->stream>>>(
-        x, x4, d->batch * d->in_h, (int)d->in_w, wp, (int)d->pad_l, (int)d->ch_in, d->x_nchw ? (int)d->in_h : 0);
+        x, x4, d->batch, (int)d->in_h, hp, 0, (int)d->in_w, wp, (int)d->pad_l, (int)d->ch_in,
+        d->x_nchw ? 1 : 0);
   else
     pad_channels4_kernel<<<grid_for(ctx, pixels, 256, 8), 256, 0, ctx->stream>>>(x, x4, pixels, (int)d->ch_in,
                                                                                  d->x_nchw ? d->in_h * d->in_w : 0);

@@ -15,7 +15,8 @@ launch with CUDA events in a second pass over the same steps, against a cuBLAS T
 process (burst and sustained); `cpu_baseline` = the CPU oracle (a port of the reference's cpu backend) on a bounded
 sample, on all host threads and on one; `weak` (N > 1) = the same with B images on every GPU; `one_process`
 (N > 1) = the split batch driven by one process through ReplicaGroup.run with outputs gathered by peer copies;
-`configs` / `layers` (N = 1) = the other benchmark configurations and the reference's own operator shapes.
+`configs` / `layers` (N = 1) = the other benchmark configurations and the reference's own operator shapes;
+`configs_sharded` = configurations 4 and 5 with their batch split over the N ranks (device time, max over ranks).
 No explicit L2 flush: every step streams far more than the 126 MB L2 (at 256 images the input alone is 154 MB; at
 the 32 images a GPU gets from a batch split eight ways, a step still walks about 300 MB of weights and their split
 copies and over 1 GB of activations), so nothing a step reads at its start is still cached from the step before.
@@ -412,6 +413,49 @@ def other_configs(ctx, tf32_peak: float) -> list:
     return rows
 
 
+SHARDED_CONFIGS = [
+    # name, global batch, model factory (per-GPU batch), input shapes (per-GPU batch)
+    ("C4 LSTM seq128 in256 hid512", 64, lambda b: __import__("webdnn_b200.zoo", fromlist=["zoo"]).lstm(batch=b),
+     lambda b: [(128, b, 256)]),
+    ("C5 DETR-style 800x800", 8, lambda b: __import__("webdnn_b200.zoo", fromlist=["zoo"]).detr(batch=b),
+     lambda b: [(b, 3, 800, 800)]),
+]
+
+
+def sharded_configs(ctx, stream, rank: int, world: int, barrier, max_over_ranks, reps: int = 10) -> list:
+    """Configurations 4 and 5 with their batch split evenly over the ranks (no exchange between them: every rank
+    runs its share as a replayed graph, inputs resident).  Timed on the device, barrier on both sides, max over
+    ranks; items/s counts the whole batch.  A batch the ranks cannot split evenly is left out."""
+    import torch
+
+    from webdnn_b200 import zoo
+    from webdnn_b200.backend import CPUTensor
+    from webdnn_b200.runner import load
+    rows = []
+    for name, gbatch, factory, shapes_of in SHARDED_CONFIGS:
+        if gbatch % world != 0:
+            continue
+        b = gbatch // world
+        runner = load(factory(b), backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": ctx}})
+        host = [CPUTensor.from_array(zoo.make_input(sh, "normal", seed=1 + rank)) for sh in shapes_of(b)]
+        cap = runner.capture(host)
+        for _ in range(3):
+            cap.launch()
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record(stream)
+        for _ in range(reps):
+            cap.launch()
+        ev1.record(stream)
+        barrier()
+        (ms,) = max_over_ranks(ev0.elapsed_time(ev1) / reps)
+        cap.dispose()
+        runner.dispose()
+        rows.append({"name": name, "global_batch": gbatch, "items_per_gpu": b, "ms_per_run": ms,
+                     "items_per_s": gbatch / ms * 1e3, "step": "replayed CUDA graph", "reps": reps})
+    return rows
+
+
 def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     import torch
 
@@ -535,6 +579,12 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         # rank 0 is timing
         dist.barrier(group=host_group)
 
+    # ---- configurations 4 and 5 with their batch split over the ranks (N = 1: the whole batch, the reference point)
+    sharded = None
+    if not args.no_extra:
+        barrier()
+        sharded = sharded_configs(ctx, stream, rank, world, barrier, max_over_ranks)
+
     if rank == 0:
         value = G * args.steps / (dev_ms * 1e-3)
         e2e_value = G * args.steps / (e2e_ms * 1e-3)
@@ -591,6 +641,8 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                         "tile's epilogue: about 10 us) and, at this share, 1-3 waves of tiles per launch, so the cost is not "
                         "amortised as it is at 256 images per GPU; a 218 KB / 512-TMEM-column CTA cannot share its SM with "
                         "the next launch's CTA, so programmatic dependent launch hides the launch latency only"}
+        if sharded is not None:
+            line["configs_sharded"] = sharded
         if weak is not None:
             line["weak"] = weak
         if one_proc is not None:

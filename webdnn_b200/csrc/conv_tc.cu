@@ -73,7 +73,8 @@ constexpr int EPI_WARP0 = 8;
 constexpr int NUM_EPI_WARPS = 8;
 constexpr int NUM_THREADS = 16 * 32;
 constexpr int RES_L2_KBLOCKS = 4;   // residual L2 prefetch for launches with at most this many K blocks
-constexpr int SEG_KBLOCKS = 4;        // K blocks accumulated in TMEM before the partial sum is drained
+constexpr int SEG_KBLOCKS = 4;        // K blocks accumulated in TMEM before the partial sum is drained; a unit's last
+                                      // segment also takes a remainder of 1-3 blocks (see segments_of)
 constexpr int NBUF = 2;               // TMEM segment accumulators of 128 columns
 constexpr int EPI_BUF_BYTES = 32 * 32 * 4;   // epilogue staging: 32 rows x 32 columns per buffer, 2 per warp
 constexpr int TMEM_A_COL0 = NBUF * 128;  // first column of the A stages
@@ -259,6 +260,13 @@ __host__ __device__ __forceinline__ bool duo_mode(const TcProblem& p, bool a_by_
   return a_by_tma && p.tile_n <= 64 && p.kblocks >= DUO_MIN_KBLOCKS && !TC_DBG(p, 8192);
 }
 
+// Segments of a work unit of kbn K blocks: floor(kbn / 4) of them (at least one), 4 K blocks each, the last one
+// with the remainder as well (up to 7): a short trailing segment would cost a whole accumulator drain for little
+// accuracy (the stem's 7 K blocks are one segment instead of 4 + 3).
+__host__ __device__ __forceinline__ int segments_of(int kbn) {
+  return kbn < 2 * SEG_KBLOCKS ? 1 : kbn / SEG_KBLOCKS;
+}
+
 // Work unit u of a launch: a full tile (sp = -1, all K blocks), or range sp of one of the remaining tiles
 // (K blocks kb0 .. kb0 + kbn - 1); `rest` is the tile's index among the remaining tiles.
 __device__ __forceinline__ void unit_of(const TcProblem& p, int u, int& tile, int& sp, int& kb0, int& kbn) {
@@ -321,16 +329,34 @@ __device__ __forceinline__ uint32_t make_idesc(int n) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_M >> 4) << 24);
 }
 
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void umma_tf32_ts(uint32_t tmem_c, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
-                                             uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
-      :
-      : "r"(tmem_c), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
+// D[tmem] (+)= A[tmem] * B[smem], the shared-memory descriptor given as its two 32-bit halves (only the low one, which holds the start
+// address, changes from MMA to MMA) and the accumulate flag as a compile-time constant where it is one: the issuing
+// thread is a single lane whose instruction count per K block is part of the kernel's serial path.
+template <bool kAccumulate>
+__device__ __forceinline__ void umma_tf32_ts2(uint32_t tmem_c, uint32_t tmem_a, uint32_t desc_lo, uint32_t desc_hi,
+                                              uint32_t idesc, uint32_t accumulate = 1) {
+  if (kAccumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 d;\n\t"
+        "mov.b64 d, {%2, %3};\n\t"
+        "setp.eq.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], d, %4, p;\n\t}"
+        :
+        : "r"(tmem_c), "r"(tmem_a), "r"(desc_lo), "r"(desc_hi), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 d;\n\t"
+        "mov.b64 d, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], d, %4, p;\n\t}"
+        :
+        : "r"(tmem_c), "r"(tmem_a), "r"(desc_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void umma_commit_addr(uint32_t bar_saddr) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_saddr) : "memory");
 }
 __device__ __forceinline__ void umma_commit(unsigned long long* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -538,7 +564,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     PROF_DECL(5);
     for (int64_t g = group; g < items; g += ngroups) {
       PROF_ADD(4);
-      if (t0) PROF_CNT(10, !a_tok);
+      if (t0) PROF_CNT(13, !a_tok);
       if (!a_tok && !mbar_wait(&ss->a_full_bar[as], aphase, ss, p.status, 11, p.nap_ns)) break;
       PROF_ADD(0);
       if (t0) PROF_EV(0, g);
@@ -563,7 +589,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         e_tok = mbar_test(&ss->empty_bar[stage], phase ^ 1);
         if (g + ngroups < items) a_tok_n = mbar_test(&ss->a_full_bar[as_n], aphase_n);
       }
-      if (t0) PROF_CNT(11, !e_tok);
+      if (t0) PROF_CNT(14, !e_tok);
       if (!e_tok && !mbar_wait(&ss->empty_bar[stage], phase ^ 1, ss, p.status, 12, p.nap_ns)) break;
       PROF_ADD(1);
       if (t0) PROF_EV(1, g);
@@ -830,19 +856,28 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
       int stage = 0;
       uint32_t phase = 0;
       const uint32_t idesc = make_idesc(p.tile_n);
+      // per-stage operand addresses from a few bases: descriptor low words (start address in 16-byte units) of the
+      // W_hi / W_lo slots, the high word all descriptors share, TMEM column of the stage's A, barrier addresses
+      const uint64_t desc0 = make_smem_desc(smem_u32(w_hi_ptr(0)));
+      const uint32_t desc_hi32 = (uint32_t)(desc0 >> 32);
+      const uint32_t dwh0 = (uint32_t)desc0, dwl0 = (uint32_t)make_smem_desc(smem_u32(w_lo_ptr(0)));
+      const uint32_t dslot = w_slot >> 4;
+      const uint32_t a_col0 = tmem_base + (uint32_t)TMEM_A_COL0;
+      const uint32_t empty0 = smem_u32(&ss->empty_bar[0]);
       int64_t seg = 0;  // segments issued by this CTA so far
       bool ok = true;
       bool f_tok = false;   // answer of the probe made one K block earlier
       bool s_tok = false;   // the same for the next segment's accumulator
-      PROF_DECL(3);
+      PROF_DECL(5);
       int gk = 0;
       for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         int tile, sp, kb0, kbn;
         unit_of(p, u, tile, sp, kb0, kbn);
         uint32_t d_tmem = 0;
         int buf = 0;
+        int in_seg = 0;
         for (int kb = 0; kb < kbn; kb++) {
-          const int in_seg = kb % SEG_KBLOCKS;
+          const bool seg_last = kb == kbn - 1 || (in_seg == SEG_KBLOCKS - 1 && kbn - (kb + 1) >= SEG_KBLOCKS);
           PROF_ADD(2);
           if (in_seg == 0) {
             buf = (int)(seg % NBUF);
@@ -853,7 +888,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             d_tmem = tmem_base + (uint32_t)(buf * 128);
           }
-          PROF_CNT(12, !f_tok);
+          PROF_CNT(15, !f_tok);
           if (!f_tok && !mbar_wait(&ss->full_bar[stage], phase, ss, p.status, 32, p.nap_ns)) { ok = false; break; }
           PROF_ADD(1);
           PROF_EV(3, gk);
@@ -862,37 +897,44 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
           const uint32_t phase_n = stage_n ? phase : phase ^ 1;
           f_tok = !TC_DBG(p, 4096) && mbar_test(&ss->full_bar[stage_n], phase_n);
           // ... and, on a segment's last K block, the accumulator the next segment will use
-          if ((in_seg == SEG_KBLOCKS - 1 || kb == kbn - 1) && !TC_DBG(p, 4096))
+          if (seg_last && !TC_DBG(p, 4096))
             s_tok = mbar_test(&ss->seg_empty_bar[(int)((seg + 1) % NBUF)], (uint32_t)(((seg + 1) / NBUF) & 1) ^ 1);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          const uint32_t a_hi = tmem_base + (uint32_t)(TMEM_A_COL0 + stage * 64);
+          const uint32_t a_hi = a_col0 + (uint32_t)(stage * 64);
           const uint32_t a_lo = a_hi + 32u;
-          const uint64_t dw_hi = make_smem_desc(smem_u32(w_hi_ptr(stage)));
-          const uint64_t dw_lo = make_smem_desc(smem_u32(w_lo_ptr(stage)));
+          const uint32_t dw_hi = dwh0 + (uint32_t)stage * dslot;
+          const uint32_t dw_lo = dwl0 + (uint32_t)stage * dslot;
 #pragma unroll
           for (int k = 0; k < BLOCK_K / 8; k++) {
-            const uint64_t adv = (uint64_t)(k * 2);  // 8 tf32 = 32 bytes = 2 x 16-byte units of W
+            const uint32_t adv = (uint32_t)(k * 2);  // 8 tf32 = 32 bytes = 2 x 16-byte units of W
             const uint32_t acol = (uint32_t)(k * 8); // 8 TMEM columns of A
             if (TC_DBG(p, 4)) continue;
             if (p.single_pass) {
-              umma_tf32_ts(d_tmem, a_hi + acol, dw_hi + adv, idesc, (in_seg | k) ? 1u : 0u);
+              if (k == 0) umma_tf32_ts2<false>(d_tmem, a_hi, dw_hi, desc_hi32, idesc, in_seg ? 1u : 0u);
+              else umma_tf32_ts2<true>(d_tmem, a_hi + acol, dw_hi + adv, desc_hi32, idesc);
               continue;
             }
-            umma_tf32_ts(d_tmem, a_lo + acol, dw_hi + adv, idesc, (in_seg | k) ? 1u : 0u);
-            umma_tf32_ts(d_tmem, a_hi + acol, dw_lo + adv, idesc, 1u);
-            umma_tf32_ts(d_tmem, a_hi + acol, dw_hi + adv, idesc, 1u);
+            if (k == 0) umma_tf32_ts2<false>(d_tmem, a_lo, dw_hi, desc_hi32, idesc, in_seg ? 1u : 0u);
+            else umma_tf32_ts2<true>(d_tmem, a_lo + acol, dw_hi + adv, desc_hi32, idesc);
+            umma_tf32_ts2<true>(d_tmem, a_hi + acol, dw_lo + adv, desc_hi32, idesc);
+            umma_tf32_ts2<true>(d_tmem, a_hi + acol, dw_hi + adv, desc_hi32, idesc);
           }
-          umma_commit(&ss->empty_bar[stage]);  // stage reusable once these MMAs have read it
+          PROF_ADD(3);
+          umma_commit_addr(empty0 + (uint32_t)stage * 8u);  // stage reusable once these MMAs have read it
+          PROF_ADD(4);
           PROF_EV(4, gk);
           gk++;
           stage = stage_n; phase = phase_n;
-          if (in_seg == SEG_KBLOCKS - 1 || kb == kbn - 1) {
+          if (seg_last) {
             umma_commit(&ss->seg_full_bar[buf]);  // partial sum of this segment is complete
             seg++;
+            in_seg = 0;
+          } else {
+            in_seg++;
           }
         }
       }
-      PROF_OUT(6, 3);
+      PROF_OUT(6, 5);
     }
   } else if (warp >= EPI_WARP0) {
     // ===================================================================== accumulate + epilogue warps
@@ -901,7 +943,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
     const int half = ew >> 2;                     // which half of the tile's columns (eight warps)
     const int ncols = duo ? p.tile_n : p.tile_n >> 1;   // 16, 32 or 64 columns per warp
     const int col0 = half * ncols;
-    int nseg = (p.kblocks + SEG_KBLOCKS - 1) / SEG_KBLOCKS;
+    int nseg = segments_of(p.kblocks);
     int64_t seg = 0;
     bool ok = true;
     if (use_shift_tab) {
@@ -943,7 +985,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
         unit_of(p, u, tile, sp, kb0, kbn);
         const bool direct = sp < 0;                     // full tile: fused epilogue; else raw partial sums
         const bool res_u = use_res && direct;
-        nseg = (kbn + SEG_KBLOCKS - 1) / SEG_KBLOCKS;
+        nseg = segments_of(kbn);
         // Short-K (memory-bound) launches: while this tile accumulates, L2 fetches the residual chunks of
         // the warp's next tile.  Each staging buffer holds one chunk, so without this every chunk waits
         // for a full trip to HBM.  Long-K launches hide that trip behind the MMAs and skip the extra requests.
@@ -1757,10 +1799,10 @@ int launch_tc(wdc_context* ctx, TcProblem& p, const float* x, const float* w, fl
                 ev[5 * 64 + g] ? ev[5 * 64 + g] - t0 : -1, ev[3 * 64 + g] - t0, ev[4 * 64 + g] - t0);
     }
     fprintf(stderr, "prof M=%lld N=%d kb=%d tile_n=%d c4=%d | per K block, cycles: split[a_full %.0f empty %.0f ld+st %.0f wait_st %.0f "
-            "loop %.0f total %.0f] mma[seg_empty %.0f full %.0f issue %.0f total %.0f]\n", (long long)p.M, p.N, p.kblocks, p.tile_n,
+            "loop %.0f total %.0f] mma[seg_empty %.0f full %.0f loop %.0f mmas %.0f commit %.0f total %.0f]\n", (long long)p.M, p.N, p.kblocks, p.tile_n,
             p.c4, acc[0] / steps, acc[1] / steps, acc[2] / steps, acc[3] / steps, acc[4] / steps, acc[5] / steps, acc[6] / steps,
-            acc[7] / steps, acc[8] / steps, acc[9] / steps);
-    fprintf(stderr, "   blocking waits per K block: a_full %.2f empty %.2f full %.2f\n", acc[10] / steps, acc[11] / steps, acc[12] / steps);
+            acc[7] / steps, acc[8] / steps, acc[9] / steps, acc[10] / steps, acc[11] / steps);
+    fprintf(stderr, "   blocking waits per K block: a_full %.2f empty %.2f full %.2f\n", acc[13] / steps, acc[14] / steps, acc[15] / steps);
   }
 #endif
   if (p.splits > 1) {

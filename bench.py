@@ -383,9 +383,26 @@ def one_process_replicas(world: int, batch: int, steps: int, warmup: int) -> dic
                 ref = out
             else:
                 res["peer_equals_host_gather"] = bool(np.array_equal(ref, out))
+        # the same call pipelined: step i + 1 is started (slice, transfer, run, result transfer all queued) before
+        # the result of step i is taken, so the input transfer of one step overlaps the GPUs' work on the other
+        pend = group.run_async([x])
+        for _ in range(max(warmup, 3)):
+            nxt = group.run_async([x])
+            (out,) = pend.result()
+            pend = nxt
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            nxt = group.run_async([x])
+            (out,) = pend.result()
+            pend = nxt
+        dt = time.perf_counter() - t0
+        (out,) = pend.result()
+        res["pipelined"] = {"images_per_s": batch * steps / dt, "ms_per_step": 1e3 * dt / steps,
+                            "equals_synchronous": bool(np.array_equal(ref, out))}
         res["output_shape"] = list(ref.shape)
         res["load_s"] = t_load
-        res["api"] = "ReplicaGroup.run(inputs, gather='peer'|'host'): one process, one host thread per GPU"
+        res["api"] = ("ReplicaGroup.run(inputs, gather='peer'|'host') and ReplicaGroup.run_async(inputs).result(): one "
+                      "process, one host thread per GPU")
         return res
     finally:
         group.close()

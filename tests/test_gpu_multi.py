@@ -61,3 +61,31 @@ def test_two_outputs_over_two_gpus():
                 assert max_err_rel_linf(g, w) <= 1e-4, gather
     finally:
         group.close()
+
+
+@pytest.mark.parametrize("devices", [[0], [0, 1]])
+def test_pipelined_group_runs_equal_synchronous_runs(devices):
+    """ReplicaGroup.run_async: two steps in flight (the second started before the first result is taken), node by
+    node at first and as replayed graphs from the third step of the shape on; every result equals the synchronous
+    call's bit for bit.  The one-device group runs on any box."""
+    if _device_count() < len(devices):
+        pytest.skip("needs two GPUs")
+    from webdnn_b200.replicas import ReplicaGroup
+    model = zoo.conv_bn_relu(8, 32, 14)
+    xs = [zoo.make_input((8, 32, 14, 14), seed=s) for s in range(21, 27)]
+    group = ReplicaGroup(model, devices=devices)
+    try:
+        want = [group.run([x])[0] for x in xs]
+        pend = group.run_async([xs[0]])
+        got = []
+        for x in xs[1:]:
+            nxt = group.run_async([x])
+            got.append(pend.result(deadline_s=60)[0])
+            pend = nxt
+        got.append(pend.result()[0])
+        for g, w in zip(got, want):
+            assert np.array_equal(g, w)
+        (oracle0,) = ref_runner.run_model(model, [xs[0]])
+        assert max_err_rel_linf(got[0], oracle0) <= 1e-4
+    finally:
+        group.close()

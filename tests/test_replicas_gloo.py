@@ -119,6 +119,44 @@ def test_replica_group_slices_and_gathers_like_one_run():
         ReplicaGroup(replicas=[])
 
 
+class _QueueingReplica(_OracleReplica):
+    """Like CudaReplica's queue: start_async may be called again before the first step is finished."""
+
+    def __init__(self, model):
+        super().__init__(model)
+        self.queue = []
+
+    def start_async(self, shard):
+        self.queue.append([np.asarray(a) for a in shard])
+
+    def finish(self):
+        if self.queue:
+            self.shard = self.queue.pop(0)
+        return super().finish()
+
+
+def test_replica_group_pipelined_steps_come_back_in_order():
+    from oracle import ref_runner
+    from webdnn_b200 import zoo
+    from webdnn_b200.replicas import ReplicaGroup
+    model = zoo.mlp(6)
+    xs = [zoo.make_input((6, 784), "uniform", seed=s) for s in (1, 2, 3)]
+    want = [ref_runner.run_model(model, [x])[0] for x in xs]
+    group = ReplicaGroup(replicas=[_QueueingReplica(model) for _ in range(2)])
+    first = group.run_async([xs[0]])
+    second = group.run_async([xs[1]])
+    with pytest.raises(RuntimeError, match="order"):
+        second.result()                      # the older step's result has not been taken yet
+    with pytest.raises(RuntimeError, match="in flight"):
+        group.run([xs[2]])                   # the synchronous call does not jump the queue
+    assert np.array_equal(first.result(deadline_s=60)[0], want[0])
+    third = group.run_async([xs[2]])
+    assert np.array_equal(second.result()[0], want[1])
+    assert np.array_equal(third.result()[0], want[2])
+    assert np.array_equal(group.run([xs[0]])[0], want[0])     # nothing in flight any more
+    group.close()
+
+
 def test_replica_group_names_the_replica_that_failed_or_stalled():
     from webdnn_b200 import zoo
     from webdnn_b200.lib import CudaBackendError

@@ -104,7 +104,11 @@ class CudaReplica:
     the GPU: the shard is copied into pinned staging memory, moved on the context's copy stream
     (wdc_upload_async) and run (as a replayed CUDA graph from the third step of a given shape on, when
     ``graph_replay``); ``finish()`` waits and returns host arrays; ``finish_on_device()`` returns the device
-    tensors for a peer gather."""
+    tensors for a peer gather.  Steps are queued: ``start_async(shard)`` also enqueues the device-to-host transfer of
+    the outputs (on the download stream, into page-locked staging), so that a second step may be started before the
+    first is finished; ``finish()`` always answers the oldest step."""
+
+    MAX_IN_FLIGHT = 2          # steps started and not yet finished (staging buffers are double-buffered)
 
     def __init__(self, source, device: int, graph_replay: bool = True):
         from .backend import WebDNNCudaContext
@@ -114,10 +118,10 @@ class CudaReplica:
         self.context.initialize()
         self.runner = load(source, backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": self.context}})
         self.graph_replay = graph_replay
-        self._pinned = {}       # (input index, shape, dtype) -> pinned staging array
+        self._pinned = {}       # (input index, shape, dtype) -> [pinned staging arrays, next index]
         self._captured = {}     # shape signature -> CapturedRun
         self._seen = {}
-        self._pending = None
+        self._queue = []        # steps in flight, oldest first
 
     def _stage(self, j: int, a: np.ndarray):
         from .backend import CPUTensor
@@ -125,14 +129,23 @@ class CudaReplica:
             # the caller's array is page-locked already (WebDNNCudaContext.pinned_array): transfer straight from it
             return CPUTensor(list(a.shape), "int32" if a.dtype == np.int32 else "float32", a)
         key = (j, a.shape, a.dtype.str)
-        buf = self._pinned.get(key)
-        if buf is None:
-            buf = self._pinned[key] = self.context.pinned_array(a.shape, a.dtype)
+        ring = self._pinned.setdefault(key, [[], 0])
+        if len(ring[0]) < self.MAX_IN_FLIGHT + 1:      # one more than the steps in flight: never the one in transfer
+            ring[0].append(self.context.pinned_array(a.shape, a.dtype))
+            buf = ring[0][-1]
+        else:
+            ring[1] = (ring[1] + 1) % len(ring[0])
+            buf = ring[0][ring[1]]
         buf[...] = a
         return CPUTensor(list(a.shape), "int32" if a.dtype == np.int32 else "float32", buf)
 
-    def start(self, shard: Sequence[np.ndarray]) -> None:
+    def start_async(self, shard: Sequence[np.ndarray]) -> None:
+        self.start(shard, download=True)
+
+    def start(self, shard: Sequence[np.ndarray], download: bool = False) -> None:
         ctx = self.context
+        if len(self._queue) >= self.MAX_IN_FLIGHT:
+            raise RuntimeError(f"replica on device {self.device}: {len(self._queue)} steps in flight already")
         host = [self._stage(j, a if isinstance(a, np.ndarray) else np.asarray(a)) for j, a in enumerate(shard)]
         dev_in = [ctx.prefetch_tensor(t) for t in host]
         sig = tuple((tuple(t.dims), t.data_type) for t in host)
@@ -148,15 +161,19 @@ class CudaReplica:
                 ctx.wait_upload(src)
                 ctx._call("wdc_copy", _vp(dst.ptr), _vp(src.ptr), dst.length * 4)
             cap.launch()
-            self._pending = (dev_in, list(cap.outputs), False)
+            outs, owned = list(cap.outputs), False
         else:
-            outs = self.runner.run(dev_in, outputs_on_device=True)
-            self._pending = (dev_in, outs, True)
+            outs, owned = self.runner.run(dev_in, outputs_on_device=True), True
+        # (a captured run's output buffers are written again by the next replay: their transfer is queued now, in
+        # stream order, when the caller wants to start another step before finishing this one)
+        downloads = [ctx.download_async(o) for o in outs] if download else None
+        self._queue.append((dev_in, outs, owned, downloads))
 
     def finish_on_device(self):
         """(device tensors in canonical layout, release callback)."""
-        dev_in, outs, owned = self._pending
-        self._pending = None
+        dev_in, outs, owned, downloads = self._queue.pop(0)
+        if downloads is not None:
+            raise RuntimeError("this step was started with start_async: finish() has its outputs")
         canon = [self.context.canonical(o) for o in outs]
 
         def release():
@@ -170,6 +187,16 @@ class CudaReplica:
         return canon, release
 
     def finish(self) -> List[np.ndarray]:
+        if self._queue and self._queue[0][3] is not None:
+            dev_in, outs, owned, downloads = self._queue.pop(0)
+            try:
+                return [d.result().reshape(o.dims) for d, o in zip(downloads, outs)]
+            finally:
+                if owned:
+                    for o in outs:
+                        o.dispose()
+                for t in dev_in:
+                    t.dispose()
         canon, release = self.finish_on_device()
         try:
             return [c.get_data().reshape(c.dims) for c in canon]
@@ -243,13 +270,13 @@ class ReplicaGroup:
         thread is abandoned, the group should then be closed)."""
         if gather not in ("host", "peer"):
             raise ValueError("gather must be 'host' or 'peer'")
+        if getattr(self, "_started", 0) != getattr(self, "_finished", 0):
+            raise RuntimeError("steps started by run_async are still in flight: take their results first")
         n = len(self.replicas)
         shards = [shard_for_rank(inputs, i, n, self.batch_axis) for i in range(n)]
         self._on_threads(lambda i, r: r.start(shards[i]), deadline_s)      # enqueue everything first
         if gather == "host":
-            per_replica = self._on_threads(lambda i, r: r.finish(), deadline_s)
-            axes = self.output_axes or [self.batch_axis] * len(per_replica[0])
-            return [np.concatenate([rep[j] for rep in per_replica], axis=axes[j]) for j in range(len(per_replica[0]))]
+            return self._finish_host(deadline_s)
         pending = [r.finish_on_device() for r in self.replicas]
         n_out = len(pending[0][0])
         axes = self.output_axes or [self.batch_axis] * n_out
@@ -273,6 +300,38 @@ class ReplicaGroup:
             release()
         return results
 
+    def run_async(self, inputs: Sequence[np.ndarray], deadline_s: Optional[float] = None) -> "PendingGroupRun":
+        """Starts a step on every replica (slice, transfer, run, and the transfer of the outputs back, all queued)
+        and returns without waiting for the GPUs; ``PendingGroupRun.result()`` waits and concatenates through the
+        host.  Up to two steps may be in flight; their results are taken in the order they were started.  With page-
+        locked inputs (``WebDNNCudaContext.pinned_array``) the transfer of step i + 1 overlaps the GPUs' work on
+        step i."""
+        n = len(self.replicas)
+        shards = [shard_for_rank(inputs, i, n, self.batch_axis) for i in range(n)]
+        self._on_threads(lambda i, r: getattr(r, "start_async", r.start)(shards[i]), deadline_s)
+        self._started = getattr(self, "_started", 0) + 1
+        return PendingGroupRun(self, self._started)
+
+    def _finish_host(self, deadline_s: Optional[float]) -> List[np.ndarray]:
+        per_replica = self._on_threads(lambda i, r: r.finish(), deadline_s)
+        axes = self.output_axes or [self.batch_axis] * len(per_replica[0])
+        return [np.concatenate([rep[j] for rep in per_replica], axis=axes[j]) for j in range(len(per_replica[0]))]
+
     def close(self) -> None:
         for r in self.replicas:
             r.close()
+
+
+class PendingGroupRun:
+    """A step started by ``ReplicaGroup.run_async``."""
+
+    def __init__(self, group: ReplicaGroup, seq: int):
+        self.group, self.seq = group, seq
+
+    def result(self, deadline_s: Optional[float] = None) -> List[np.ndarray]:
+        g = self.group
+        if self.seq != getattr(g, "_finished", 0) + 1:
+            raise RuntimeError("results of pipelined steps are taken in the order the steps were started")
+        out = g._finish_host(deadline_s)
+        g._finished = self.seq
+        return out

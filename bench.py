@@ -453,21 +453,33 @@ def sharded_configs(ctx, stream, rank: int, world: int, barrier, max_over_ranks,
         if gbatch % world != 0:
             continue
         b = gbatch // world
-        runner = load(factory(b), backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": ctx}})
-        host = [CPUTensor.from_array(zoo.make_input(sh, "normal", seed=1 + rank)) for sh in shapes_of(b)]
-        cap = runner.capture(host)
-        for _ in range(3):
-            cap.launch()
+        # a rank that fails here still meets the others at the barriers; its time is reported as an error
+        err, cap, runner = None, None, None
+        try:
+            runner = load(factory(b), backend_order=["cuda", "cpu"], backend_options={"cuda": {"context": ctx}})
+            host = [CPUTensor.from_array(zoo.make_input(sh, "normal", seed=1 + rank)) for sh in shapes_of(b)]
+            cap = runner.capture(host)
+            for _ in range(3):
+                cap.launch()
+        except Exception as e:
+            err = f"{type(e).__name__}: {e}"
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record(stream)
-        for _ in range(reps):
-            cap.launch()
+        if err is None:
+            for _ in range(reps):
+                cap.launch()
         ev1.record(stream)
         barrier()
-        (ms,) = max_over_ranks(ev0.elapsed_time(ev1) / reps)
-        cap.dispose()
-        runner.dispose()
+        ms, failed = max_over_ranks(ev0.elapsed_time(ev1) / reps, 0.0 if err is None else 1.0)
+        if cap is not None:
+            cap.dispose()
+        if runner is not None:
+            runner.dispose()
+        if failed:
+            rows.append({"name": name, "global_batch": gbatch, "items_per_gpu": b,
+                         "error": err or "another rank failed"})
+            continue
         rows.append({"name": name, "global_batch": gbatch, "items_per_gpu": b, "ms_per_run": ms,
                      "items_per_s": gbatch / ms * 1e3, "step": "replayed CUDA graph", "reps": reps})
     return rows

@@ -243,6 +243,55 @@ __global__ void __launch_bounds__(256) gap_group_kernel(const float* __restrict_
   }
 }
 
+// Dense NCHW maps of at most 96 pixels: the maps of consecutive (image, channel) pairs are one contiguous stretch of
+// memory, so a CTA brings 128 of them into shared memory with full-width coalesced 16-byte loads (a 49-pixel map is
+// 196 bytes: read map by map, no access is aligned) and 128 threads then add up one map each (a row stride of `area`
+// words: conflict-free for odd areas, 2-way at worst for the even ones that matter).  Sums in double, like the others.
+constexpr int GAP_MAPS = 128;
+constexpr int GAP_MAX_AREA = 96;
+__global__ void __launch_bounds__(GAP_MAPS) gap_dense_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                                             int64_t rows, int area) {
+  extern __shared__ __align__(16) float buf[];             // GAP_MAPS * area words: several CTAs per SM
+  const double inv_area = 1.0 / (double)area;
+  const int64_t chunks = (rows + GAP_MAPS - 1) / GAP_MAPS;
+  for (int64_t c = blockIdx.x; c < chunks; c += gridDim.x) {
+    const int64_t row0 = c * GAP_MAPS;
+    const int maps = (int)(rows - row0 < GAP_MAPS ? rows - row0 : GAP_MAPS);
+    const int words = maps * area;
+    const float* src = x + row0 * area;                    // 16-byte aligned: GAP_MAPS * area * 4 is a multiple of 16
+    const int vec = words >> 2;
+    // eight loads per thread in flight before the first store (a load-store loop would pay the memory latency
+    // once per iteration)
+    for (int base = 0; base < vec; base += GAP_MAPS * 8) {
+      float4 r[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int i = base + u * GAP_MAPS + (int)threadIdx.x;
+        r[u] = i < vec ? __ldg(reinterpret_cast<const float4*>(src) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        const int i = base + u * GAP_MAPS + (int)threadIdx.x;
+        if (i < vec) reinterpret_cast<float4*>(buf)[i] = r[u];
+      }
+    }
+    for (int i = (vec << 2) + threadIdx.x; i < words; i += blockDim.x) buf[i] = __ldg(src + i);
+    __syncthreads();
+    if ((int)threadIdx.x < maps) {
+      const float* m = buf + threadIdx.x * area;
+      double s0 = 0, s1 = 0;
+      int i = 0;
+      for (; i + 1 < area; i += 2) {
+        s0 += (double)m[i];
+        s1 += (double)m[i + 1];
+      }
+      if (i < area) s0 += (double)m[i];
+      y[row0 + threadIdx.x] = (float)((s0 + s1) * inv_area);
+    }
+    __syncthreads();
+  }
+}
+
 extern "C" int wdc_global_avgpool(wdc_context* ctx, const float* x, float* y, int64_t batch, int64_t ch,
                                   int64_t area, int64_t xs_n, int64_t xs_c, int64_t xs_p) {
   if (!ctx) return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_global_avgpool: null context");
@@ -254,6 +303,14 @@ extern "C" int wdc_global_avgpool(wdc_context* ctx, const float* x, float* y, in
   if (xs_c == 1) {
     gap_cl_kernel<<<grid_for(ctx, batch * ch, 256, 8), 256, 0, ctx->stream>>>(x, y, batch, ch, area, xs_n, xs_p);
     return wdc_check_launch(ctx, "gap_cl_kernel");
+  }
+  if (area <= GAP_MAX_AREA && xs_p == 1 && xs_c == area && xs_n == ch * area && (((uintptr_t)x) & 15) == 0) {
+    const int64_t rows = batch * ch;
+    const int64_t chunks = (rows + GAP_MAPS - 1) / GAP_MAPS;
+    const size_t smem = (size_t)GAP_MAPS * area * 4;       // 25 KB for 7x7 maps: eight CTAs per SM
+    const int64_t cap = (int64_t)ctx->sm_count * 8;
+    gap_dense_kernel<<<(int)(chunks < cap ? chunks : cap), GAP_MAPS, smem, ctx->stream>>>(x, y, rows, (int)area);
+    return wdc_check_launch(ctx, "gap_dense_kernel");
   }
   if (area <= 128 && batch * ch < (1ll << 31) && ch < (1ll << 31)) {
     const int64_t rows = batch * ch;

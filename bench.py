@@ -362,7 +362,9 @@ def one_process_replicas(world: int, batch: int, steps: int, warmup: int) -> dic
     from webdnn_b200.replicas import ReplicaGroup
     model = zoo.resnet50(batch // world)
     t_load = time.perf_counter()
-    group = ReplicaGroup(model, devices=list(range(world)), graph_replay=batch // world <= GRAPH_MAX_BATCH)
+    # every replica replays a recorded graph whatever its share: one interpreter drives all GPUs here, and node by
+    # node its per-node work for N replicas would be longer than the GPUs' step
+    group = ReplicaGroup(model, devices=list(range(world)), graph_replay=True)
     t_load = time.perf_counter() - t_load
     # the batch sits in page-locked host memory, as in the other end-to-end figure: each replica transfers its
     # slice straight from it (a pageable array would first be copied into the replica's staging buffer)

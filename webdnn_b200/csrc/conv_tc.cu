@@ -63,6 +63,7 @@ constexpr int BLOCK_K = 32;           // fp32 elements per K block = one 128-byt
 constexpr int STAGES = 3;             // W tiles in shared memory and A (hi, lo) column groups in TMEM
 constexpr int A_STAGES = 3;           // raw A tiles in shared memory (kTmaA)
 constexpr int A_STAGES_MAX = 6;       // tiles of at most 64 columns leave half of the W region free: 3 more A stages
+constexpr int PROBE_AFTER_K = 1;      // the MMA issuer probes its next barriers after this k step of a K block (0..3)
 constexpr int DUO_MIN_KBLOCKS = 4;    // shortest reduction that runs with two splitter groups (see duo_mode)
 constexpr int NUM_A_WARPS = 4;
 constexpr int TMA_WARP = 4;
@@ -890,15 +891,11 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
           }
           PROF_CNT(15, !f_tok);
           if (!f_tok && !mbar_wait(&ss->full_bar[stage], phase, ss, p.status, 32, p.nap_ns)) { ok = false; break; }
+          f_tok = false;
           PROF_ADD(1);
           PROF_EV(3, gk);
-          // probe the next stage's barrier before issuing this stage's MMAs (see the operand splitters)
           const int stage_n = stage + 1 == STAGES ? 0 : stage + 1;
           const uint32_t phase_n = stage_n ? phase : phase ^ 1;
-          f_tok = !TC_DBG(p, 4096) && mbar_test(&ss->full_bar[stage_n], phase_n);
-          // ... and, on a segment's last K block, the accumulator the next segment will use
-          if (seg_last && !TC_DBG(p, 4096))
-            s_tok = mbar_test(&ss->seg_empty_bar[(int)((seg + 1) % NBUF)], (uint32_t)(((seg + 1) / NBUF) & 1) ^ 1);
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t a_hi = a_col0 + (uint32_t)(stage * 64);
           const uint32_t a_lo = a_hi + 32u;
@@ -918,9 +915,18 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
             else umma_tf32_ts2<true>(d_tmem, a_lo + acol, dw_hi + adv, desc_hi32, idesc);
             umma_tf32_ts2<true>(d_tmem, a_hi + acol, dw_lo + adv, desc_hi32, idesc);
             umma_tf32_ts2<true>(d_tmem, a_hi + acol, dw_hi + adv, desc_hi32, idesc);
+            if (k == PROBE_AFTER_K && !TC_DBG(p, 4096)) {
+              // Probe the next stage's barrier (see the operand splitters) with MMAs of this stage already queued:
+              // the answer takes about 150 cycles, during which this lane issues nothing and the tensor pipe works on
+              // what is queued.  On a segment's last K block also the accumulator the next segment will use.
+              f_tok = mbar_test(&ss->full_bar[stage_n], phase_n);
+              if (seg_last)
+                s_tok = mbar_test(&ss->seg_empty_bar[(int)((seg + 1) % NBUF)], (uint32_t)(((seg + 1) / NBUF) & 1) ^ 1);
+            }
           }
           PROF_ADD(3);
           umma_commit_addr(empty0 + (uint32_t)stage * 8u);  // stage reusable once these MMAs have read it
+
           PROF_ADD(4);
           PROF_EV(4, gk);
           gk++;
@@ -1051,6 +1057,7 @@ tc_igemm_kernel(const __grid_constant__ TcProblem p, const float* __restrict__ x
           if (lane == 0) mbar_arrive(&ss->seg_empty_bar[buf]);
         }
         if (!ok) break;
+
 #pragma unroll
         for (int c = 0; c < 2; c++) {
           if (c < nch && ok) {

@@ -669,7 +669,7 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
                 "contraction_launches_per_step": n_contr,
                 "us_per_contraction_launch": 1e3 * step_ms / max(n_contr, 1),
                 "note": "per contraction launch a persistent 148-CTA grid has a fixed cost (launch, pipeline fill, the last "
-                        "tile's epilogue: about 10 us) and, at this share, 1-3 waves of tiles per launch, so the cost is not "
+                        "tile's epilogue: about 5 us) and, at this share, 1-3 waves of tiles per launch, so the cost is not "
                         "amortised as it is at 256 images per GPU; a 218 KB / 512-TMEM-column CTA cannot share its SM with "
                         "the next launch's CTA, so programmatic dependent launch hides the launch latency only"}
         if sharded is not None:

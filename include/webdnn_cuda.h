@@ -71,6 +71,11 @@ int wdc_graph_launch(wdc_context* ctx, wdc_graph* graph);
 int wdc_graph_destroy(wdc_context* ctx, wdc_graph* graph);
 int wdc_upload_async(wdc_context* ctx, void* dst, const void* host, int64_t bytes, int64_t* ticket);
 int wdc_wait_upload(wdc_context* ctx, int64_t ticket);
+/* wdc_upload_async for a destination that no queued work has touched since wdc_alloc returned it (a tensor created
+ * for this transfer, the usual case of moveTensor, runnerImpl.ts:420-447): only a previous tenant of the memory can
+ * still be in use, so the transfer waits for the compute stream's position at the arena's most recent wdc_free
+ * instead of for everything queued so far, and can overlap a run that was queued before the call. */
+int wdc_upload_fresh_async(wdc_context* ctx, void* dst, const void* host, int64_t bytes, int64_t* ticket);
 /* Device-to-host transfer on a third stream, for callers that queue the next run before they read the result of
  * this one (the reference's getData, webgpuTensorImpl.ts:31-53, maps a staging buffer and awaits it; its runner
  * has one run in flight).  The transfer starts after the work queued so far on the compute stream and does not

@@ -400,7 +400,8 @@ class WebDNNCudaContext:
         dst = CudaTensor(self, tensor.dims, tensor.data_type)
         arr = np.ascontiguousarray(np.asarray(tensor.data).reshape(-1), dtype=NP_DTYPE[tensor.data_type])
         ticket = ctypes.c_int64()
-        self._call("wdc_upload_async", c_void_p(dst.ptr), arr.ctypes.data_as(c_void_p), arr.nbytes, byref(ticket))
+        # (dst was allocated two lines up: nothing queued touches it, so the transfer need not wait for queued runs)
+        self._call("wdc_upload_fresh_async", c_void_p(dst.ptr), arr.ctypes.data_as(c_void_p), arr.nbytes, byref(ticket))
         dst.upload_ticket = ticket.value
         dst._prefetch_source = arr  # keeps the host memory alive until the tensor goes away
         return dst

@@ -56,6 +56,7 @@ struct wdc_context {
   // second stream for host-to-device transfers that overlap the kernels of `stream`
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t copy_fence = nullptr;             // recorded on `stream`, waited by `copy_stream`
+  cudaEvent_t free_fence = nullptr;             // recorded on `stream` at every wdc_free of the main arena (once `copy_stream` exists)
   static const int kUploadTickets = 16;
   cudaEvent_t upload_done[kUploadTickets] = {};  // recorded on `copy_stream` after each transfer
   int64_t upload_seq = 0;

@@ -124,6 +124,7 @@ extern "C" int wdc_destroy(wdc_context* ctx) {
     cudaStreamSynchronize(ctx->copy_stream);
     cudaStreamDestroy(ctx->copy_stream);
     cudaEventDestroy(ctx->copy_fence);
+    cudaEventDestroy(ctx->free_fence);
     for (auto& ev : ctx->upload_done)
       if (ev) cudaEventDestroy(ev);
   }
@@ -267,6 +268,12 @@ extern "C" int wdc_free(wdc_context* ctx, void* dptr) {
   }
   it->second = {size, true};
   a.free_by_size.insert({size, {slab, off}});
+  // A block of the main arena may be handed to a transfer on the copy stream next (wdc_upload_fresh_async): the
+  // position of this free in the compute stream's order is what that transfer has to wait for.
+  if (owner == &ctx->arena && ctx->copy_stream && !ctx->capture_arena) {
+    DeviceGuard g(ctx->device);
+    cudaEventRecord(ctx->free_fence, ctx->stream);
+  }
   return WDC_OK;
 }
 
@@ -296,20 +303,29 @@ extern "C" int wdc_upload(wdc_context* ctx, void* dst, const void* host, int64_t
   return WDC_OK;
 }
 
-extern "C" int wdc_upload_async(wdc_context* ctx, void* dst, const void* host, int64_t bytes, int64_t* ticket) {
+static int upload_async(wdc_context* ctx, void* dst, const void* host, int64_t bytes, int64_t* ticket, bool fresh) {
   if (!ctx || !ticket || bytes < 0 || (bytes > 0 && (!dst || !host)))
     return wdc_fail(ctx, WDC_ERR_INVALID, "wdc_upload_async: bad argument");
   DeviceGuard g(ctx->device);
   if (!ctx->copy_stream) {
     WDC_CUDA(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
     WDC_CUDA(ctx, cudaEventCreateWithFlags(&ctx->copy_fence, cudaEventDisableTiming));
+    WDC_CUDA(ctx, cudaEventCreateWithFlags(&ctx->free_fence, cudaEventDisableTiming));
     for (auto& ev : ctx->upload_done) WDC_CUDA(ctx, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    // every free before this moment had no fence of its own: this one stands for them all
+    WDC_CUDA(ctx, cudaEventRecord(ctx->free_fence, ctx->stream));
   }
   wdc_tc_evict(ctx, dst, bytes);
-  // dst comes from the arena, whose reuse is ordered on `stream`: the transfer may start only after
-  // everything already queued there (a previous tenant of this memory may still be read)
-  WDC_CUDA(ctx, cudaEventRecord(ctx->copy_fence, ctx->stream));
-  WDC_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->copy_fence, 0));
+  if (fresh) {
+    // dst is untouched since wdc_alloc returned it: only a previous tenant of the memory can still be in use, and
+    // it was freed no later than the arena's most recent free
+    WDC_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->free_fence, 0));
+  } else {
+    // the transfer may start only after everything already queued on `stream` (work that reads or writes dst, or a
+    // previous tenant of its memory)
+    WDC_CUDA(ctx, cudaEventRecord(ctx->copy_fence, ctx->stream));
+    WDC_CUDA(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->copy_fence, 0));
+  }
   if (bytes > 0)
     WDC_CUDA(ctx, cudaMemcpyAsync(dst, host, (size_t)bytes, cudaMemcpyHostToDevice, ctx->copy_stream));
   const int64_t t = ctx->upload_seq++;
@@ -317,6 +333,14 @@ extern "C" int wdc_upload_async(wdc_context* ctx, void* dst, const void* host, i
   ctx->h2d_bytes += bytes;
   *ticket = t;
   return WDC_OK;
+}
+
+extern "C" int wdc_upload_async(wdc_context* ctx, void* dst, const void* host, int64_t bytes, int64_t* ticket) {
+  return upload_async(ctx, dst, host, bytes, ticket, false);
+}
+
+extern "C" int wdc_upload_fresh_async(wdc_context* ctx, void* dst, const void* host, int64_t bytes, int64_t* ticket) {
+  return upload_async(ctx, dst, host, bytes, ticket, true);
 }
 
 extern "C" int wdc_wait_upload(wdc_context* ctx, int64_t ticket) {
@@ -374,6 +398,9 @@ extern "C" int wdc_capture_end(wdc_context* ctx, wdc_graph** out) {
   ctx->capture_arena = nullptr;
   cudaGraph_t graph = nullptr;
   cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+  // blocks of the main arena that were freed while the capture was open got no fence of their own (an event record
+  // would have been captured): this one stands for them
+  if (ctx->copy_stream) cudaEventRecord(ctx->free_fence, ctx->stream);
   cudaGraphExec_t exec = nullptr;
   if (e == cudaSuccess) e = cudaGraphInstantiate(&exec, graph, 0);
   if (e != cudaSuccess) {

@@ -92,6 +92,7 @@ SIGNATURES = {
     "wdc_graph_launch": (c_int, [c_void_p, c_void_p]),
     "wdc_graph_destroy": (c_int, [c_void_p, c_void_p]),
     "wdc_upload_async": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, POINTER(c_int64)]),
+    "wdc_upload_fresh_async": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, POINTER(c_int64)]),
     "wdc_wait_upload": (c_int, [c_void_p, c_int64]),
     "wdc_download_async": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, POINTER(c_int64)]),
     "wdc_wait_download": (c_int, [c_void_p, c_int64]),

@@ -160,6 +160,12 @@ class CudaReplica:
             for dst, src in zip(cap.inputs, dev_in):
                 ctx.wait_upload(src)
                 ctx._call("wdc_copy", _vp(dst.ptr), _vp(src.ptr), dst.length * 4)
+            # The transfer buffers go back to the arena now, BEFORE the graph is queued: the arena hands a freed block
+            # to another stream only behind everything queued up to the free, so a block freed after the launch
+            # would make the next step's transfer (copy stream) wait for this step's whole graph.
+            for t in dev_in:
+                t.dispose()
+            dev_in = []
             cap.launch()
             outs, owned = list(cap.outputs), False
         else:

@@ -541,3 +541,35 @@ def test_graph_replay_is_automatic_for_small_batches_only(cuda_context):
     assert auto.graph_replays == 3          # 40 > 32: not recorded
     auto.dispose()
     off.dispose()
+
+
+def test_a_transfer_into_reused_memory_waits_for_its_previous_tenant(cuda_context):
+    """prefetch_tensor binds wdc_upload_fresh_async, whose transfer (copy stream) waits only for the compute
+    stream's position at the arena's most recent free.  Here a 64 MB tensor is read by a queue of kernels, disposed
+    while they are still queued, and a transfer of other data into a new tensor of the same size (which the arena
+    serves from the block just freed) is started at once: every queued kernel must still have seen the old data."""
+    from webdnn_b200.backend import CPUTensor
+    from webdnn_b200.operators.cuda import CudaUnary
+    ctx = cuda_context
+    n = 16 << 20
+    old = ctx.pinned_array((n,), np.float32)
+    new = ctx.pinned_array((n,), np.float32)
+    old[...] = np.arange(n, dtype=np.float32) % 1000.0 - 500.0
+    new[...] = 7.0
+    relu = CudaUnary("Relu")
+    want = np.maximum(np.asarray(old), 0.0)
+    for _ in range(3):
+        t = ctx.prefetch_tensor(CPUTensor([n], "float32", old))
+        ctx.wait_upload(t)
+        outs = [relu.run(ctx, [t], 1)[0] for _ in range(24)]      # ~24 x 128 MB of queued reads of t
+        addr = t.ptr
+        t.dispose()
+        t2 = ctx.prefetch_tensor(CPUTensor([n], "float32", new))   # same size: the block just freed
+        reused = t2.ptr == addr
+        for o in outs:
+            assert np.array_equal(o.get_data(), want)
+            o.dispose()
+        ctx.wait_upload(t2)
+        assert np.array_equal(t2.get_data(), np.asarray(new))
+        t2.dispose()
+        assert reused     # otherwise the case did not exercise the reuse it is about

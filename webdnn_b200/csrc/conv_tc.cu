@@ -13,8 +13,9 @@
 // The tensor core's fp32 accumulator truncates when it aligns addends, which biases long sums
 // toward zero (measured ~0.15 ulp of the running sum per MMA).  To keep fp32-class accuracy through
 // 50+ layers the accumulation has two levels: TMEM holds the partial sum of one SEGMENT of 4 K blocks
-// (K = 128), and the epilogue warps add each finished segment into fp32 registers with
-// round-to-nearest while the next segment runs into the other TMEM buffer.
+// (K = 128; a unit's last segment also takes a remainder of 1-3), and the epilogue warps add each
+// finished segment into fp32 registers with round-to-nearest while the next segment runs into the
+// other TMEM buffer.
 //
 // Shared memory bandwidth (128 B/clk) is the scarce resource of a 3xTF32 kernel: with both operands
 // in shared memory a 128x128x8 MMA reads 8 KB per 64 clocks, which alone saturates it.  So the A
@@ -37,6 +38,13 @@
 //               columns; accumulators start at the per-channel shift; per segment tcgen05.ld + add into
 //               registers; at the end of a tile the residual tile (brought by TMA into the warp's
 //               staging buffer) is added, Relu applied, the result written over it and stored by TMA.
+//               Tiles of at most 64 columns with at least 4 K blocks: warps 8-11 only (all of the tile's
+//               columns each); warps 12-15 are then a second group of A splitters, and the two groups
+//               take alternate K blocks (duo_mode).
+// A barrier operation takes about 150 cycles to answer on this part even when its phase is long over,
+// so the roles on the serial path ask ahead with the non-blocking mbarrier.test_wait while they have
+// work in flight (the splitters while their shared-memory loads return, the MMA issuer between the k
+// steps of a K block) and fall back to the bounded blocking wait only when they asked too early.
 // tc_igemm_kernel<false> keeps the earlier producers for geometries an im2col tensor map cannot
 // express: warps 0-3 gather A from global memory themselves (8 x 128-bit loads per row and K block,
 // running 2 K blocks ahead).  Outputs whose row pitch is not a multiple of 16 bytes use the plain

@@ -575,6 +575,14 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
     ctx.profile_enable(False)
     barrier()
     dev_ms, e2e_ms, h2d_ms = max_over_ranks(dev_ms, e2e_ms, h2d_ms)
+    # ---- configurations 4 and 5 with their batch split over the ranks (N = 1: the whole batch, the reference point);
+    # before the peak measurement below, for the reason given there
+    sharded = None
+    if not args.no_extra:
+        barrier()
+        sharded = sharded_configs(ctx, stream, rank, world, barrier, max_over_ranks)
+        barrier()
+
     # the roofline's denominators, measured AFTER the timed regions: seconds of back-to-back cuBLAS GEMMs pull the
     # clock down under the power cap, and a step timed right behind them would pay for it
     tf32_peak = tf32_sustained = None
@@ -609,12 +617,6 @@ def run_ours(args, rank: int, local_rank: int, world: int) -> None:
         # the other ranks wait on the host (gloo): an NCCL barrier would keep a kernel spinning on the very GPUs
         # rank 0 is timing
         dist.barrier(group=host_group)
-
-    # ---- configurations 4 and 5 with their batch split over the ranks (N = 1: the whole batch, the reference point)
-    sharded = None
-    if not args.no_extra:
-        barrier()
-        sharded = sharded_configs(ctx, stream, rank, world, barrier, max_over_ranks)
 
     if rank == 0:
         value = G * args.steps / (dev_ms * 1e-3)

@@ -157,6 +157,26 @@ def test_replica_group_pipelined_steps_come_back_in_order():
     group.close()
 
 
+def test_replica_group_pipelined_step_that_fails_names_the_replica():
+    from webdnn_b200 import zoo
+    from webdnn_b200.lib import CudaBackendError
+    from webdnn_b200.replicas import ReplicaError, ReplicaGroup
+    model = zoo.mlp(6)
+    x = zoo.make_input((6, 784), "uniform")
+
+    class _FailsLater(_QueueingReplica):
+        def finish(self):
+            raise CudaBackendError(5, "a bounded device-side wait expired (kernel status 61)")
+
+    group = ReplicaGroup(replicas=[_QueueingReplica(model), _FailsLater(model)])
+    pend = group.run_async([x])
+    with pytest.raises(ReplicaError) as e:
+        pend.result(deadline_s=60)
+    assert list(e.value.failures) == [1] and e.value.failures[1].status == 5
+    group.close()      # what a caller does after a failed step
+    assert all(r.closed for r in group.replicas)
+
+
 def test_replica_group_names_the_replica_that_failed_or_stalled():
     from webdnn_b200 import zoo
     from webdnn_b200.lib import CudaBackendError

@@ -261,3 +261,25 @@ def test_lstm_rejects_what_the_kernels_do_not_implement():
     rt = onnx_io.decode_model(onnx_io.encode_model(onnx_io.Model(onnx_io.Graph("g", [ok], [], [], []))))
     acts = [a for a in rt.graph.node[0].attribute if a.name == "activations"][0]
     assert [s.decode() for s in acts.strings] == ["Sigmoid", "Tanh", "Tanh"]
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` times the CPU restatement of the reference's cpu backend (no GPU involved) and
+    prints one JSON line with the keys the benchmark contract names; here on a one-image sample."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--steps", "1",
+                          "--warmup", "0", "--ref-images", "1"], capture_output=True, text=True, timeout=600, cwd=root)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["metric"] == "resnet50_fp32_inference_images_per_sec"
+    assert d["unit"] == "images/s" and d["higher_is_better"] is True and d["value"] > 0
+    assert d["steps"] == 1 and d["n_gpus"] == 1 and d["dtype"] == "f32" and d["data"] == "synthetic"
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["value"] == d["value"]
+    assert d["e2e"] == {"value": d["value"], "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "workload" in d["config"]
